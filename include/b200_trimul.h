@@ -1,0 +1,131 @@
+/*
+ * C ABI of the B200 (sm_100a) triangle-multiplicative-update forward path.
+ *
+ * What it replaces in the reference project (CSSB-SNU/MiniWorld): the engine operator behind
+ * `TriangleMultiplication.forward(pair, mask)`, whose functional entry is
+ * `b200_infer.inference(leaves[11], flat_mask, flat_scale, direction)`
+ * (benchmarks/engine_ops/trimul_batch.py:24-39,66; direction 1 = outgoing, 2 = incoming), called by
+ * src/miniworld/blocks/msa_module.py:116-117, src/miniworld/blocks/template.py:84-85 and the
+ * FoldForge Pairformer block (benchmarks/protenix_finetune/patch_engine.py:89-90).
+ *
+ * Conventions
+ *  - All pointers are device pointers unless the name says `host`. Activations are bf16, LayerNorm
+ *    affine vectors fp32, linear weights bf16 or fp32 (`weight_dtype`), masks uint8 (non-zero = valid).
+ *  - d_pair = d_hidden = 128 is the only supported width (B200_TRIMUL_E_UNSUPPORTED otherwise).
+ *    N must be a multiple of 8 (16-byte rows for the bulk copies); callers pad with masked tokens.
+ *  - The caller owns every buffer, including the workspace; the library never allocates or frees
+ *    device memory and keeps no mutable global state besides a per-process cache of two function
+ *    pointers. Calls are asynchronous on `cuda_stream` and may be issued from any host thread.
+ *  - Return value: 0 on success, a negative B200_TRIMUL_E_* code otherwise. Device-side waits are
+ *    bounded; if one runs out the kernels finish, and `b200_trimul_read_status` reports a positive
+ *    device code (101 producer, 102 MMA issuer, 103 epilogue, 104 statistics, 105 drain).
+ *  - Intermediate layout ("row-plane"): left / right / tri are [B, rows, 128, N] bf16, i.e. for every
+ *    pair row a [channel, column] slab.
+ */
+#ifndef B200_TRIMUL_H_
+#define B200_TRIMUL_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_TRIMUL_OUTGOING 1 /* t_ij = sum_k a_ik b_jk  (einsum bikd,bjkd->bijd) */
+#define B200_TRIMUL_INCOMING 2 /* t_ij = sum_k a_ki b_kj  (einsum bkid,bkjd->bijd) */
+
+#define B200_TRIMUL_DTYPE_BF16 0
+#define B200_TRIMUL_DTYPE_F32 1
+
+#define B200_TRIMUL_OK 0
+#define B200_TRIMUL_E_NULL (-1)        /* a required pointer is null */
+#define B200_TRIMUL_E_SHAPE (-2)       /* bad B / N / rows / direction */
+#define B200_TRIMUL_E_UNSUPPORTED (-3) /* d_pair or d_hidden other than 128, N not a multiple of 8 */
+#define B200_TRIMUL_E_ALIGN (-4)       /* a pointer is not 16-byte aligned (workspace: 1024) */
+#define B200_TRIMUL_E_WORKSPACE (-5)   /* workspace too small */
+#define B200_TRIMUL_E_CUDA (-6)        /* a CUDA runtime / driver call failed; see b200_trimul_last_cuda_error */
+#define B200_TRIMUL_E_DEVICE (-7)      /* not an sm_100 device */
+
+/* Library version (major * 100 + minor). */
+int b200_trimul_version(void);
+
+/* Human-readable text for a status code (host or device). Never null. */
+const char* b200_trimul_strerror(int code);
+
+/* Last cudaError_t seen by this thread inside the library (0 if none). */
+int b200_trimul_last_cuda_error(void);
+
+/* Bytes of workspace needed by b200_trimul_forward for a full (unsharded) call. */
+int b200_trimul_workspace_bytes(int B, int N, int d_pair, int d_hidden, int direction, size_t* out_bytes);
+
+/* Offsets (bytes) of the regions inside a workspace: [0] status words, [1] packed weights,
+ * [2] left, [3] right, [4] tri. For tests and profilers that want to look at the stages. */
+int b200_trimul_workspace_layout(int B, int N, size_t out_offsets[5]);
+
+/* Bytes of the packed-weight block written by b200_trimul_pack_weights. */
+size_t b200_trimul_packed_bytes(void);
+
+/*
+ * Fold the LayerNorm affines into the six linears and write the packed block the kernels read.
+ * Replaces the engine's per-call `weight.to(pair.dtype)` casts and `prepack_lr_operand`
+ * (docs/archive/trimul-fusion/training-audit/harness/benchmarks/runners/bench.py:646-651).
+ * `bias_opt` is null or an array of six device pointers (left, left_gate, right, right_gate, gate, out),
+ * each null or fp32[128]; null everywhere is the reference layout (bias-free linears).
+ */
+int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const void* w_right,
+                             const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                             const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                             const float* ln_out_b, const void* const* bias_opt, void* packed, void* cuda_stream);
+
+/*
+ * Stage 1: LayerNorm + gated left/right projections + mask, for `rows` pair rows of each sample.
+ * z: [B, rows, N, 128] bf16 (rows row_begin .. row_begin+rows-1 of the full pair tensor);
+ * token_mask: [B, N] uint8 or null; pair_mask: [B, rows, N] uint8 (the same rows as z) or null;
+ * left / right: [B, rows, 128, N] bf16. `status` is a device int (e.g. the workspace start).
+ */
+int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
+                         void* left, void* right, int B, int N, int row_begin, int rows, float eps_in,
+                         int* status, void* cuda_stream);
+
+/*
+ * Stage 2: per-channel contraction for output rows row_begin .. row_begin+rows-1.
+ * outgoing: left is [B, rows, 128, N] (the local rows), right is [B, N, 128, N] (all rows).
+ * incoming: left and right are both [B, N, 128, N] (all rows k).
+ * tri: [B, rows, 128, N] bf16. Replaces the `torch.bmm` every reference backend uses for this step
+ * (docs/archive/trimul-fusion/inference.md:17).
+ */
+int b200_trimul_contract(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
+                         int direction, int* status, void* cuda_stream);
+
+/*
+ * Stage 3: output LayerNorm + output projection + sigmoid output gate (+ residual) for `rows` rows.
+ * tri: [B, rows, 128, N]; z, y: [B, rows, N, 128] bf16. y may alias z.
+ */
+int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows,
+                         float eps_in, float eps_out, int residual, int* status, void* cuda_stream);
+
+/*
+ * Whole forward on one device: pack -> prologue -> contract -> epilogue, all on `cuda_stream`.
+ * y = z + update when `residual` is non-zero (the reference module owns its residual,
+ * src/miniworld/blocks/msa_module.py:116-117), else the update alone.
+ * Mirrors `inference(leaves, flat_mask, flat_scale, direction)` of the reference engine
+ * (benchmarks/engine_ops/trimul_batch.py:66).
+ */
+int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
+                        const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                        const float* ln_in_w, const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,
+                        const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask, void* y,
+                        void* workspace, size_t workspace_bytes, int B, int N, int d_pair, int d_hidden,
+                        int direction, float eps_in, float eps_out, int residual, void* cuda_stream);
+
+/* Zero the status words at the start of a workspace (asynchronous). */
+int b200_trimul_clear_status(int* status, void* cuda_stream);
+
+/* Synchronise `cuda_stream` and copy the device status word to *host_status. */
+int b200_trimul_read_status(const int* status, void* cuda_stream, int* host_status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_TRIMUL_H_ */

@@ -1,0 +1,22 @@
+"""B200-native forward path of MiniWorld's Pairformer triangle multiplicative update.
+
+Public surface: the module classes (drop-in for ``miniworld_engine.modules.TriangleMultiplication`` as
+MiniWorld's blocks use it), the functional entry points over the C ABI, and the row-sharded /
+batch-parallel multi-GPU wrappers.
+"""
+
+from .modules import (  # noqa: F401
+    TriangleMultiplication,
+    TriangleMultiplicationIncoming,
+    TriangleMultiplicationOutgoing,
+    from_openfold_state_dict,
+    to_openfold_state_dict,
+)
+
+__all__ = [
+    "TriangleMultiplication",
+    "TriangleMultiplicationOutgoing",
+    "TriangleMultiplicationIncoming",
+    "to_openfold_state_dict",
+    "from_openfold_state_dict",
+]

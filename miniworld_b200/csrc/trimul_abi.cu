@@ -1,0 +1,520 @@
+// C-ABI entry points of the B200 triangle-multiplication forward path (see include/b200_trimul.h).
+// Host side only builds tensor maps, checks arguments and launches; all arithmetic is in the kernels.
+
+#include "../../include/b200_trimul.h"
+
+#include <atomic>
+#include <mutex>
+
+#include "contract.cuh"
+#include "epilogue.cuh"
+#include "prologue.cuh"
+
+namespace trimul {
+
+constexpr int kC = 128;
+constexpr size_t kStatusBytes = 1024;
+constexpr size_t kPackedMatrixBytes = 6 * 32768;
+constexpr size_t kPackedD1Off = kPackedMatrixBytes;            // float[4][128]
+constexpr size_t kPackedC3Off = kPackedMatrixBytes + 2048;     // float4[128]
+constexpr size_t kPackedBytes = kPackedMatrixBytes + 4096;     // 200704, a multiple of 1024
+
+static thread_local int tl_last_cuda_error = 0;
+
+#define TRIMUL_CUDA(expr)                             \
+  do {                                                \
+    cudaError_t _e = (expr);                          \
+    if (_e != cudaSuccess) {                          \
+      tl_last_cuda_error = static_cast<int>(_e);      \
+      return B200_TRIMUL_E_CUDA;                      \
+    }                                                 \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Weight packing: one warp per matrix row.
+//   matrices 0..3 (left, left gate, right, right gate): W' = bf16(0.5 W gamma_in), d = 0.5 (W beta_in + bias)
+//   matrix 4 (out):  W' = bf16(0.5 W gamma_out), s = rowsum(W'), d = 0.5 (W beta_out + bias)
+//   matrix 5 (gate): W' = bf16(0.5 W gamma_in),  s = rowsum(W'), d = 0.5 (W beta_in + bias)
+struct PackArgs {
+  const void* w[6];
+  const float* bias[6];
+  const float* ln_in_w;
+  const float* ln_in_b;
+  const float* ln_out_w;
+  const float* ln_out_b;
+  int f32_weights;
+};
+
+__global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* packed) {
+  const int gw = blockIdx.x * 4 + (threadIdx.x >> 5);  // 0 .. 767
+  const int lane = threadIdx.x & 31;
+  const int m = gw >> 7;
+  const int row = gw & 127;
+  const float* gamma = (m == 4) ? a.ln_out_w : a.ln_in_w;
+  const float* beta = (m == 4) ? a.ln_out_b : a.ln_in_b;
+  float w[4];
+  if (a.f32_weights) {
+    const float4 v = reinterpret_cast<const float4*>(a.w[m])[row * 32 + lane];
+    w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+  } else {
+    const uint2 v = reinterpret_cast<const uint2*>(a.w[m])[row * 32 + lane];
+    w[0] = bf16_lo(v.x), w[1] = bf16_hi(v.x), w[2] = bf16_lo(v.y), w[3] = bf16_hi(v.y);
+  }
+  const float4 g = reinterpret_cast<const float4*>(gamma)[lane];
+  const float4 b = reinterpret_cast<const float4*>(beta)[lane];
+  const float gg[4] = {g.x, g.y, g.z, g.w};
+  const float bb[4] = {b.x, b.y, b.z, b.w};
+  float s = 0.f, d = 0.f;
+  __nv_bfloat16 o[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    o[t] = __float2bfloat16_rn(0.5f * w[t] * gg[t]);
+    s += __bfloat162float(o[t]);
+    d = fmaf(w[t], bb[t], d);
+  }
+  uint2 ov;
+  ov.x = static_cast<uint32_t>(__bfloat16_as_ushort(o[0])) | (static_cast<uint32_t>(__bfloat16_as_ushort(o[1])) << 16);
+  ov.y = static_cast<uint32_t>(__bfloat16_as_ushort(o[2])) | (static_cast<uint32_t>(__bfloat16_as_ushort(o[3])) << 16);
+  reinterpret_cast<uint2*>(packed + static_cast<size_t>(m) * 32768)[row * 32 + lane] = ov;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+    d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
+  }
+  if (lane == 0) {
+    const float bias = a.bias[m] != nullptr ? a.bias[m][row] : 0.f;
+    d = 0.5f * (d + bias);
+    if (m < 4) {
+      reinterpret_cast<float*>(packed + kPackedD1Off)[m * 128 + row] = d;
+    } else {
+      float* c3 = reinterpret_cast<float*>(packed + kPackedC3Off) + row * 4;
+      if (m == 5) {
+        c3[0] = s;
+        c3[1] = d;
+      } else {
+        c3[2] = s;
+        c3[3] = d;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host helpers
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static std::once_flag once;
+  static EncodeTiledFn fn = nullptr;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+// bf16 tensor map with 128-byte swizzle. dims[0] is the contiguous dimension; strides (bytes) are for
+// dims[1..rank-1].
+static int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                    const uint32_t* box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) {
+    tl_last_cuda_error = static_cast<int>(cudaErrorNotSupported);
+    return B200_TRIMUL_E_CUDA;
+  }
+  cuuint64_t d[5];
+  cuuint64_t s[4];
+  cuuint32_t b[5];
+  cuuint32_t e[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    e[i] = 1;
+    if (i > 0) s[i - 1] = strides[i - 1];
+  }
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, s,
+                  b, e, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    tl_last_cuda_error = 100000 + static_cast<int>(r);
+    return B200_TRIMUL_E_CUDA;
+  }
+  return B200_TRIMUL_OK;
+}
+
+struct DeviceInfo {
+  int sms;
+  int cc_major;
+};
+
+static int device_info(DeviceInfo* info) {
+  int dev = 0;
+  TRIMUL_CUDA(cudaGetDevice(&dev));
+  TRIMUL_CUDA(cudaDeviceGetAttribute(&info->sms, cudaDevAttrMultiProcessorCount, dev));
+  TRIMUL_CUDA(cudaDeviceGetAttribute(&info->cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (info->cc_major != 10) return B200_TRIMUL_E_DEVICE;
+  return B200_TRIMUL_OK;
+}
+
+template <typename K>
+static int set_smem(K kernel, int bytes) {
+  TRIMUL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return B200_TRIMUL_OK;
+}
+
+static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+static int check_bn(int B, int N) {
+  if (B < 1 || N < 8) return B200_TRIMUL_E_SHAPE;
+  if (N % 8 != 0) return B200_TRIMUL_E_UNSUPPORTED;
+  if (static_cast<long long>(B) * N > 0x7FFFFFFFll / 128) return B200_TRIMUL_E_SHAPE;
+  return B200_TRIMUL_OK;
+}
+
+static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static size_t plane_tensor_bytes(int B, int rows, int N) {
+  return round_up(static_cast<size_t>(B) * rows * kC * N * 2, 1024);
+}
+
+// Column tile width of the contraction: the candidate that wastes the fewest padded columns.
+static int choose_bn(int N) {
+  const int cands[3] = {256, 192, 128};
+  int best = 256;
+  long long best_pad = -1;
+  for (int c : cands) {
+    const long long padded = static_cast<long long>((N + c - 1) / c) * c;
+    if (best_pad < 0 || padded < best_pad) {
+      best_pad = padded;
+      best = c;
+    }
+  }
+  return best;
+}
+
+template <int BN, bool INCOMING>
+static int launch_contract(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mt, const ContractParams& p,
+                           int sms, cudaStream_t stream) {
+  auto kernel = contract_kernel<BN, INCOMING>;
+  constexpr int smem = ContractSmem<BN>::kTotal;
+  int rc = set_smem(kernel, smem);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const long long tiles = static_cast<long long>(p.planes) * p.m_tiles * p.n_tiles;
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  kernel<<<grid, kContractThreads, smem, stream>>>(ma, mb, mt, p);
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
+}
+
+}  // namespace trimul
+
+using namespace trimul;
+
+extern "C" {
+
+int b200_trimul_version(void) { return 100; }
+
+const char* b200_trimul_strerror(int code) {
+  switch (code) {
+    case B200_TRIMUL_OK: return "ok";
+    case B200_TRIMUL_E_NULL: return "a required pointer is null";
+    case B200_TRIMUL_E_SHAPE: return "bad shape, row range or direction";
+    case B200_TRIMUL_E_UNSUPPORTED: return "unsupported size: d_pair = d_hidden = 128 and N a multiple of 8 are required";
+    case B200_TRIMUL_E_ALIGN: return "pointer not aligned (16 bytes; workspace and packed weights 1024)";
+    case B200_TRIMUL_E_WORKSPACE: return "workspace too small";
+    case B200_TRIMUL_E_CUDA: return "CUDA call failed (see b200_trimul_last_cuda_error)";
+    case B200_TRIMUL_E_DEVICE: return "device is not sm_100";
+    case kDevTimeoutProducer: return "device: copy producer gave up waiting";
+    case kDevTimeoutMma: return "device: MMA issuer gave up waiting";
+    case kDevTimeoutEpilogue: return "device: epilogue gave up waiting";
+    case kDevTimeoutStats: return "device: statistics warps gave up waiting";
+    case kDevTimeoutDrain: return "device: copies still in flight at exit";
+    default: return "unknown status";
+  }
+}
+
+int b200_trimul_last_cuda_error(void) { return tl_last_cuda_error; }
+
+size_t b200_trimul_packed_bytes(void) { return kPackedBytes; }
+
+int b200_trimul_workspace_layout(int B, int N, size_t out_offsets[5]) {
+  if (out_offsets == nullptr) return B200_TRIMUL_E_NULL;
+  int rc = check_bn(B, N);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const size_t t = plane_tensor_bytes(B, N, N);
+  out_offsets[0] = 0;
+  out_offsets[1] = kStatusBytes;
+  out_offsets[2] = kStatusBytes + kPackedBytes;
+  out_offsets[3] = out_offsets[2] + t;
+  out_offsets[4] = out_offsets[3] + t;
+  return B200_TRIMUL_OK;
+}
+
+int b200_trimul_workspace_bytes(int B, int N, int d_pair, int d_hidden, int direction, size_t* out_bytes) {
+  if (out_bytes == nullptr) return B200_TRIMUL_E_NULL;
+  if (d_pair != kC || d_hidden != kC) return B200_TRIMUL_E_UNSUPPORTED;
+  if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING) return B200_TRIMUL_E_SHAPE;
+  size_t off[5];
+  int rc = b200_trimul_workspace_layout(B, N, off);
+  if (rc != B200_TRIMUL_OK) return rc;
+  *out_bytes = off[4] + plane_tensor_bytes(B, N, N);
+  return B200_TRIMUL_OK;
+}
+
+int b200_trimul_clear_status(int* status, void* cuda_stream) {
+  if (status == nullptr) return B200_TRIMUL_E_NULL;
+  TRIMUL_CUDA(cudaMemsetAsync(status, 0, 64, static_cast<cudaStream_t>(cuda_stream)));
+  return B200_TRIMUL_OK;
+}
+
+int b200_trimul_read_status(const int* status, void* cuda_stream, int* host_status) {
+  if (status == nullptr || host_status == nullptr) return B200_TRIMUL_E_NULL;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  TRIMUL_CUDA(cudaMemcpyAsync(host_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  TRIMUL_CUDA(cudaStreamSynchronize(stream));
+  return B200_TRIMUL_OK;
+}
+
+int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const void* w_right,
+                             const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                             const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                             const float* ln_out_b, const void* const* bias_opt, void* packed, void* cuda_stream) {
+  if (!w_left || !w_left_gate || !w_right || !w_right_gate || !w_gate || !w_out || !ln_in_w || !ln_in_b ||
+      !ln_out_w || !ln_out_b || !packed)
+    return B200_TRIMUL_E_NULL;
+  if (weight_dtype != B200_TRIMUL_DTYPE_BF16 && weight_dtype != B200_TRIMUL_DTYPE_F32) return B200_TRIMUL_E_SHAPE;
+  PackArgs a;
+  a.w[0] = w_left;
+  a.w[1] = w_left_gate;
+  a.w[2] = w_right;
+  a.w[3] = w_right_gate;
+  a.w[4] = w_out;
+  a.w[5] = w_gate;
+  for (int i = 0; i < 6; ++i) {
+    if (!aligned(a.w[i], 16)) return B200_TRIMUL_E_ALIGN;
+    a.bias[i] = nullptr;
+  }
+  if (bias_opt != nullptr) {
+    // ABI order: left, left_gate, right, right_gate, gate, out  ->  matrix order: ..., out (4), gate (5)
+    for (int i = 0; i < 4; ++i) a.bias[i] = static_cast<const float*>(bias_opt[i]);
+    a.bias[5] = static_cast<const float*>(bias_opt[4]);
+    a.bias[4] = static_cast<const float*>(bias_opt[5]);
+  }
+  if (!aligned(ln_in_w, 16) || !aligned(ln_in_b, 16) || !aligned(ln_out_w, 16) || !aligned(ln_out_b, 16))
+    return B200_TRIMUL_E_ALIGN;
+  if (!aligned(packed, 1024)) return B200_TRIMUL_E_ALIGN;
+  a.ln_in_w = ln_in_w;
+  a.ln_in_b = ln_in_b;
+  a.ln_out_w = ln_out_w;
+  a.ln_out_b = ln_out_b;
+  a.f32_weights = weight_dtype == B200_TRIMUL_DTYPE_F32;
+  pack_kernel<<<192, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(a, static_cast<uint8_t*>(packed));
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
+}
+
+int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
+                         void* left, void* right, int B, int N, int row_begin, int rows, float eps_in, int* status,
+                         void* cuda_stream) {
+  if (!z || !packed || !left || !right || !status) return B200_TRIMUL_E_NULL;
+  int rc = check_bn(B, N);
+  if (rc != B200_TRIMUL_OK) return rc;
+  if (rows < 1 || row_begin < 0 || row_begin + rows > N) return B200_TRIMUL_E_SHAPE;
+  if (!aligned(z, 16) || !aligned(left, 16) || !aligned(right, 16) || !aligned(packed, 1024)) return B200_TRIMUL_E_ALIGN;
+  DeviceInfo info;
+  rc = device_info(&info);
+  if (rc != B200_TRIMUL_OK) return rc;
+
+  CUtensorMap map_z, map_w;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(kC), static_cast<uint64_t>(N), static_cast<uint64_t>(B) * rows};
+    const uint64_t strides[2] = {kC * 2ull, static_cast<uint64_t>(N) * kC * 2ull};
+    const uint32_t box[3] = {64, 128, 1};
+    rc = make_map(&map_z, z, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(kC), 6ull * 128};
+    const uint64_t strides[1] = {kC * 2ull};
+    const uint32_t box[2] = {64, 128};
+    rc = make_map(&map_w, packed, 2, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  PrologueParams p;
+  p.batch = B;
+  p.rows = rows;
+  p.n = N;
+  p.row_offset = row_begin;
+  p.tiles_per_row = (N + 127) / 128;
+  p.num_tiles = B * rows * p.tiles_per_row;
+  p.token_mask = token_mask;
+  p.pair_mask = pair_mask;
+  p.d1 = reinterpret_cast<const float*>(static_cast<const uint8_t*>(packed) + kPackedD1Off);
+  p.left_out = static_cast<__nv_bfloat16*>(left);
+  p.right_out = static_cast<__nv_bfloat16*>(right);
+  p.eps = eps_in;
+  p.status = status;
+  rc = set_smem(prologue_kernel, kProSmemBytes);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const int grid = p.num_tiles < info.sms ? p.num_tiles : info.sms;
+  prologue_kernel<<<grid, kPrologueThreads, kProSmemBytes, static_cast<cudaStream_t>(cuda_stream)>>>(map_z, map_w, p);
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
+}
+
+int b200_trimul_contract(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
+                         int direction, int* status, void* cuda_stream) {
+  if (!left || !right || !tri || !status) return B200_TRIMUL_E_NULL;
+  int rc = check_bn(B, N);
+  if (rc != B200_TRIMUL_OK) return rc;
+  if (rows < 1 || row_begin < 0 || row_begin + rows > N) return B200_TRIMUL_E_SHAPE;
+  if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING) return B200_TRIMUL_E_SHAPE;
+  if (!aligned(left, 16) || !aligned(right, 16) || !aligned(tri, 16)) return B200_TRIMUL_E_ALIGN;
+  DeviceInfo info;
+  rc = device_info(&info);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const bool incoming = direction == B200_TRIMUL_INCOMING;
+  const int bn = choose_bn(N);
+  const uint64_t n64 = static_cast<uint64_t>(N);
+  const uint64_t row_stride = kC * n64 * 2;  // bytes between consecutive pair rows
+  const uint64_t h_stride = n64 * 2;
+  const uint64_t left_rows = incoming ? n64 : static_cast<uint64_t>(rows);
+
+  CUtensorMap map_a, map_b, map_t;
+  {
+    const uint64_t dims[4] = {n64, left_rows, static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
+    const uint64_t strides[3] = {row_stride, h_stride, left_rows * row_stride};
+    const uint32_t box_out[4] = {64, 128, 1, 1};
+    const uint32_t box_in[4] = {64, 64, 1, 1};
+    rc = make_map(&map_a, left, 4, dims, strides, incoming ? box_in : box_out);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[4] = {n64, n64, static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
+    const uint64_t strides[3] = {row_stride, h_stride, n64 * row_stride};
+    const uint32_t box_out[4] = {64, static_cast<uint32_t>(bn), 1, 1};
+    const uint32_t box_in[4] = {64, 64, 1, 1};
+    rc = make_map(&map_b, right, 4, dims, strides, incoming ? box_in : box_out);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[4] = {n64, static_cast<uint64_t>(rows), static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
+    const uint64_t strides[3] = {row_stride, h_stride, static_cast<uint64_t>(rows) * row_stride};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    rc = make_map(&map_t, tri, 4, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  ContractParams p;
+  p.H = kC;
+  p.planes = B * kC;
+  p.m_tiles = (rows + kBM - 1) / kBM;
+  p.n_tiles = (N + bn - 1) / bn;
+  p.num_kb = (N + kBK - 1) / kBK;
+  p.a_col_off = incoming ? row_begin : 0;
+  p.n_cols = N;
+  p.status = status;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (!incoming) {
+    if (bn == 256) return launch_contract<256, false>(map_a, map_b, map_t, p, info.sms, stream);
+    if (bn == 192) return launch_contract<192, false>(map_a, map_b, map_t, p, info.sms, stream);
+    return launch_contract<128, false>(map_a, map_b, map_t, p, info.sms, stream);
+  }
+  if (bn == 256) return launch_contract<256, true>(map_a, map_b, map_t, p, info.sms, stream);
+  if (bn == 192) return launch_contract<192, true>(map_a, map_b, map_t, p, info.sms, stream);
+  return launch_contract<128, true>(map_a, map_b, map_t, p, info.sms, stream);
+}
+
+int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows,
+                         float eps_in, float eps_out, int residual, int* status, void* cuda_stream) {
+  if (!tri || !z || !packed || !y || !status) return B200_TRIMUL_E_NULL;
+  int rc = check_bn(B, N);
+  if (rc != B200_TRIMUL_OK) return rc;
+  if (rows < 1 || rows > N) return B200_TRIMUL_E_SHAPE;
+  if (!aligned(tri, 16) || !aligned(z, 16) || !aligned(y, 16) || !aligned(packed, 1024)) return B200_TRIMUL_E_ALIGN;
+  DeviceInfo info;
+  rc = device_info(&info);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const uint64_t n64 = static_cast<uint64_t>(N);
+  const uint64_t nrows = static_cast<uint64_t>(B) * rows;
+
+  CUtensorMap map_t, map_z, map_y, map_w;
+  {
+    const uint64_t dims[3] = {n64, static_cast<uint64_t>(kC), nrows};
+    const uint64_t strides[2] = {n64 * 2, kC * n64 * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    rc = make_map(&map_t, tri, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(kC), n64, nrows};
+    const uint64_t strides[2] = {kC * 2ull, n64 * kC * 2ull};
+    const uint32_t box[3] = {64, 128, 1};
+    rc = make_map(&map_z, z, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = make_map(&map_y, y, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(kC), 6ull * 128};
+    const uint64_t strides[1] = {kC * 2ull};
+    const uint32_t box[2] = {64, 128};
+    rc = make_map(&map_w, packed, 2, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  EpilogueParams p;
+  p.tiles_per_row = (N + 127) / 128;
+  p.num_tiles = static_cast<int>(nrows) * p.tiles_per_row;
+  p.c3 = reinterpret_cast<const float4*>(static_cast<const uint8_t*>(packed) + kPackedC3Off);
+  p.eps_in = eps_in;
+  p.eps_out = eps_out;
+  p.residual = residual;
+  p.status = status;
+  rc = set_smem(epilogue_kernel, kEpiSmemBytes);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const int grid = p.num_tiles < info.sms ? p.num_tiles : info.sms;
+  epilogue_kernel<<<grid, kEpilogueThreads, kEpiSmemBytes, static_cast<cudaStream_t>(cuda_stream)>>>(map_t, map_z, map_y,
+                                                                                                       map_w, p);
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
+}
+
+int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
+                        const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                        const float* ln_in_w, const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,
+                        const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask, void* y,
+                        void* workspace, size_t workspace_bytes, int B, int N, int d_pair, int d_hidden,
+                        int direction, float eps_in, float eps_out, int residual, void* cuda_stream) {
+  if (!z || !y || !workspace) return B200_TRIMUL_E_NULL;
+  size_t need = 0;
+  int rc = b200_trimul_workspace_bytes(B, N, d_pair, d_hidden, direction, &need);
+  if (rc != B200_TRIMUL_OK) return rc;
+  if (workspace_bytes < need) return B200_TRIMUL_E_WORKSPACE;
+  if (!aligned(workspace, 1024)) return B200_TRIMUL_E_ALIGN;
+  size_t off[5];
+  rc = b200_trimul_workspace_layout(B, N, off);
+  if (rc != B200_TRIMUL_OK) return rc;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int* status = reinterpret_cast<int*>(ws + off[0]);
+  void* packed = ws + off[1];
+  void* left = ws + off[2];
+  void* right = ws + off[3];
+  void* tri = ws + off[4];
+  rc = b200_trimul_clear_status(status, cuda_stream);
+  if (rc != B200_TRIMUL_OK) return rc;
+  rc = b200_trimul_pack_weights(w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out, weight_dtype, ln_in_w,
+                                ln_in_b, ln_out_w, ln_out_b, bias_opt, packed, cuda_stream);
+  if (rc != B200_TRIMUL_OK) return rc;
+  rc = b200_trimul_prologue(z, packed, token_mask, pair_mask, left, right, B, N, 0, N, eps_in, status, cuda_stream);
+  if (rc != B200_TRIMUL_OK) return rc;
+  rc = b200_trimul_contract(left, right, tri, B, N, 0, N, direction, status, cuda_stream);
+  if (rc != B200_TRIMUL_OK) return rc;
+  return b200_trimul_epilogue(tri, z, packed, y, B, N, N, eps_in, eps_out, residual, status, cuda_stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,286 @@
+"""Functional entry points: torch tensors in, C-ABI kernels on the current CUDA stream, torch tensors out.
+
+PyTorch is used only for device memory and streams. Every function raises ``RuntimeError`` when the
+CUDA library is missing or a call fails; nothing here falls back to PyTorch arithmetic.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_size_t, c_void_p
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+D = 128  # d_pair = d_hidden supported by the kernels
+
+WEIGHT_KEYS = ("to_left.weight", "to_left_gate.weight", "to_right.weight", "to_right_gate.weight", "to_gate.weight", "to_out.weight")
+LN_KEYS = ("ln_pair.weight", "ln_pair.bias", "ln_out.weight", "ln_out.bias")
+BIAS_ORDER = ("to_left", "to_left_gate", "to_right", "to_right_gate", "to_gate", "to_out")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this path has no CPU implementation")
+
+
+def aligned_empty(nbytes: int, device: torch.device, align: int = 1024) -> torch.Tensor:
+    """uint8 buffer of ``nbytes`` whose data pointer is ``align``-byte aligned."""
+    raw = torch.empty(nbytes + align, dtype=torch.uint8, device=device)
+    off = (-raw.data_ptr()) % align
+    return raw[off : off + nbytes]
+
+
+def workspace_bytes(B: int, N: int, outgoing: bool = True) -> int:
+    out = c_size_t(0)
+    rc = _lib.load().b200_trimul_workspace_bytes(B, N, D, D, _lib.OUTGOING if outgoing else _lib.INCOMING, ctypes.byref(out))
+    _lib.check(rc, "b200_trimul_workspace_bytes")
+    return int(out.value)
+
+
+def workspace_layout(B: int, N: int) -> list[int]:
+    arr = (c_size_t * 5)()
+    rc = _lib.load().b200_trimul_workspace_layout(B, N, arr)
+    _lib.check(rc, "b200_trimul_workspace_layout")
+    return [int(v) for v in arr]
+
+
+def packed_bytes() -> int:
+    return int(_lib.load().b200_trimul_packed_bytes())
+
+
+def as_mask_u8(mask: Optional[torch.Tensor], device: torch.device) -> Optional[torch.Tensor]:
+    """Bool / integer / float mask -> contiguous uint8 (non-zero = valid) on ``device``."""
+    if mask is None:
+        return None
+    m = mask.to(device)
+    if m.dtype == torch.bool:
+        return m.contiguous().view(torch.uint8)
+    return (m != 0).contiguous().view(torch.uint8)
+
+
+class _Weights:
+    """Validated pointers of one parameter set (all weights in one dtype, LN affine fp32)."""
+
+    def __init__(self, params: dict, biases: Optional[dict], device: torch.device):
+        ws = [params[k] for k in WEIGHT_KEYS]
+        dt = ws[0].dtype
+        if dt not in (torch.bfloat16, torch.float32):
+            raise RuntimeError(f"linear weights must be bf16 or fp32, got {dt}")
+        keep = []
+        for k, w in zip(WEIGHT_KEYS, ws):
+            _require_cuda(w, k)
+            if w.dtype != dt:
+                raise RuntimeError("all six linear weights must share one dtype")
+            if tuple(w.shape) != (D, D):
+                raise RuntimeError(f"{k}: expected shape ({D},{D}), got {tuple(w.shape)} (only d_pair = d_hidden = 128 is supported)")
+            keep.append(w.detach().contiguous())
+        lns = []
+        for k in LN_KEYS:
+            v = params[k]
+            _require_cuda(v, k)
+            if tuple(v.shape) != (D,):
+                raise RuntimeError(f"{k}: expected shape ({D},)")
+            lns.append(v.detach().to(torch.float32).contiguous())
+        self.weights = keep
+        self.lns = lns
+        self.dtype_code = _lib.DTYPE_BF16 if dt == torch.bfloat16 else _lib.DTYPE_F32
+        self.bias_tensors = None
+        self.bias_array = None
+        if biases:
+            bt = []
+            arr = (c_void_p * 6)()
+            for i, k in enumerate(BIAS_ORDER):
+                b = biases.get(k)
+                if b is None:
+                    bt.append(None)
+                    arr[i] = None
+                else:
+                    bb = b.detach().to(device=device, dtype=torch.float32).contiguous()
+                    if tuple(bb.shape) != (D,):
+                        raise RuntimeError(f"bias {k}: expected shape ({D},)")
+                    bt.append(bb)
+                    arr[i] = bb.data_ptr()
+            self.bias_tensors = bt
+            self.bias_array = arr
+
+
+def _check_z(z: torch.Tensor) -> tuple[int, int]:
+    _require_cuda(z, "pair tensor")
+    if z.dtype != torch.bfloat16:
+        raise RuntimeError(f"pair tensor must be bf16, got {z.dtype}")
+    if z.dim() != 4 or z.shape[3] != D:
+        raise RuntimeError(f"pair tensor must be [B, rows, N, {D}], got {tuple(z.shape)}")
+    if not z.is_contiguous():
+        raise RuntimeError("pair tensor must be contiguous")
+    return int(z.shape[0]), int(z.shape[2])
+
+
+def pack_weights(params: dict, packed: torch.Tensor, biases: Optional[dict] = None) -> None:
+    w = _Weights(params, biases, packed.device)
+    with torch.cuda.device(packed.device):
+        rc = _lib.load().b200_trimul_pack_weights(
+            *[_ptr(t) for t in w.weights[:4]],
+            _ptr(w.weights[4]),
+            _ptr(w.weights[5]),
+            w.dtype_code,
+            *[_ptr(t) for t in w.lns],
+            w.bias_array,
+            _ptr(packed),
+            _stream(packed.device),
+        )
+    _lib.check(rc, "b200_trimul_pack_weights")
+
+
+def prologue(
+    z: torch.Tensor,
+    packed: torch.Tensor,
+    left: torch.Tensor,
+    right: torch.Tensor,
+    status: torch.Tensor,
+    token_mask: Optional[torch.Tensor] = None,
+    pair_mask: Optional[torch.Tensor] = None,
+    row_begin: int = 0,
+    eps_in: float = 1e-5,
+) -> None:
+    """``z`` holds pair rows row_begin .. row_begin+rows-1: [B, rows, N, 128]; writes left/right [B, rows, 128, N]."""
+    B, N = _check_z(z)
+    rows = int(z.shape[1])
+    tm = as_mask_u8(token_mask, z.device)
+    pm = as_mask_u8(pair_mask, z.device)
+    with torch.cuda.device(z.device):
+        rc = _lib.load().b200_trimul_prologue(
+            _ptr(z), _ptr(packed), _ptr(tm), _ptr(pm), _ptr(left), _ptr(right), B, N, row_begin, rows, float(eps_in),
+            _ptr(status), _stream(z.device),
+        )
+    _lib.check(rc, "b200_trimul_prologue")
+
+
+def contract(
+    left: torch.Tensor,
+    right: torch.Tensor,
+    tri: torch.Tensor,
+    status: torch.Tensor,
+    B: int,
+    N: int,
+    row_begin: int,
+    rows: int,
+    outgoing: bool,
+) -> None:
+    with torch.cuda.device(tri.device):
+        rc = _lib.load().b200_trimul_contract(
+            _ptr(left), _ptr(right), _ptr(tri), B, N, row_begin, rows, _lib.OUTGOING if outgoing else _lib.INCOMING,
+            _ptr(status), _stream(tri.device),
+        )
+    _lib.check(rc, "b200_trimul_contract")
+
+
+def epilogue(
+    tri: torch.Tensor,
+    z: torch.Tensor,
+    packed: torch.Tensor,
+    y: torch.Tensor,
+    status: torch.Tensor,
+    eps_in: float = 1e-5,
+    eps_out: float = 1e-5,
+    residual: bool = True,
+) -> None:
+    B, N = _check_z(z)
+    rows = int(z.shape[1])
+    with torch.cuda.device(z.device):
+        rc = _lib.load().b200_trimul_epilogue(
+            _ptr(tri), _ptr(z), _ptr(packed), _ptr(y), B, N, rows, float(eps_in), float(eps_out), int(bool(residual)),
+            _ptr(status), _stream(z.device),
+        )
+    _lib.check(rc, "b200_trimul_epilogue")
+
+
+def read_status(status: torch.Tensor) -> int:
+    """Synchronise the current stream and return the device status word (0 = ok)."""
+    out = c_int(0)
+    with torch.cuda.device(status.device):
+        rc = _lib.load().b200_trimul_read_status(_ptr(status), _stream(status.device), ctypes.byref(out))
+    _lib.check(rc, "b200_trimul_read_status")
+    return int(out.value)
+
+
+def check_status(status: torch.Tensor, what: str = "trimul") -> None:
+    code = read_status(status)
+    if code != 0:
+        raise RuntimeError(f"{what}: {_lib.strerror(code)} [{code}]")
+
+
+def trimul_forward(
+    z: torch.Tensor,
+    params: dict,
+    mask: Optional[torch.Tensor] = None,
+    *,
+    outgoing: bool = True,
+    eps_in: float = 1e-5,
+    eps_out: float = 1e-5,
+    pair_mask: Optional[torch.Tensor] = None,
+    residual: bool = True,
+    biases: Optional[dict] = None,
+    workspace: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    check: bool = False,
+) -> torch.Tensor:
+    """One module forward on one GPU. ``z`` [B,N,N,128] bf16; ``mask`` Bool[B,N] or None; returns ``out``.
+
+    ``workspace`` (uint8, 1024-aligned, at least :func:`workspace_bytes`) is allocated when not given.
+    ``check=True`` synchronises and raises if a device-side wait gave up.
+    """
+    B, N = _check_z(z)
+    if z.shape[1] != N:
+        raise RuntimeError(f"pair tensor must be square in its token dims, got {tuple(z.shape)}")
+    dev = z.device
+    w = _Weights(params, biases, dev)
+    need = workspace_bytes(B, N, outgoing)
+    if workspace is None:
+        workspace = aligned_empty(need, dev)
+    elif workspace.numel() * workspace.element_size() < need:
+        raise RuntimeError(f"workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
+    if out is None:
+        out = torch.empty_like(z)
+    tm = as_mask_u8(mask, dev)
+    pm = as_mask_u8(pair_mask, dev)
+    if tm is not None and tuple(tm.shape) != (B, N):
+        raise RuntimeError(f"token mask must be [B, N] = ({B}, {N}), got {tuple(tm.shape)}")
+    if pm is not None and tuple(pm.shape) != (B, N, N):
+        raise RuntimeError(f"pair mask must be [B, N, N], got {tuple(pm.shape)}")
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200_trimul_forward(
+            _ptr(z),
+            *[_ptr(t) for t in w.weights],
+            w.dtype_code,
+            *[_ptr(t) for t in w.lns],
+            w.bias_array,
+            _ptr(tm),
+            _ptr(pm),
+            _ptr(out),
+            _ptr(workspace),
+            workspace.numel() * workspace.element_size(),
+            B,
+            N,
+            D,
+            D,
+            _lib.OUTGOING if outgoing else _lib.INCOMING,
+            float(eps_in),
+            float(eps_out),
+            int(bool(residual)),
+            _stream(dev),
+        )
+    _lib.check(rc, "b200_trimul_forward")
+    if check:
+        check_status(workspace[:4].view(torch.int32), "b200_trimul_forward")
+    return out

@@ -1,0 +1,230 @@
+"""Host-side mirror of the reference module interface for the triangle multiplicative update.
+
+``TriangleMultiplication`` keeps the constructor, ``forward(pair, mask)`` signature, parameter names and
+``state_dict`` layout of ``miniworld_engine.modules.TriangleMultiplication`` as MiniWorld uses it
+(``src/miniworld/blocks/msa_module.py:60-71,116-117``, ``src/miniworld/blocks/template.py:41-52,84-85``
+in the reference project): parameters ``ln_pair.{weight,bias}``, ``to_left``, ``to_left_gate``,
+``to_right``, ``to_right_gate``, ``ln_out.{weight,bias}``, ``to_gate``, ``to_out`` (all linears
+bias-free, ``benchmarks/protenix_finetune/patch_engine.py:25-29,51``); the module returns
+``pair + update`` (it owns the residual).  ``TriangleMultiplicationOutgoing`` / ``...Incoming`` are the
+OpenFold-style names with ``forward(z, pair_mask)``.
+
+Only the inference path exists (no autograd, no dropout): calling it with gradients enabled on inputs
+that require them, or in training mode with ``p_drop > 0``, raises ``NotImplementedError``.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from . import functional as F_
+
+D_SUPPORTED = 128
+
+# reference name -> OpenFold / Protenix name (benchmarks/protenix_finetune/patch_engine.py:25-29)
+OPENFOLD_ALIASES = {
+    "ln_pair": "layer_norm_in",
+    "to_left": "linear_a_p",
+    "to_left_gate": "linear_a_g",
+    "to_right": "linear_b_p",
+    "to_right_gate": "linear_b_g",
+    "ln_out": "layer_norm_out",
+    "to_gate": "linear_g",
+    "to_out": "linear_z",
+}
+
+_ACCEPTED_IMPLEMENTATIONS = {None, "b200", "miniworld", "miniworld_engine", "engine", "cuda"}
+
+
+def to_openfold_state_dict(sd: dict) -> dict:
+    """Rename reference keys (``to_left.weight`` ...) to OpenFold keys (``linear_a_p.weight`` ...)."""
+    out = {}
+    for k, v in sd.items():
+        head, _, tail = k.partition(".")
+        out[f"{OPENFOLD_ALIASES.get(head, head)}.{tail}"] = v
+    return out
+
+
+def from_openfold_state_dict(sd: dict) -> dict:
+    """Inverse of :func:`to_openfold_state_dict`; OpenFold bias entries of the linears are rejected."""
+    inv = {v: k for k, v in OPENFOLD_ALIASES.items()}
+    out = {}
+    for k, v in sd.items():
+        head, _, tail = k.partition(".")
+        name = inv.get(head, head)
+        if tail == "bias" and not name.startswith("ln_"):
+            raise KeyError(f"{k}: the reference layout has bias-free linears; pass biases explicitly via set_biases()")
+        out[f"{name}.{tail}"] = v
+    return out
+
+
+class TriangleMultiplication(nn.Module):
+    """Triangle multiplicative update, forward only, on B200 kernels.
+
+    ``forward(pair [B,N,N,d_pair] bf16, mask Bool[B,N] | None) -> pair + update`` (bf16).
+    Linear weights may be bf16 or fp32 masters; LayerNorm affine parameters are kept in fp32 whatever
+    ``.to(dtype)`` is applied to the module (``src/miniworld/layers/primitives.py:86-88``).
+    ``ln_pair.eps`` / ``ln_out.eps`` are read at call time.
+    """
+
+    def __init__(
+        self,
+        d_pair: int,
+        d_hidden: Optional[int] = None,
+        outgoing: bool = True,
+        implementation=None,
+        p_drop: float = 0.0,
+        residual: bool = True,
+        check_status: bool = False,
+    ):
+        super().__init__()
+        d_hidden = d_pair if d_hidden is None else d_hidden
+        if d_pair != D_SUPPORTED or d_hidden != D_SUPPORTED:
+            raise NotImplementedError(
+                f"only d_pair = d_hidden = {D_SUPPORTED} is implemented on this path (got {d_pair}, {d_hidden})"
+            )
+        impl = getattr(implementation, "value", implementation)
+        impl = impl.lower() if isinstance(impl, str) else impl
+        if impl not in _ACCEPTED_IMPLEMENTATIONS:
+            raise ValueError(f"implementation={implementation!r}: this module has exactly one backend (B200 CUDA kernels)")
+        self.d_pair = d_pair
+        self.d_hidden = d_hidden
+        self.outgoing = bool(outgoing)
+        self.p_drop = float(p_drop)
+        self.residual = bool(residual)
+        self.check_status = bool(check_status)
+        self.ln_pair = nn.LayerNorm(d_pair, eps=1e-5)
+        self.to_left = nn.Linear(d_pair, d_hidden, bias=False)
+        self.to_left_gate = nn.Linear(d_pair, d_hidden, bias=False)
+        self.to_right = nn.Linear(d_pair, d_hidden, bias=False)
+        self.to_right_gate = nn.Linear(d_pair, d_hidden, bias=False)
+        self.ln_out = nn.LayerNorm(d_hidden, eps=1e-5)
+        self.to_gate = nn.Linear(d_pair, d_pair, bias=False)
+        self.to_out = nn.Linear(d_hidden, d_pair, bias=False)
+        # the reference initialises the two output linears to zero ("init='zero'")
+        nn.init.zeros_(self.to_gate.weight)
+        nn.init.zeros_(self.to_out.weight)
+        self._biases: Optional[dict] = None
+        self._workspace: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ dtype handling
+    def _apply(self, fn, recurse=True):
+        super()._apply(fn, recurse)
+        for ln in (self.ln_pair, self.ln_out):  # LayerNorm affine stays fp32
+            for p in ln.parameters(recurse=False):
+                if p.dtype != torch.float32:
+                    p.data = p.data.to(torch.float32)
+        self._workspace = None
+        return self
+
+    def set_biases(self, biases: Optional[dict]) -> None:
+        """Optional fp32[d] biases for the linears, keys ``to_left`` ... ``to_out`` (None = reference layout).
+
+        They are not parameters and are not part of the ``state_dict`` (the reference module has none).
+        """
+        self._biases = None if not biases else dict(biases)
+
+    def _params(self) -> dict:
+        return {
+            "ln_pair.weight": self.ln_pair.weight,
+            "ln_pair.bias": self.ln_pair.bias,
+            "to_left.weight": self.to_left.weight,
+            "to_left_gate.weight": self.to_left_gate.weight,
+            "to_right.weight": self.to_right.weight,
+            "to_right_gate.weight": self.to_right_gate.weight,
+            "ln_out.weight": self.ln_out.weight,
+            "ln_out.bias": self.ln_out.bias,
+            "to_gate.weight": self.to_gate.weight,
+            "to_out.weight": self.to_out.weight,
+        }
+
+    def load_openfold_state_dict(self, sd: dict, strict: bool = True):
+        return self.load_state_dict(from_openfold_state_dict(sd), strict=strict)
+
+    def _get_workspace(self, B: int, N: int, device: torch.device) -> torch.Tensor:
+        need = F_.workspace_bytes(B, N, self.outgoing)
+        ws = self._workspace
+        if ws is None or ws.device != device or ws.numel() < need:
+            ws = F_.aligned_empty(need, device)
+            self._workspace = ws
+        return ws
+
+    def _run(self, pair: torch.Tensor, token_mask, pair_mask) -> torch.Tensor:
+        if self.training and self.p_drop > 0.0:
+            raise NotImplementedError("row-shared dropout (training mode with p_drop > 0) is not implemented on this path")
+        if torch.is_grad_enabled() and pair.requires_grad:
+            raise NotImplementedError("backward is not implemented: call under torch.no_grad() or with an input that does not require grad")
+        if pair.dim() != 4 or pair.shape[1] != pair.shape[2] or pair.shape[3] != self.d_pair:
+            raise RuntimeError(f"pair must be [B, N, N, {self.d_pair}], got {tuple(pair.shape)}")
+        if not pair.is_cuda:
+            raise RuntimeError("pair must be a CUDA tensor: this module has no CPU implementation")
+        in_dtype = pair.dtype
+        z = pair.detach()
+        if z.dtype != torch.bfloat16:
+            z = z.to(torch.bfloat16)
+        z = z.contiguous()
+        B, N = int(z.shape[0]), int(z.shape[1])
+        pad = (-N) % 8
+        if pad:
+            # pad with masked tokens: masked rows/columns of left/right are zero, so the crop is exact
+            zp = z.new_zeros(B, N + pad, N + pad, self.d_pair)
+            zp[:, :N, :N] = z
+            tm = torch.ones(B, N, dtype=torch.bool, device=z.device) if token_mask is None else token_mask.to(z.device) != 0
+            tmp = torch.zeros(B, N + pad, dtype=torch.bool, device=z.device)
+            tmp[:, :N] = tm
+            pmp = None
+            if pair_mask is not None:
+                pmp = torch.zeros(B, N + pad, N + pad, dtype=torch.bool, device=z.device)
+                pmp[:, :N, :N] = pair_mask.to(z.device) != 0
+            z, token_mask, pair_mask = zp, tmp, pmp
+        Np = N + pad
+        with torch.no_grad():
+            y = F_.trimul_forward(
+                z,
+                self._params(),
+                token_mask,
+                outgoing=self.outgoing,
+                eps_in=float(self.ln_pair.eps),
+                eps_out=float(self.ln_out.eps),
+                pair_mask=pair_mask,
+                residual=self.residual,
+                biases=self._biases,
+                workspace=self._get_workspace(B, Np, z.device),
+                check=self.check_status,
+            )
+        if pad:
+            y = y[:, :N, :N].contiguous()
+        return y if in_dtype == torch.bfloat16 else y.to(in_dtype)
+
+    def forward(self, pair: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if mask is not None and mask.dim() != 2:
+            raise RuntimeError(f"mask must be a token mask [B, N], got {tuple(mask.shape)}")
+        return self._run(pair, mask, None)
+
+
+class _OpenFoldStyle(TriangleMultiplication):
+    """``forward(z, pair_mask)`` where ``pair_mask`` is None, a token mask [B,N] or a pair mask [B,N,N]."""
+
+    _outgoing = True
+
+    def __init__(self, d_pair: int = D_SUPPORTED, d_hidden: Optional[int] = None, residual: bool = True, **kw):
+        kw.pop("outgoing", None)
+        super().__init__(d_pair, d_hidden, outgoing=self._outgoing, residual=residual, **kw)
+
+    def forward(self, z: torch.Tensor, pair_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if pair_mask is None or pair_mask.dim() == 2:
+            return self._run(z, pair_mask, None)
+        if pair_mask.dim() == 3:
+            return self._run(z, None, pair_mask)
+        raise RuntimeError(f"pair_mask must be [B,N] or [B,N,N], got {tuple(pair_mask.shape)}")
+
+
+class TriangleMultiplicationOutgoing(_OpenFoldStyle):
+    _outgoing = True
+
+
+class TriangleMultiplicationIncoming(_OpenFoldStyle):
+    _outgoing = False

@@ -1,0 +1,46 @@
+"""Shared helpers of the parity tests (the oracle is used only here, as the checker)."""
+
+import torch
+
+from oracle import trimul_oracle as oracle
+
+REL_FRO_TOL = 5e-3  # relative Frobenius error of the module output, bf16 I/O
+MAX_ABS_TOL = 3e-2  # max abs error of the module output, bf16 I/O
+UPDATE_REL_TOL = 1.2e-2  # the update alone (y - z) is held to a looser, separately stated bound
+
+
+def to_row_plane(x_bnnh: torch.Tensor) -> torch.Tensor:
+    """[B, N, N, H] channel-last -> [B, N, H, N] row-plane (the GPU intermediate layout)."""
+    return x_bnnh.permute(0, 1, 3, 2).contiguous()
+
+
+def from_row_plane(x_bnhn: torch.Tensor) -> torch.Tensor:
+    return x_bnhn.permute(0, 1, 3, 2).contiguous()
+
+
+def params_to(params: dict, device) -> dict:
+    return {k: v.to(device) for k, v in params.items()}
+
+
+def rand_params(seed: int, dtype=torch.bfloat16, c: int = 128, ln_bias_scale: float = 0.02) -> dict:
+    from miniworld_b200.synthetic import make_params
+
+    g = torch.Generator().manual_seed(seed)
+    p = make_params(g, c, c, dtype)
+    if ln_bias_scale != 0.02:
+        p["ln_pair.bias"] = p["ln_pair.bias"] * (ln_bias_scale / 0.02)
+        p["ln_out.bias"] = p["ln_out.bias"] * (ln_bias_scale / 0.02)
+    return p
+
+
+def assert_module_parity(y_gpu: torch.Tensor, y_ref: torch.Tensor, z: torch.Tensor, what: str = "") -> None:
+    y = y_gpu.detach().float().cpu()
+    ref = y_ref.detach().float().cpu()
+    zf = z.detach().float().cpu()
+    assert torch.isfinite(y).all(), what
+    rel = oracle.rel_frobenius(y, ref)
+    mab = oracle.max_abs(y, ref)
+    upd = oracle.rel_frobenius(y - zf, ref - zf)
+    assert rel <= REL_FRO_TOL, (what, "rel_frobenius", rel)
+    assert mab <= MAX_ABS_TOL, (what, "max_abs", mab)
+    assert upd <= UPDATE_REL_TOL, (what, "update rel_frobenius", upd)

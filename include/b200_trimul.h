@@ -82,11 +82,12 @@ int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const 
  * Stage 1: LayerNorm + gated left/right projections + mask, for `rows` pair rows of each sample.
  * z: [B, rows, N, 128] bf16 (rows row_begin .. row_begin+rows-1 of the full pair tensor);
  * token_mask: [B, N] uint8 or null; pair_mask: [B, rows, N] uint8 (the same rows as z) or null;
- * left / right: [B, rows, 128, N] bf16. `status` is a device int (e.g. the workspace start).
+ * left / right: [B, rows, 128, N] bf16. `has_bias`: non-zero iff `packed` was built with a bias on any of the
+ * four left/right linears. `status` is a device int (e.g. the workspace start).
  */
 int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
                          void* left, void* right, int B, int N, int row_begin, int rows, float eps_in,
-                         int* status, void* cuda_stream);
+                         int has_bias, int* status, void* cuda_stream);
 
 /*
  * Stage 2: per-channel contraction for output rows row_begin .. row_begin+rows-1.

@@ -30,7 +30,7 @@ SIGNATURES = {
     ),
     "b200_trimul_prologue": (
         c_int,
-        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     ),
     "b200_trimul_contract": (
         c_int,

@@ -5,17 +5,21 @@
 // Both LayerNorms are folded around the GEMMs so the tensor cores consume the raw bf16 tiles:
 //   LN(v) W^T = rstd * (v W'^T - mean * s) + d,   W' = bf16(0.5 * W * gamma), s = rowsum(W'), d = 0.5 * (W beta + bias)
 // (the 0.5 turns sigmoid(g) * p into (tanh(g/2) + 1) * (p/2)).  mean / rstd are per position and come
-// from the tiles already in shared memory; s, d are per output channel.
+// from the tiles already in shared memory; s, d are per output channel.  (Mixing a bf16 activation with
+// an fp16 weight in one kind::f16 MMA is rejected by the hardware as an illegal instruction, so the
+// folded weights are bf16 like the activations.)
 //
 // One persistent CTA per SM walks tiles of 128 consecutive columns j of one pair row (b, i).  Per tile
 //   P[pos, c] = t^T[pos, h] * Wo'[c, h]   (A = t tile as loaded from the row-plane layout: MN-major)
 //   G[pos, c] = z[pos, c'] * Wg'[c, c']   (A = z tile, K-major)
-// run on tcgen05 with TMEM lanes = positions, so each epilogue thread owns one position: its statistics
-// live in registers, it adds the residual from the z tile in shared memory and writes y in place into
-// that tile, which one thread then hands to a TMA store.
+// run on tcgen05 with TMEM lanes = positions.  An epilogue thread owns one position and 64 of the 128
+// output channels: it adds the residual from the z tile in shared memory and writes y in place into that
+// tile, which one thread then hands to a TMA store.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2-5 and 6-9 two
-// epilogue groups that take alternate tiles (each owns one shared-memory stage and one TMEM buffer).
+// Warp roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2-9 and 10-17 two
+// epilogue groups of 256 threads that take alternate tiles (each owns one shared-memory stage and one
+// TMEM buffer).  Inside a group the statistics are computed cooperatively (partial sums over channel
+// slices, merged with the pairwise mean / M2 update) while the MMAs of the tile run.
 #pragma once
 
 #include "ptx.cuh"
@@ -32,10 +36,12 @@ struct EpilogueParams {
   int* status;
 };
 
-constexpr int kEpilogueThreads = 320;
+constexpr int kEpilogueThreads = 576;
 constexpr int kEpiWBytes = 2 * 32768;
-constexpr int kEpiStageBytes = 65536;  // t tile (32 KiB) then z tile (32 KiB)
-constexpr int kEpiSmemBytes = kEpiWBytes + 2 * kEpiStageBytes + 2048 + 128 + 1024;
+constexpr int kEpiStageBytes = 65536;         // t tile (32 KiB) then z tile (32 KiB)
+constexpr int kEpiConstBytes = 2048;          // per channel pair: {sg0,sg1,dg0,dg1} and {so0,so1,do0,do1}
+constexpr int kEpiXchgBytes = 6144;           // per group: 2 x 128 input partials + 4 x 128 output partials (float2)
+constexpr int kEpiSmemBytes = kEpiWBytes + 2 * kEpiStageBytes + kEpiConstBytes + 2 * kEpiXchgBytes + 128 + 1024;
 
 __global__ void __launch_bounds__(kEpilogueThreads, 1)
 epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_z,
@@ -48,7 +54,8 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
   const uint32_t wg_base = smem_base + 32768;
   const uint32_t stage_base = smem_base + kEpiWBytes;
   const uint32_t const_base = stage_base + 2 * kEpiStageBytes;
-  const uint32_t bar_base = const_base + 2048;
+  const uint32_t xchg_base = const_base + kEpiConstBytes;
+  const uint32_t bar_base = xchg_base + 2 * kEpiXchgBytes;
   float4* const_ptr = reinterpret_cast<float4*>(smem + kEpiWBytes + 2 * kEpiStageBytes);
   // barriers: w_full, tile_full[2], tile_empty[2], acc_full[2], acc_empty[2]
   const uint32_t w_full = bar_base;
@@ -56,7 +63,8 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
   auto tile_empty = [&](int s) { return bar_base + 8u * (3 + s); };
   auto acc_full = [&](int s) { return bar_base + 8u * (5 + s); };
   auto acc_empty = [&](int s) { return bar_base + 8u * (7 + s); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kEpiWBytes + 2 * kEpiStageBytes + 2048 + 8 * 9);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kEpiWBytes + 2 * kEpiStageBytes + kEpiConstBytes +
+                                                    2 * kEpiXchgBytes + 8 * 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -68,7 +76,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       mbar_init(tile_full(s), 1);
       mbar_init(tile_empty(s), 1);
       mbar_init(acc_full(s), 1);
-      mbar_init(acc_empty(s), 4);
+      mbar_init(acc_empty(s), 8);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -77,7 +85,14 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
     prefetch_tmap(&map_y);
     prefetch_tmap(&map_w);
   }
-  if (threadIdx.x >= 64 && threadIdx.x < 192) const_ptr[threadIdx.x - 64] = p.c3[threadIdx.x - 64];
+  if (threadIdx.x >= 64 && threadIdx.x < 128) {
+    // constants regrouped per channel pair so that one 16-byte load feeds a packed fp32x2 FMA
+    const int cp = threadIdx.x - 64;
+    const float4 a = p.c3[2 * cp];
+    const float4 b = p.c3[2 * cp + 1];
+    const_ptr[2 * cp] = make_float4(a.x, b.x, a.y, b.y);      // s_gate pair, d_gate pair
+    const_ptr[2 * cp + 1] = make_float4(a.z, b.z, a.w, b.w);  // s_out pair,  d_out pair
+  }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
@@ -165,16 +180,26 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue groups
-    const int grp = (warp - 2) >> 2;  // 0: even tiles, 1: odd tiles
-    const int q = warp & 3;
-    const int pos = q * 32 + lane;    // position inside the tile == TMEM lane
+    // ------------------------------------------------------------ epilogue groups (256 threads each)
+    const int grp = (warp - 2) >> 3;         // 0: even tiles, 1: odd tiles
+    const int wg = (warp - 2) & 7;           // warp inside the group
+    const int tg = wg * 32 + lane;           // thread inside the group
+    const int half = wg >> 2;                // which 64 output channels this thread finishes
+    const int q = warp & 3;                  // TMEM lane quarter this warp may read
+    const int pos = q * 32 + lane;           // position inside the tile == TMEM lane
     const int bar_id = 2 + grp;
-    const bool store_thread = (((warp - 2) & 3) == 0) && lane == 0;
+    const bool store_thread = tg == 0;
     const uint32_t ts = stage_base + grp * kEpiStageBytes;
     const uint32_t zs = ts + 32768;
-    const uint32_t t_p = tmem_base + grp * 256 + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t xin = xchg_base + grp * kEpiXchgBytes;   // float2 [2][128]: {mean, M2} over 64 channels of z
+    const uint32_t xout = xin + 2048;                        // float2 [4][128]: {mean, M2} over 32 channels of t
+    const uint32_t t_p = tmem_base + grp * 256 + half * 64 + (static_cast<uint32_t>(q * 32) << 16);
     const uint32_t t_g = t_p + 128;
+    // output statistics: this thread covers positions 2*pp, 2*pp+1 over channels 32*hq .. 32*hq+31
+    const int pp = tg & 63;
+    const int hq = tg >> 6;
+    const uint32_t tcol = ts + ((2 * pp) >> 6) * 16384 + ((pp & 3) << 2);
+    const uint32_t tchunk = ((2 * pp) & 63) >> 3;
     int it = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       if ((it & 1) != grp) continue;
@@ -183,117 +208,132 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       const int j0 = (tile - row * p.tiles_per_row) * 128;
       {
         const bool got = mbar_wait(tile_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
-        if (!named_bar_and(bar_id, 128, got)) break;
+        if (!named_bar_and(bar_id, 256, got)) break;
       }
-      // ---- input statistics from this position's z row (kept in registers for the residual)
-      const uint32_t zrow = zs + pos * 128;
-      uint4 zr[16];
+      // ---- input partial statistics over this thread's 64 channels of its z row (kept for the residual)
+      const uint32_t zrow = zs + half * 16384 + pos * 128;
+      uint4 zr[8];
 #pragma unroll
-      for (int half = 0; half < 2; ++half)
+      for (int c = 0; c < 8; ++c) {
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(zr[c].x), "=r"(zr[c].y), "=r"(zr[c].z), "=r"(zr[c].w)
+                     : "r"(zrow + ((c ^ (pos & 7)) << 4)));
+      }
+      {
+        const float pv = bf16_lo(zr[0].x);
+        const float2 npv = make_float2(-pv, -pv);
+        float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const uint32_t addr = zrow + half * 16384 + ((c ^ (pos & 7)) << 4);
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(zr[half * 8 + c].x), "=r"(zr[half * 8 + c].y), "=r"(zr[half * 8 + c].z),
-                         "=r"(zr[half * 8 + c].w)
-                       : "r"(addr));
+          const uint32_t w4[4] = {zr[c].x, zr[c].y, zr[c].z, zr[c].w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 d = __fadd2_rn(bf16x2_to_float2(w4[t]), npv);
+            s1 = __fadd2_rn(s1, d);
+            s2 = __ffma2_rn(d, d, s2);
+          }
         }
-      float sum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        sum += bf16_lo(zr[c].x) + bf16_hi(zr[c].x);
-        sum += bf16_lo(zr[c].y) + bf16_hi(zr[c].y);
-        sum += bf16_lo(zr[c].z) + bf16_hi(zr[c].z);
-        sum += bf16_lo(zr[c].w) + bf16_hi(zr[c].w);
+        const float a1 = s1.x + s1.y, a2 = s2.x + s2.y;
+        const float mean = pv + a1 * (1.0f / 64.0f);
+        const float m2 = fmaxf(a2 - a1 * a1 * (1.0f / 64.0f), 0.f);
+        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xin + (half * 128 + pos) * 8), "f"(mean), "f"(m2) : "memory");
       }
-      const float mean_in = sum * (1.0f / 128.0f);
-      float ssq = 0.f;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const uint32_t w4[4] = {zr[c].x, zr[c].y, zr[c].z, zr[c].w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float d0 = bf16_lo(w4[t]) - mean_in;
-          const float d1 = bf16_hi(w4[t]) - mean_in;
-          ssq = fmaf(d0, d0, ssq);
-          ssq = fmaf(d1, d1, ssq);
-        }
-      }
-      const float rs_in = rsqrtf(ssq * (1.0f / 128.0f) + p.eps_in);
-      const float nmr_in = -mean_in * rs_in;
-
-      // ---- output statistics from this position's column of the t tile (128 channels)
-      float rs_out, nmr_out;
+      // ---- output partial statistics: two adjacent positions, 32 channels of the t tile
       {
-        const uint32_t tcol = ts + (pos >> 6) * 16384 + ((pos & 7) << 1);
-        const uint32_t chunk = (pos & 63) >> 3;
-        float pivot = 0.f, s1 = 0.f, s2 = 0.f;
-#pragma unroll 16
-        for (int h = 0; h < 128; ++h) {
-          uint16_t raw;
-          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(tcol + h * 128 + ((chunk ^ (h & 7)) << 4)));
-          const float x = __uint_as_float(static_cast<uint32_t>(raw) << 16);
-          if (h == 0) pivot = x;
-          const float d = x - pivot;
-          s1 += d;
-          s2 = fmaf(d, d, s2);
+        float2 pv = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
+#pragma unroll 8
+        for (int hh = 0; hh < 32; ++hh) {
+          const int h = hq * 32 + hh;
+          uint32_t raw;
+          asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw) : "r"(tcol + h * 128 + ((tchunk ^ (h & 7)) << 4)));
+          const float2 x = bf16x2_to_float2(raw);
+          if (hh == 0) pv = x;
+          const float2 d = __fadd2_rn(x, make_float2(-pv.x, -pv.y));
+          s1 = __fadd2_rn(s1, d);
+          s2 = __ffma2_rn(d, d, s2);
         }
-        const float m1 = s1 * (1.0f / 128.0f);
-        const float var = fmaxf(s2 * (1.0f / 128.0f) - m1 * m1, 0.f);
-        rs_out = rsqrtf(var + p.eps_out);
-        nmr_out = -(pivot + m1) * rs_out;
+        const float mean0 = pv.x + s1.x * (1.0f / 32.0f), mean1 = pv.y + s1.y * (1.0f / 32.0f);
+        const float m20 = fmaxf(s2.x - s1.x * s1.x * (1.0f / 32.0f), 0.f);
+        const float m21 = fmaxf(s2.y - s1.y * s1.y * (1.0f / 32.0f), 0.f);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(xout + (hq * 128 + 2 * pp) * 8), "f"(mean0),
+                     "f"(m20), "f"(mean1), "f"(m21)
+                     : "memory");
       }
+      named_bar_sync(bar_id, 256);
+      // ---- merge the partials of this thread's position (equal-sized groups: mean of means, M2 + n * spread)
+      float rs_in, nmr_in, rs_out, nmr_out;
+      {
+        float ma, qa, mb, qb;
+        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(ma), "=f"(qa) : "r"(xin + pos * 8));
+        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(mb), "=f"(qb) : "r"(xin + (128 + pos) * 8));
+        const float mean = 0.5f * (ma + mb);
+        const float dlt = ma - mb;
+        const float m2 = qa + qb + dlt * dlt * 32.0f;  // n_a n_b / (n_a + n_b) = 32
+        rs_in = rsqrtf(m2 * (1.0f / 128.0f) + p.eps_in);
+        nmr_in = -mean * rs_in;
+      }
+      {
+        float m[4], qv[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(m[k]), "=f"(qv[k]) : "r"(xout + (k * 128 + pos) * 8));
+        const float mean = 0.25f * (m[0] + m[1] + m[2] + m[3]);
+        float m2 = qv[0] + qv[1] + qv[2] + qv[3];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m2 = fmaf(32.0f * (m[k] - mean), m[k] - mean, m2);
+        rs_out = rsqrtf(m2 * (1.0f / 128.0f) + p.eps_out);
+        nmr_out = -mean * rs_out;
+      }
+      const float2 rs_in2 = make_float2(rs_in, rs_in), nmr_in2 = make_float2(nmr_in, nmr_in);
+      const float2 rs_out2 = make_float2(rs_out, rs_out), nmr_out2 = make_float2(nmr_out, nmr_out);
 
       {
         const bool got = mbar_wait(acc_full(grp), ph, abort_flag, p.status, kDevTimeoutEpilogue);
-        if (!named_bar_and(bar_id, 128, got)) break;
+        if (!named_bar_and(bar_id, 256, got)) break;
       }
       tc_fence_after();
 #pragma unroll
-      for (int c32 = 0; c32 < 4; ++c32) {  // fully unrolled so that zr[] stays in registers
-        uint32_t vp[32], vg[32];
-        tmem_ld32(t_p + c32 * 32, vp);
-        tmem_ld32(t_g + c32 * 32, vg);
+      for (int c16 = 0; c16 < 4; ++c16) {  // fully unrolled so that zr[] stays in registers
+        uint32_t vp[16], vg[16];
+        tmem_ld16(t_p + c16 * 16, vp);
+        tmem_ld16(t_g + c16 * 16, vg);
         tmem_ld_wait();
-        if (c32 == 3) {
+        if (c16 == 3) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty(grp));
         }
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          const int cc = c32 * 4 + c8;  // 16-byte chunk of the row: channels 8*cc .. 8*cc+7
-          float r[8];
+        for (int c8 = 0; c8 < 2; ++c8) {
+          const int cc = c16 * 2 + c8;  // 16-byte chunk inside this thread's 64 channels
+          uint32_t o[4];
+          const uint32_t zz[4] = {zr[cc].x, zr[cc].y, zr[cc].z, zr[cc].w};
 #pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            float sg, dg, so, dout;
+          for (int t = 0; t < 4; ++t) {
+            const int pair = half * 32 + cc * 4 + t;  // channel pair index 0..63
+            float4 cg, co;
             asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                         : "=f"(sg), "=f"(dg), "=f"(so), "=f"(dout)
-                         : "r"(const_base + (cc * 8 + t) * 16));
-            const float g2 = fmaf(__uint_as_float(vg[c8 * 8 + t]), rs_in, fmaf(nmr_in, sg, dg));
-            const float hp = fmaf(__uint_as_float(vp[c8 * 8 + t]), rs_out, fmaf(nmr_out, so, dout));
-            const float th = tanh_approx(g2);
-            r[t] = fmaf(th, hp, hp);
+                         : "=f"(cg.x), "=f"(cg.y), "=f"(cg.z), "=f"(cg.w)
+                         : "r"(const_base + pair * 32));
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(co.x), "=f"(co.y), "=f"(co.z), "=f"(co.w)
+                         : "r"(const_base + pair * 32 + 16));
+            const float2 accg = make_float2(__uint_as_float(vg[c8 * 8 + 2 * t]), __uint_as_float(vg[c8 * 8 + 2 * t + 1]));
+            const float2 accp = make_float2(__uint_as_float(vp[c8 * 8 + 2 * t]), __uint_as_float(vp[c8 * 8 + 2 * t + 1]));
+            const float2 g2 = __ffma2_rn(accg, rs_in2, __ffma2_rn(nmr_in2, make_float2(cg.x, cg.y), make_float2(cg.z, cg.w)));
+            const float2 hp = __ffma2_rn(accp, rs_out2, __ffma2_rn(nmr_out2, make_float2(co.x, co.y), make_float2(co.z, co.w)));
+            const float2 th = make_float2(tanh_approx(g2.x), tanh_approx(g2.y));
+            float2 u = __ffma2_rn(th, hp, hp);
+            if (p.residual) u = __fadd2_rn(u, bf16x2_to_float2(zz[t]));
+            o[t] = pack_bf16x2(u);
           }
-          if (p.residual) {
-            const uint4 zz = zr[cc];
-            r[0] += bf16_lo(zz.x);
-            r[1] += bf16_hi(zz.x);
-            r[2] += bf16_lo(zz.y);
-            r[3] += bf16_hi(zz.y);
-            r[4] += bf16_lo(zz.z);
-            r[5] += bf16_hi(zz.z);
-            r[6] += bf16_lo(zz.w);
-            r[7] += bf16_hi(zz.w);
-          }
-          const uint32_t addr = zrow + (cc >> 3) * 16384 + (((cc & 7) ^ (pos & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(r[0], r[1])),
-                       "r"(pack_bf16x2(r[2], r[3])), "r"(pack_bf16x2(r[4], r[5])), "r"(pack_bf16x2(r[6], r[7]))
+          const uint32_t addr = zrow + ((cc ^ (pos & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
                        : "memory");
         }
       }
       fence_proxy_async_smem();
-      named_bar_sync(bar_id, 128);
+      named_bar_sync(bar_id, 256);
       if (store_thread) {
         tma_store_3d(&map_y, zs, 0, j0, row);
         tma_store_3d(&map_y, zs + 16384, 64, j0, row);

@@ -1,21 +1,32 @@
 // Fused prologue: input LayerNorm + left/right gated projections + sigmoid gate + pair mask.
 //
-//   x_hat = (z - mean) * rstd                          (affine folded into the packed weights)
-//   left  = sigmoid(x_hat Wlg'^T + dlg) * (x_hat Wl'^T + dl) * valid(i,k)
-//   right = likewise with Wrg', Wr'
+//   x_hat = LayerNorm_in(z)  (fp32 statistics, affine applied, rounded once to fp16 for the tensor cores:
+//                             |x_hat| <= sqrt(127) |gamma| + |beta| fits easily and keeps three more
+//                             mantissa bits than bf16; the packed weights are fp16 too)
+//   left  = sigmoid(x_hat Wlg^T + blg) * (x_hat Wl^T + bl) * valid(i,k)      (biases optional)
+//   right = likewise with Wrg, Wr
 //
-// Packed weights carry 0.5 * W * gamma (bf16) and d = 0.5 * (W beta + bias), so that
+// Packed weights are fp16(0.5 * W) and d = 0.5 * bias, so that
 // sigmoid(g) * p = (tanh(g/2) + 1) * (p/2) costs one MUFU op and one FMA per output.
 //
 // One persistent CTA per SM walks tiles of 128 consecutive columns j of one pair row (b, i).
-// Per tile the four GEMMs are issued as D^T[h, pos] = W'[h, c] * x_hat^T[c, pos] on tcgen05, so TMEM
+// Per tile the four GEMMs are issued as D^T[h, pos] = W[h, c] * x_hat^T[c, pos] on tcgen05, so TMEM
 // lanes are channels and columns are positions: each epilogue thread owns one channel and writes
 // runs of consecutive positions, which is exactly the row-plane layout [B, rows, H, N] of the outputs.
 //
-// Warp roles (448 threads): warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2-5 LayerNorm
-// (one thread per position, normalises the tile in place in shared memory and builds the mask),
-// warps 6-9 epilogue for `left`, warps 10-13 epilogue for `right`.  The left and right accumulator
-// pairs are separate TMEM buffers, so the MMAs of one overlap the epilogue of the other.
+// Outputs leave through a swizzled shared-memory staging tile and TMA stores (full 128-byte rows);
+// direct per-thread 16-byte stores to 128 different channel rows ran the store path at a third of this.
+//
+// Warp roles (832 threads):
+//   warp 0        TMA producer (z tiles, weights once)
+//   warp 1        MMA issuer / TMEM owner
+//   warps 2-9     LayerNorm: 8 threads per position (16 channels each, their gamma/beta in registers),
+//                 32 positions per pass, 4 passes per tile; normalises the tile in place in shared memory.
+//                 The first four of these warps also build the tile's validity bitmap.
+//   warps 10-17   epilogue for `left`  (64 positions at a time: TMEM -> tanh gate -> mask -> staging -> TMA store)
+//   warps 18-25   epilogue for `right`
+// The left and right accumulator pairs are separate TMEM buffers, so the MMAs of one overlap the
+// epilogue of the other.
 #pragma once
 
 #include "ptx.cuh"
@@ -31,23 +42,29 @@ struct PrologueParams {
   int num_tiles;       // B * rows * tiles_per_row
   const uint8_t* token_mask;  // [B, N] non-zero = valid, or null
   const uint8_t* pair_mask;   // [B, rows, N] non-zero = valid, or null
-  const float* d1;            // [4][128] additive constants: left, left gate, right, right gate
+  const float* d1;            // [4][128] additive constants (0.5 * bias): left, left gate, right, right gate
+  const float* ln_w;          // [128] LayerNorm gamma
+  const float* ln_b;          // [128] LayerNorm beta
   __nv_bfloat16* left_out;    // [B, rows, 128, N]
   __nv_bfloat16* right_out;   // [B, rows, 128, N]
   float eps;
   int* status;
 };
 
-constexpr int kPrologueThreads = 448;
-constexpr int kProStages = 3;
+constexpr int kPrologueThreads = 832;
+constexpr int kProStages = 2;
 constexpr int kProRing = 5;            // mask ring entries (>= stages + 2)
+constexpr int kProStageOutBytes = 2 * 16384;  // one [128 channels][64 positions] staging tile per output
 constexpr int kProRingBytes = 272;     // 64 pair-mask words + 4 ballots
 constexpr int kProWBytes = 4 * 32768;  // four 128x128 bf16 matrices
 constexpr int kProZBytes = 32768;      // 128 positions x 128 channels bf16
-constexpr int kProSmemBytes = kProWBytes + kProStages * kProZBytes + kProRing * kProRingBytes + 128 + 1024;
+constexpr int kProSmemBytes =
+    kProWBytes + kProStages * kProZBytes + kProStageOutBytes + kProRing * kProRingBytes + 128 + 1024;
 
+template <bool HAS_BIAS>
 __global__ void __launch_bounds__(kPrologueThreads, 1)
 prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_w,
+                const __grid_constant__ CUtensorMap map_l, const __grid_constant__ CUtensorMap map_r,
                 const PrologueParams p) {
   constexpr int S = kProStages;
   extern __shared__ uint8_t smem_raw[];
@@ -55,9 +72,10 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t w_base = smem_base;
   const uint32_t z_base = smem_base + kProWBytes;
-  const uint32_t ring_base = z_base + S * kProZBytes;
+  const uint32_t stage_out_base = z_base + S * kProZBytes;
+  const uint32_t ring_base = stage_out_base + kProStageOutBytes;
   const uint32_t bar_base = ring_base + kProRing * kProRingBytes;
-  uint32_t* ring_ptr = reinterpret_cast<uint32_t*>(smem + kProWBytes + S * kProZBytes);
+  uint32_t* ring_ptr = reinterpret_cast<uint32_t*>(smem + kProWBytes + S * kProZBytes + kProStageOutBytes);
   // barriers: w_full, z_full[S], xn_ready[S], z_empty[S], acc_full[2], acc_empty[2]
   const uint32_t w_full = bar_base;
   auto z_full = [&](int s) { return bar_base + 8u * (1 + s); };
@@ -66,7 +84,8 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
   auto acc_full = [&](int a) { return bar_base + 8u * (1 + 3 * S + a); };
   auto acc_empty = [&](int a) { return bar_base + 8u * (1 + 3 * S + 2 + a); };
   uint32_t* tmem_slot =
-      reinterpret_cast<uint32_t*>(smem + kProWBytes + S * kProZBytes + kProRing * kProRingBytes + 8 * (1 + 3 * S + 4));
+      reinterpret_cast<uint32_t*>(smem + kProWBytes + S * kProZBytes + kProStageOutBytes + kProRing * kProRingBytes +
+                                  8 * (1 + 3 * S + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -76,17 +95,19 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
     mbar_init(w_full, 1);
     for (int s = 0; s < S; ++s) {
       mbar_init(z_full(s), 1);
-      mbar_init(xn_ready(s), 4);
+      mbar_init(xn_ready(s), 8);
       mbar_init(z_empty(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full(a), 1);
-      mbar_init(acc_empty(a), 4);
+      mbar_init(acc_empty(a), 8);
     }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&map_z);
     prefetch_tmap(&map_w);
+    prefetch_tmap(&map_l);
+    prefetch_tmap(&map_r);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), 512);
@@ -150,7 +171,7 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(128, 128, false, false);
+      constexpr uint32_t idesc = umma_idesc(128, 128, false, false, kFmtF16, kFmtF16);
       bool ok = mbar_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma);
       int s = 0;
       uint32_t ph = 0;
@@ -186,85 +207,94 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
         }
       }
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------ LayerNorm + mask (one thread per position)
-    const int pos = (warp - 2) * 32 + lane;
+  } else if (warp < 10) {
+    // ------------------------------------------------------------ LayerNorm (+ validity bitmap)
+    const int ts = threadIdx.x - 64;  // 0 .. 255
+    const int sub = ts & 7;           // 16-byte chunk: channels 8*sub .. 8*sub+7 of each 64-channel half
+    const int slot = ts >> 3;         // position slot inside a pass
+    float2 g[8], b[8];                // gamma / beta of this thread's 16 channels, as pairs
+#pragma unroll
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int c = half * 64 + sub * 8 + 2 * t;
+        g[half * 4 + t] = make_float2(p.ln_w[c], p.ln_w[c + 1]);
+        b[half * 4 + t] = make_float2(p.ln_b[c], p.ln_b[c + 1]);
+      }
     int s = 0;
     uint32_t ph = 0;
     int e = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       const int row = tile / p.tiles_per_row;
       const int j0 = (tile - row * p.tiles_per_row) * 128;
-      const int bb = row / p.rows;
-      const int il = row - bb * p.rows;
-      const int j = j0 + pos;
-      bool valid = j < p.n;
-      if (valid && p.token_mask != nullptr) {
-        const uint8_t* tm = p.token_mask + static_cast<size_t>(bb) * p.n;
-        valid = (tm[p.row_offset + il] != 0) && (tm[j] != 0);
+      bool valid = false;
+      if (ts < 128) {  // these four warps own one position each for the bitmap
+        const int bb = row / p.rows;
+        const int il = row - bb * p.rows;
+        const int j = j0 + ts;
+        const bool inside = j < p.n;
+        const int jc = inside ? j : 0;  // clamped so that the three loads below can be issued together
+        uint32_t mi = 1u, mj = 1u, mp = 1u;
+        if (p.token_mask != nullptr) {
+          const uint8_t* tm = p.token_mask + static_cast<size_t>(bb) * p.n;
+          mi = tm[p.row_offset + il];
+          mj = tm[jc];
+        }
+        if (p.pair_mask != nullptr) mp = p.pair_mask[static_cast<size_t>(row) * p.n + jc];
+        valid = inside && mi != 0u && mj != 0u && mp != 0u;
       }
-      if (valid && p.pair_mask != nullptr) valid = p.pair_mask[static_cast<size_t>(row) * p.n + j] != 0;
 
       const bool got = mbar_wait(z_full(s), ph, abort_flag, p.status, kDevTimeoutStats);
-      if (!named_bar_and(2, 128, got)) break;
+      if (!named_bar_and(2, 256, got)) break;
 
-      const uint32_t rowaddr = z_base + s * kProZBytes + pos * 128;
-      uint4 v[16];
+      const uint32_t zs = z_base + s * kProZBytes;
+#pragma unroll 2
+      for (int pass = 0; pass < 4; ++pass) {
+        const int pos = pass * 32 + slot;
+        const uint32_t a0 = zs + pos * 128 + ((sub ^ (pos & 7)) << 4);
+        const uint32_t a1 = a0 + 16384;
+        uint32_t w[8];
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(a0));
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(a1));
+        float2 v[8];
 #pragma unroll
-      for (int half = 0; half < 2; ++half)
+        for (int t = 0; t < 8; ++t) v[t] = bf16x2_to_float2(w[t]);
+        float2 acc = v[0];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t addr = rowaddr + half * 16384 + ((c ^ (pos & 7)) << 4);
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(v[half * 8 + c].x), "=r"(v[half * 8 + c].y), "=r"(v[half * 8 + c].z),
-                         "=r"(v[half * 8 + c].w)
-                       : "r"(addr));
+        for (int t = 1; t < 8; ++t) acc = __fadd2_rn(acc, v[t]);
+        float sum = acc.x + acc.y;
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+        const float mean = sum * (1.0f / 128.0f);
+        const float2 nmean = make_float2(-mean, -mean);
+        float2 q2 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          v[t] = __fadd2_rn(v[t], nmean);
+          q2 = __ffma2_rn(v[t], v[t], q2);
         }
-      float sum = 0.f;
+        float ssq = q2.x + q2.y;
+        ssq += __shfl_xor_sync(0xFFFFFFFFu, ssq, 1);
+        ssq += __shfl_xor_sync(0xFFFFFFFFu, ssq, 2);
+        ssq += __shfl_xor_sync(0xFFFFFFFFu, ssq, 4);
+        const float rstd = rsqrtf(ssq * (1.0f / 128.0f) + p.eps);
+        const float2 rstd2 = make_float2(rstd, rstd);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        sum += bf16_lo(v[c].x) + bf16_hi(v[c].x);
-        sum += bf16_lo(v[c].y) + bf16_hi(v[c].y);
-        sum += bf16_lo(v[c].z) + bf16_hi(v[c].z);
-        sum += bf16_lo(v[c].w) + bf16_hi(v[c].w);
+        for (int t = 0; t < 8; ++t) w[t] = pack_f16x2(__ffma2_rn(__fmul2_rn(v[t], rstd2), g[t], b[t]));
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a0), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a1), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
       }
-      const float mean = sum * (1.0f / 128.0f);
-      float ssq = 0.f;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const uint32_t w4[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float d0 = bf16_lo(w4[t]) - mean;
-          const float d1 = bf16_hi(w4[t]) - mean;
-          ssq = fmaf(d0, d0, ssq);
-          ssq = fmaf(d1, d1, ssq);
+      if (ts < 128) {
+        // mask ring entry: 64 pair-mask words (one per two positions) and the four warp ballots
+        const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, valid);
+        uint32_t* ring = ring_ptr + e * (kProRingBytes / 4);
+        if (lane < 16) {
+          const uint32_t two = (ballot >> (2 * lane)) & 3u;
+          ring[(warp - 2) * 16 + lane] = ((two & 1u) ? 0x0000FFFFu : 0u) | ((two & 2u) ? 0xFFFF0000u : 0u);
         }
+        if (lane == 0) ring[64 + (warp - 2)] = ballot;
       }
-      const float rstd = rsqrtf(ssq * (1.0f / 128.0f) + p.eps);
-      const float nmr = -mean * rstd;
-#pragma unroll
-      for (int half = 0; half < 2; ++half)
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 in = v[half * 8 + c];
-          uint4 o;
-          o.x = pack_bf16x2(fmaf(bf16_lo(in.x), rstd, nmr), fmaf(bf16_hi(in.x), rstd, nmr));
-          o.y = pack_bf16x2(fmaf(bf16_lo(in.y), rstd, nmr), fmaf(bf16_hi(in.y), rstd, nmr));
-          o.z = pack_bf16x2(fmaf(bf16_lo(in.z), rstd, nmr), fmaf(bf16_hi(in.z), rstd, nmr));
-          o.w = pack_bf16x2(fmaf(bf16_lo(in.w), rstd, nmr), fmaf(bf16_hi(in.w), rstd, nmr));
-          const uint32_t addr = rowaddr + half * 16384 + ((c ^ (pos & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
-                       : "memory");
-        }
-      // mask ring entry: 64 pair-mask words (one per two positions) and the four warp ballots
-      const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, valid);
-      uint32_t* ring = ring_ptr + e * (kProRingBytes / 4);
-      if (lane < 16) {
-        const uint32_t two = (ballot >> (2 * lane)) & 3u;
-        ring[(warp - 2) * 16 + lane] = ((two & 1u) ? 0x0000FFFFu : 0u) | ((two & 2u) ? 0xFFFF0000u : 0u);
-      }
-      if (lane == 0) ring[64 + (warp - 2)] = ballot;
       fence_proxy_async_smem();  // x_hat was written through the generic proxy; the MMA reads it through the async one
       __syncwarp();
       if (lane == 0) mbar_arrive(xn_ready(s));
@@ -275,14 +305,26 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
       if (++e == kProRing) e = 0;
     }
   } else {
-    // ------------------------------------------------------------ epilogue: warps 6-9 left, 10-13 right
-    const int set = (warp - 6) >> 2;
-    const int q = warp & 3;
+    // ------------------------------------------------------------ epilogue: warps 10-17 left, 18-25 right
+    // The 8 warps of a set work on 64 positions at a time: warp pair (same TMEM lane quarter) splits them
+    // 32 + 32. Results go to a 16 KiB swizzled staging tile [128 channels][64 positions] that one thread
+    // hands to a TMA store, so global memory sees full 128-byte rows.
+    const int ew = warp - 10;
+    const int set = ew >> 3;
+    const int sub = (ew >> 2) & 1;  // which 32 of the 64 positions in flight
+    const int q = warp & 3;         // TMEM lane quarter this warp may read
     const int h = q * 32 + lane;
-    const float dp = p.d1[(set * 2 + 0) * 128 + h];
-    const float dg = p.d1[(set * 2 + 1) * 128 + h];
-    __nv_bfloat16* out_base = set == 0 ? p.left_out : p.right_out;
-    const uint32_t t_p = tmem_base + set * 256 + (static_cast<uint32_t>(q * 32) << 16);
+    const int bar_id = 3 + set;
+    const bool store_thread = ((ew & 7) == 0) && lane == 0;
+    const CUtensorMap* map_o = set == 0 ? &map_l : &map_r;
+    float dp = 0.f, dg = 0.f;
+    if constexpr (HAS_BIAS) {
+      dp = p.d1[(set * 2 + 0) * 128 + h];
+      dg = p.d1[(set * 2 + 1) * 128 + h];
+    }
+    const uint32_t stg = stage_out_base + set * 16384;
+    const uint32_t stg_row = stg + h * 128;
+    const uint32_t t_p = tmem_base + set * 256 + sub * 32 + (static_cast<uint32_t>(q * 32) << 16);
     const uint32_t t_g = t_p + 128;
     int it = 0;
     int e = 0;
@@ -290,59 +332,80 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
       const int row = tile / p.tiles_per_row;
       const int j0 = (tile - row * p.tiles_per_row) * 128;
       const bool got = mbar_wait(acc_full(set), it & 1, abort_flag, p.status, kDevTimeoutEpilogue);
-      if (!named_bar_and(3 + set, 128, got)) break;
+      if (!named_bar_and(bar_id, 256, got)) break;
       tc_fence_after();
       const uint32_t ring = ring_base + e * kProRingBytes;
-      uint32_t b0, b1, b2, b3;
-      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(ring + 256));
-      const bool all_valid = (b0 & b1 & b2 & b3) == 0xFFFFFFFFu;
-      const bool none_valid = (b0 | b1 | b2 | b3) == 0u;
-      __nv_bfloat16* dst = out_base + (static_cast<size_t>(row) * 128 + h) * p.n + j0;
+      uint32_t bal[4];
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(bal[0]), "=r"(bal[1]), "=r"(bal[2]), "=r"(bal[3])
+                   : "r"(ring + 256));
 #pragma unroll 1
-      for (int c32 = 0; c32 < 4; ++c32) {
-        uint32_t vp[32], vg[32];
-        if (!none_valid) {
-          tmem_ld32(t_p + c32 * 32, vp);
-          tmem_ld32(t_g + c32 * 32, vg);
-          tmem_ld_wait();
+      for (int half = 0; half < 2; ++half) {
+        // validity of this thread's 32 positions (selects, so that bal[] stays in registers)
+        const uint32_t bits = half == 0 ? (sub == 0 ? bal[0] : bal[1]) : (sub == 0 ? bal[2] : bal[3]);
+        uint32_t o[16];
+        if (bits != 0u) {
+#pragma unroll
+          for (int c16 = 0; c16 < 2; ++c16) {
+            uint32_t vp[16], vg[16];
+            tmem_ld16(t_p + half * 64 + c16 * 16, vp);
+            tmem_ld16(t_g + half * 64 + c16 * 16, vg);
+            tmem_ld_wait();
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              float2 hp = make_float2(__uint_as_float(vp[2 * t]), __uint_as_float(vp[2 * t + 1]));
+              float2 gg = make_float2(__uint_as_float(vg[2 * t]), __uint_as_float(vg[2 * t + 1]));
+              if constexpr (HAS_BIAS) {
+                hp = __fadd2_rn(hp, make_float2(dp, dp));
+                gg = __fadd2_rn(gg, make_float2(dg, dg));
+              }
+              const float2 th = make_float2(tanh_approx(gg.x), tanh_approx(gg.y));
+              o[c16 * 8 + t] = pack_bf16x2(__ffma2_rn(th, hp, hp));
+            }
+          }
+          if (bits != 0xFFFFFFFFu) {
+            const uint32_t ma = ring + (half * 32 + sub * 16) * 4;
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              uint32_t m0, m1, m2, m3;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(m0), "=r"(m1), "=r"(m2), "=r"(m3) : "r"(ma + v4 * 16));
+              o[v4 * 4 + 0] &= m0;
+              o[v4 * 4 + 1] &= m1;
+              o[v4 * 4 + 2] &= m2;
+              o[v4 * 4 + 3] &= m3;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) o[t] = 0u;
         }
-        if (c32 == 3) {
+        if (half == 1) {
+          // every TMEM read of this tile is done: hand the accumulators back to the MMA issuer
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty(set));
         }
+        // the staging tile may be overwritten once the previous TMA store has read it
+        if (store_thread) bulk_wait_read<0>();
+        named_bar_sync(bar_id, 256);
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          const int col = c32 * 32 + c8 * 8;
-          uint4 o = make_uint4(0u, 0u, 0u, 0u);
-          if (!none_valid) {
-            float r[8];
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-              const float hp = __uint_as_float(vp[c8 * 8 + t]) + dp;
-              const float th = tanh_approx(__uint_as_float(vg[c8 * 8 + t]) + dg);
-              r[t] = fmaf(th, hp, hp);
-            }
-            o.x = pack_bf16x2(r[0], r[1]);
-            o.y = pack_bf16x2(r[2], r[3]);
-            o.z = pack_bf16x2(r[4], r[5]);
-            o.w = pack_bf16x2(r[6], r[7]);
-            if (!all_valid) {
-              uint32_t m0, m1, m2, m3;
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(m0), "=r"(m1), "=r"(m2), "=r"(m3)
-                           : "r"(ring + (col >> 1) * 4));
-              o.x &= m0;
-              o.y &= m1;
-              o.z &= m2;
-              o.w &= m3;
-            }
-          }
-          if (j0 + col < p.n) *reinterpret_cast<uint4*>(dst + col) = o;
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t addr = stg_row + (((sub * 4 + c) ^ (h & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[4 * c]), "r"(o[4 * c + 1]),
+                       "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(bar_id, 256);
+        if (store_thread) {
+          const int col0 = j0 + half * 64;
+          if (col0 < p.n) tma_store_3d(map_o, stg, col0, 0, row);
+          bulk_commit();
         }
       }
       if (++e == kProRing) e = 0;
     }
+    if (store_thread) bulk_wait<0>();
   }
 
   tc_fence_before();

@@ -17,7 +17,8 @@ constexpr size_t kStatusBytes = 1024;
 constexpr size_t kPackedMatrixBytes = 6 * 32768;
 constexpr size_t kPackedD1Off = kPackedMatrixBytes;            // float[4][128]
 constexpr size_t kPackedC3Off = kPackedMatrixBytes + 2048;     // float4[128]
-constexpr size_t kPackedBytes = kPackedMatrixBytes + 4096;     // 200704, a multiple of 1024
+constexpr size_t kPackedLnOff = kPackedMatrixBytes + 4096;     // float[2][128]: input LayerNorm gamma, beta
+constexpr size_t kPackedBytes = kPackedMatrixBytes + 5120;     // 201728, a multiple of 1024
 
 static thread_local int tl_last_cuda_error = 0;
 
@@ -32,7 +33,8 @@ static thread_local int tl_last_cuda_error = 0;
 
 // ---------------------------------------------------------------------------------------------
 // Weight packing: one warp per matrix row.
-//   matrices 0..3 (left, left gate, right, right gate): W' = bf16(0.5 W gamma_in), d = 0.5 (W beta_in + bias)
+//   matrices 0..3 (left, left gate, right, right gate): W' = fp16(0.5 W), d = 0.5 bias
+//     (the prologue applies the input LayerNorm affine itself; gamma_in / beta_in are copied alongside)
 //   matrix 4 (out):  W' = bf16(0.5 W gamma_out), s = rowsum(W'), d = 0.5 (W beta_out + bias)
 //   matrix 5 (gate): W' = bf16(0.5 W gamma_in),  s = rowsum(W'), d = 0.5 (W beta_in + bias)
 struct PackArgs {
@@ -65,16 +67,29 @@ __global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* pa
   const float gg[4] = {g.x, g.y, g.z, g.w};
   const float bb[4] = {b.x, b.y, b.z, b.w};
   float s = 0.f, d = 0.f;
-  __nv_bfloat16 o[4];
+  uint16_t o[4];
+  // The prologue's matrices meet an fp16 x_hat, so they are fp16 (three more mantissa bits than bf16;
+  // |0.5 W| is far from 65504). The epilogue's matrices meet raw bf16 activations and both MMA operands
+  // must share one 16-bit format, so they are bf16 and carry the folded LayerNorm.
+  const bool fold = m >= 4;
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
-    o[t] = __float2bfloat16_rn(0.5f * w[t] * gg[t]);
-    s += __bfloat162float(o[t]);
-    d = fmaf(w[t], bb[t], d);
+    if (fold) {
+      const __nv_bfloat16 v = __float2bfloat16_rn(0.5f * w[t] * gg[t]);
+      o[t] = __bfloat16_as_ushort(v);
+      s += __bfloat162float(v);
+      d = fmaf(w[t], bb[t], d);
+    } else {
+      o[t] = __half_as_ushort(__float2half_rn(0.5f * w[t]));
+    }
+  }
+  if (gw == 0) {
+    reinterpret_cast<float4*>(packed + kPackedLnOff)[lane] = g;
+    reinterpret_cast<float4*>(packed + kPackedLnOff + 512)[lane] = b;
   }
   uint2 ov;
-  ov.x = static_cast<uint32_t>(__bfloat16_as_ushort(o[0])) | (static_cast<uint32_t>(__bfloat16_as_ushort(o[1])) << 16);
-  ov.y = static_cast<uint32_t>(__bfloat16_as_ushort(o[2])) | (static_cast<uint32_t>(__bfloat16_as_ushort(o[3])) << 16);
+  ov.x = static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 16);
+  ov.y = static_cast<uint32_t>(o[2]) | (static_cast<uint32_t>(o[3]) << 16);
   reinterpret_cast<uint2*>(packed + static_cast<size_t>(m) * 32768)[row * 32 + lane] = ov;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
@@ -83,7 +98,7 @@ __global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* pa
   }
   if (lane == 0) {
     const float bias = a.bias[m] != nullptr ? a.bias[m][row] : 0.f;
-    d = 0.5f * (d + bias);
+    d = 0.5f * (d + bias);  // d is the folded W beta term for matrices 4 and 5, zero for the others
     if (m < 4) {
       reinterpret_cast<float*>(packed + kPackedD1Off)[m * 128 + row] = d;
     } else {
@@ -320,8 +335,8 @@ int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const 
 }
 
 int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
-                         void* left, void* right, int B, int N, int row_begin, int rows, float eps_in, int* status,
-                         void* cuda_stream) {
+                         void* left, void* right, int B, int N, int row_begin, int rows, float eps_in, int has_bias,
+                         int* status, void* cuda_stream) {
   if (!z || !packed || !left || !right || !status) return B200_TRIMUL_E_NULL;
   int rc = check_bn(B, N);
   if (rc != B200_TRIMUL_OK) return rc;
@@ -331,12 +346,22 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
   rc = device_info(&info);
   if (rc != B200_TRIMUL_OK) return rc;
 
-  CUtensorMap map_z, map_w;
+  CUtensorMap map_z, map_w, map_l, map_r;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(kC), static_cast<uint64_t>(N), static_cast<uint64_t>(B) * rows};
     const uint64_t strides[2] = {kC * 2ull, static_cast<uint64_t>(N) * kC * 2ull};
     const uint32_t box[3] = {64, 128, 1};
     rc = make_map(&map_z, z, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    // outputs, row-plane: [B * rows][128 channels][N columns]
+    const uint64_t dims[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(kC), static_cast<uint64_t>(B) * rows};
+    const uint64_t strides[2] = {static_cast<uint64_t>(N) * 2ull, static_cast<uint64_t>(N) * kC * 2ull};
+    const uint32_t box[3] = {64, 128, 1};
+    rc = make_map(&map_l, left, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = make_map(&map_r, right, 3, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
   }
   {
@@ -356,14 +381,23 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
   p.token_mask = token_mask;
   p.pair_mask = pair_mask;
   p.d1 = reinterpret_cast<const float*>(static_cast<const uint8_t*>(packed) + kPackedD1Off);
+  p.ln_w = reinterpret_cast<const float*>(static_cast<const uint8_t*>(packed) + kPackedLnOff);
+  p.ln_b = p.ln_w + 128;
   p.left_out = static_cast<__nv_bfloat16*>(left);
   p.right_out = static_cast<__nv_bfloat16*>(right);
   p.eps = eps_in;
   p.status = status;
-  rc = set_smem(prologue_kernel, kProSmemBytes);
-  if (rc != B200_TRIMUL_OK) return rc;
   const int grid = p.num_tiles < info.sms ? p.num_tiles : info.sms;
-  prologue_kernel<<<grid, kPrologueThreads, kProSmemBytes, static_cast<cudaStream_t>(cuda_stream)>>>(map_z, map_w, p);
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (has_bias) {
+    rc = set_smem(prologue_kernel<true>, kProSmemBytes);
+    if (rc != B200_TRIMUL_OK) return rc;
+    prologue_kernel<true><<<grid, kPrologueThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, p);
+  } else {
+    rc = set_smem(prologue_kernel<false>, kProSmemBytes);
+    if (rc != B200_TRIMUL_OK) return rc;
+    prologue_kernel<false><<<grid, kPrologueThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, p);
+  }
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
 }
@@ -510,7 +544,11 @@ int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_ga
   rc = b200_trimul_pack_weights(w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out, weight_dtype, ln_in_w,
                                 ln_in_b, ln_out_w, ln_out_b, bias_opt, packed, cuda_stream);
   if (rc != B200_TRIMUL_OK) return rc;
-  rc = b200_trimul_prologue(z, packed, token_mask, pair_mask, left, right, B, N, 0, N, eps_in, status, cuda_stream);
+  int has_bias = 0;
+  if (bias_opt != nullptr)
+    for (int i = 0; i < 4; ++i) has_bias |= bias_opt[i] != nullptr;
+  rc = b200_trimul_prologue(z, packed, token_mask, pair_mask, left, right, B, N, 0, N, eps_in, has_bias, status,
+                            cuda_stream);
   if (rc != B200_TRIMUL_OK) return rc;
   rc = b200_trimul_contract(left, right, tri, B, N, 0, N, direction, status, cuda_stream);
   if (rc != B200_TRIMUL_OK) return rc;

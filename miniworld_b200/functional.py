@@ -152,6 +152,7 @@ def prologue(
     pair_mask: Optional[torch.Tensor] = None,
     row_begin: int = 0,
     eps_in: float = 1e-5,
+    has_bias: bool = False,
 ) -> None:
     """``z`` holds pair rows row_begin .. row_begin+rows-1: [B, rows, N, 128]; writes left/right [B, rows, 128, N]."""
     B, N = _check_z(z)
@@ -161,7 +162,7 @@ def prologue(
     with torch.cuda.device(z.device):
         rc = _lib.load().b200_trimul_prologue(
             _ptr(z), _ptr(packed), _ptr(tm), _ptr(pm), _ptr(left), _ptr(right), B, N, row_begin, rows, float(eps_in),
-            _ptr(status), _stream(z.device),
+            int(bool(has_bias)), _ptr(status), _stream(z.device),
         )
     _lib.check(rc, "b200_trimul_prologue")
 

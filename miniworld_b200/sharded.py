@@ -1,0 +1,109 @@
+"""Multi-GPU forms of the triangle multiplicative update (one process per GPU, ``torch.distributed``).
+
+Two schemes, neither present in the reference (it only has data-parallel training):
+
+* :class:`RowShardedTriangleMultiplication` - the pair tensor is sharded by rows ``i`` (B = 1). The prologue
+  and the epilogue are local to the rows a rank owns. The contraction needs the other ranks' rows of the
+  contracted operand(s), which are all-gathered into local HBM (NCCL) and then read by local TMA loads; no
+  kernel ever loads from a peer's memory.
+    outgoing  t[i in I_r, j] = sum_k a[i,k] b[j,k]     -> all-gather of ``right`` (rows j)
+    incoming  t[i in I_r, j] = sum_k a[k,i] b[k,j]     -> all-gather of ``left`` and ``right`` (rows k);
+                                                           the rank uses columns I_r of ``left``
+  The row-plane layout [rows, H, N] makes the gathered tensor [P, N/P, H, N] == [N, H, N] with no repacking.
+* :func:`shard_batch` - plain batch data parallelism for B > 1: samples are independent, no collective.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import functional as F_
+from .modules import TriangleMultiplication
+
+D = 128
+
+
+def row_range(n_rows: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [begin, begin+count) owned by ``rank``: equal contiguous blocks; N must divide evenly."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad world/rank {world}/{rank}")
+    if n_rows % world != 0:
+        raise ValueError(f"row sharding needs N divisible by the world size (N={n_rows}, world={world})")
+    count = n_rows // world
+    return rank * count, count
+
+
+def shard_batch(batch: int, world: int, rank: int) -> tuple[int, int]:
+    """Samples [begin, begin+count) of a batch owned by ``rank`` (contiguous, remainder to the first ranks)."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad world/rank {world}/{rank}")
+    base, rem = divmod(batch, world)
+    count = base + (1 if rank < rem else 0)
+    begin = rank * base + min(rank, rem)
+    return begin, count
+
+
+class RowShardedTriangleMultiplication(TriangleMultiplication):
+    """Same parameters and state_dict as :class:`TriangleMultiplication`; ``forward`` takes the local rows.
+
+    ``forward(pair_rows [1, N/P, N, 128] bf16, mask Bool[1, N] | None) -> [1, N/P, N, 128]``: the rows
+    ``rank*N/P ...`` of ``pair + update``. Every rank must call it (it contains a collective).
+    """
+
+    def __init__(self, d_pair: int = D, d_hidden: Optional[int] = None, outgoing: bool = True, group=None, **kw):
+        super().__init__(d_pair, d_hidden, outgoing=outgoing, **kw)
+        self.group = group
+        self._bufs = None
+
+    def _buffers(self, N: int, rows: int, device: torch.device):
+        key = (N, rows, device)
+        if self._bufs is None or self._bufs[0] != key:
+            plane = lambda r: torch.empty(1, r, D, N, dtype=torch.bfloat16, device=device)  # noqa: E731
+            bufs = dict(
+                packed=F_.aligned_empty(F_.packed_bytes(), device),
+                status=torch.zeros(16, dtype=torch.int32, device=device),
+                left=plane(rows),
+                right=plane(rows),
+                right_all=plane(N),
+                left_all=None if self.outgoing else plane(N),
+                tri=plane(rows),
+            )
+            self._bufs = (key, bufs)
+        return self._bufs[1]
+
+    def forward(self, pair_rows: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if torch.is_grad_enabled() and pair_rows.requires_grad:
+            raise NotImplementedError("backward is not implemented")
+        if not pair_rows.is_cuda:
+            raise RuntimeError("pair rows must be a CUDA tensor: this module has no CPU implementation")
+        world = dist.get_world_size(self.group)
+        rank = dist.get_rank(self.group)
+        if pair_rows.dim() != 4 or pair_rows.shape[0] != 1 or pair_rows.shape[3] != D:
+            raise RuntimeError(f"pair rows must be [1, N/P, N, {D}], got {tuple(pair_rows.shape)}")
+        rows, N = int(pair_rows.shape[1]), int(pair_rows.shape[2])
+        begin, count = row_range(N, world, rank)
+        if count != rows:
+            raise RuntimeError(f"rank {rank} of {world} owns {count} rows of N={N}, got {rows}")
+        z = pair_rows.detach().to(torch.bfloat16).contiguous()
+        dev = z.device
+        b = self._buffers(N, rows, dev)
+        F_.pack_weights(self._params(), b["packed"], self._biases)
+        b["status"].zero_()
+        has_bias = bool(self._biases) and any(self._biases.get(k) is not None for k in F_.BIAS_ORDER[:4])
+        F_.prologue(z, b["packed"], b["left"], b["right"], b["status"], token_mask=mask, row_begin=begin,
+                    eps_in=float(self.ln_pair.eps), has_bias=has_bias)
+        dist.all_gather_into_tensor(b["right_all"], b["right"], group=self.group)
+        if self.outgoing:
+            F_.contract(b["left"], b["right_all"], b["tri"], b["status"], 1, N, begin, rows, True)
+        else:
+            dist.all_gather_into_tensor(b["left_all"], b["left"], group=self.group)
+            F_.contract(b["left_all"], b["right_all"], b["tri"], b["status"], 1, N, begin, rows, False)
+        y = torch.empty_like(z)
+        F_.epilogue(b["tri"], z, b["packed"], y, b["status"], eps_in=float(self.ln_pair.eps),
+                    eps_out=float(self.ln_out.eps), residual=self.residual)
+        if self.check_status:
+            F_.check_status(b["status"], "row-sharded trimul")
+        return y

@@ -37,17 +37,23 @@ def test_pack_weights(wdtype):
     p = rand_params(3, dtype=wdtype)
     biases = {"to_left_gate": torch.full((128,), 1.0), "to_gate": torch.linspace(-1, 1, 128)}
     packed = _packed(p, {k: v.to(DEV) for k, v in biases.items()})
-    mats = packed[: 6 * 32768].view(torch.bfloat16).view(6, 128, 128).float().cpu()
+    mats = torch.cat([
+        packed[: 4 * 32768].view(torch.float16).view(4, 128, 128).float().cpu(),  # prologue matrices: fp16
+        packed[4 * 32768 : 6 * 32768].view(torch.bfloat16).view(2, 128, 128).float().cpu(),  # epilogue: bf16
+    ])
     d1 = packed[6 * 32768 : 6 * 32768 + 2048].view(torch.float32).view(4, 128).cpu()
     c3 = packed[6 * 32768 + 2048 : 6 * 32768 + 4096].view(torch.float32).view(128, 4).cpu()
+    ln = packed[6 * 32768 + 4096 : 6 * 32768 + 5120].view(torch.float32).view(2, 128).cpu()
+    assert torch.equal(ln[0], p["ln_pair.weight"]) and torch.equal(ln[1], p["ln_pair.bias"])
     names = ["to_left", "to_left_gate", "to_right", "to_right_gate", "to_out", "to_gate"]
     for m, name in enumerate(names):
         w = p[name + ".weight"].float()
         gamma = p["ln_out.weight"] if name == "to_out" else p["ln_pair.weight"]
         beta = p["ln_out.bias"] if name == "to_out" else p["ln_pair.bias"]
-        want = (0.5 * w * gamma[None, :]).to(torch.bfloat16).float()
+        folded = m >= 4  # the prologue applies the input LayerNorm affine itself
+        want = (0.5 * w * gamma[None, :]).to(torch.bfloat16).float() if folded else (0.5 * w).to(torch.float16).float()
         assert torch.equal(mats[m], want), name
-        d = 0.5 * (w @ beta + biases.get(name, torch.zeros(128)))
+        d = 0.5 * ((w @ beta if folded else 0.0) + biases.get(name, torch.zeros(128)))
         s = want.sum(1)
         if m < 4:
             torch.testing.assert_close(d1[m], d, rtol=1e-5, atol=1e-6)

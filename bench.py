@@ -279,9 +279,9 @@ def run_b200(args):
         plane = B * N * 128 * N
         status = ws[:64].view(torch.int32)
         packed = ws[layout[1] : layout[1] + F_.packed_bytes()]
-        left = ws[layout[2] : layout[2] + plane * 2].view(torch.bfloat16).view(B, N, 128, N)
-        right = ws[layout[3] : layout[3] + plane * 2].view(torch.bfloat16).view(B, N, 128, N)
-        tri = ws[layout[4] : layout[4] + plane * 2].view(torch.bfloat16).view(B, N, 128, N)
+        left = ws[layout[2] : layout[2] + plane * 2].view(torch.float16).view(B, N, 128, N)
+        right = ws[layout[3] : layout[3] + plane * 2].view(torch.float16).view(B, N, 128, N)
+        tri = ws[layout[4] : layout[4] + plane * 2].view(torch.float16).view(B, N, 128, N)
         y = torch.empty_like(z)
         params = mods["outgoing"]._params()
         names = ("pack", "prologue", "contract_outgoing", "contract_incoming", "epilogue")

@@ -19,8 +19,10 @@
  *  - Return value: 0 on success, a negative B200_TRIMUL_E_* code otherwise. Device-side waits are
  *    bounded; if one runs out the kernels finish, and `b200_trimul_read_status` reports a positive
  *    device code (101 producer, 102 MMA issuer, 103 epilogue, 104 statistics, 105 drain).
- *  - Intermediate layout ("row-plane"): left / right / tri are [B, rows, 128, N] bf16, i.e. for every
- *    pair row a [channel, column] slab.
+ *  - Intermediate layout ("row-plane"): left / right / tri are [B, rows, 128, N] fp16, i.e. for every
+ *    pair row a [channel, column] slab. fp16 (same tensor-core rate as bf16, three more mantissa bits)
+ *    is what keeps the bf16 module output inside its max-abs bound; tri holds t * 2^-4, saturated to
+ *    the fp16 range.
  */
 #ifndef B200_TRIMUL_H_
 #define B200_TRIMUL_H_
@@ -82,7 +84,7 @@ int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const 
  * Stage 1: LayerNorm + gated left/right projections + mask, for `rows` pair rows of each sample.
  * z: [B, rows, N, 128] bf16 (rows row_begin .. row_begin+rows-1 of the full pair tensor);
  * token_mask: [B, N] uint8 or null; pair_mask: [B, rows, N] uint8 (the same rows as z) or null;
- * left / right: [B, rows, 128, N] bf16. `has_bias`: non-zero iff `packed` was built with a bias on any of the
+ * left / right: [B, rows, 128, N] fp16. `has_bias`: non-zero iff `packed` was built with a bias on any of the
  * four left/right linears. `status` is a device int (e.g. the workspace start).
  */
 int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
@@ -93,7 +95,7 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
  * Stage 2: per-channel contraction for output rows row_begin .. row_begin+rows-1.
  * outgoing: left is [B, rows, 128, N] (the local rows), right is [B, N, 128, N] (all rows).
  * incoming: left and right are both [B, N, 128, N] (all rows k).
- * tri: [B, rows, 128, N] bf16. Replaces the `torch.bmm` every reference backend uses for this step
+ * tri: [B, rows, 128, N] fp16 (t * 2^-4). Replaces the `torch.bmm` every reference backend uses for this step
  * (docs/archive/trimul-fusion/inference.md:17).
  */
 int b200_trimul_contract(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
@@ -101,7 +103,7 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
 
 /*
  * Stage 3: output LayerNorm + output projection + sigmoid output gate (+ residual) for `rows` rows.
- * tri: [B, rows, 128, N]; z, y: [B, rows, N, 128] bf16. y may alias z.
+ * tri: [B, rows, 128, N] fp16 as written by stage 2; z, y: [B, rows, N, 128] bf16. y may alias z.
  */
 int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows,
                          float eps_in, float eps_out, int residual, int* status, void* cuda_stream);

@@ -5,9 +5,10 @@
 // Both LayerNorms are folded around the GEMMs so the tensor cores consume the raw bf16 tiles:
 //   LN(v) W^T = rstd * (v W'^T - mean * s) + d,   W' = bf16(0.5 * W * gamma), s = rowsum(W'), d = 0.5 * (W beta + bias)
 // (the 0.5 turns sigmoid(g) * p into (tanh(g/2) + 1) * (p/2)).  mean / rstd are per position and come
-// from the tiles already in shared memory; s, d are per output channel.  (Mixing a bf16 activation with
-// an fp16 weight in one kind::f16 MMA is rejected by the hardware as an illegal instruction, so the
-// folded weights are bf16 like the activations.)
+// from the tiles already in shared memory; s, d are per output channel.  Both operands of one MMA must
+// share a 16-bit format (mixing bf16 with fp16 raises an illegal instruction), so the output projection
+// is fp16 x fp16 (t arrives as fp16, scaled by 2^-4; eps_out is scaled by 2^-8 to match) and the gate is
+// bf16 x bf16 (z is the module's bf16 input).
 //
 // One persistent CTA per SM walks tiles of 128 consecutive columns j of one pair row (b, i).  Per tile
 //   P[pos, c] = t^T[pos, h] * Wo'[c, h]   (A = t tile as loaded from the row-plane layout: MN-major)
@@ -150,7 +151,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_p = umma_idesc(128, 128, true, false);
+      constexpr uint32_t idesc_p = umma_idesc(128, 128, true, false, kFmtF16, kFmtF16);
       constexpr uint32_t idesc_g = umma_idesc(128, 128, false, false);
       bool ok = mbar_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma);
       int it = 0;
@@ -246,7 +247,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
           const int h = hq * 32 + hh;
           uint32_t raw;
           asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw) : "r"(tcol + h * 128 + ((tchunk ^ (h & 7)) << 4)));
-          const float2 x = bf16x2_to_float2(raw);
+          const float2 x = f16x2_to_float2(raw);
           if (hh == 0) pv = x;
           const float2 d = __fadd2_rn(x, make_float2(-pv.x, -pv.y));
           s1 = __fadd2_rn(s1, d);

@@ -12,7 +12,8 @@
 // One persistent CTA per SM walks tiles of 128 consecutive columns j of one pair row (b, i).
 // Per tile the four GEMMs are issued as D^T[h, pos] = W[h, c] * x_hat^T[c, pos] on tcgen05, so TMEM
 // lanes are channels and columns are positions: each epilogue thread owns one channel and writes
-// runs of consecutive positions, which is exactly the row-plane layout [B, rows, H, N] of the outputs.
+// runs of consecutive positions, which is exactly the row-plane layout [B, rows, H, N] of the outputs
+// (written as fp16; masked cells are exactly zero).
 //
 // Outputs leave through a swizzled shared-memory staging tile and TMA stores (full 128-byte rows);
 // direct per-thread 16-byte stores to 128 different channel rows ran the store path at a third of this.
@@ -45,8 +46,6 @@ struct PrologueParams {
   const float* d1;            // [4][128] additive constants (0.5 * bias): left, left gate, right, right gate
   const float* ln_w;          // [128] LayerNorm gamma
   const float* ln_b;          // [128] LayerNorm beta
-  __nv_bfloat16* left_out;    // [B, rows, 128, N]
-  __nv_bfloat16* right_out;   // [B, rows, 128, N]
   float eps;
   int* status;
 };
@@ -360,7 +359,7 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
                 gg = __fadd2_rn(gg, make_float2(dg, dg));
               }
               const float2 th = make_float2(tanh_approx(gg.x), tanh_approx(gg.y));
-              o[c16 * 8 + t] = pack_bf16x2(__ffma2_rn(th, hp, hp));
+              o[c16 * 8 + t] = pack_f16x2(__ffma2_rn(th, hp, hp));
             }
           }
           if (bits != 0xFFFFFFFFu) {

@@ -251,6 +251,9 @@ __device__ __forceinline__ float2 bf16x2_to_float2(uint32_t v) {
   return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float2 v) { return pack_bf16x2(v.x, v.y); }
+__device__ __forceinline__ float2 f16x2_to_float2(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
 __device__ __forceinline__ uint32_t pack_f16x2(float2 v) {
   __half2 h = __float22half2_rn(v);
   return *reinterpret_cast<uint32_t*>(&h);

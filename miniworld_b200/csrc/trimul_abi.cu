@@ -35,7 +35,7 @@ static thread_local int tl_last_cuda_error = 0;
 // Weight packing: one warp per matrix row.
 //   matrices 0..3 (left, left gate, right, right gate): W' = fp16(0.5 W), d = 0.5 bias
 //     (the prologue applies the input LayerNorm affine itself; gamma_in / beta_in are copied alongside)
-//   matrix 4 (out):  W' = bf16(0.5 W gamma_out), s = rowsum(W'), d = 0.5 (W beta_out + bias)
+//   matrix 4 (out):  W' = fp16(0.5 W gamma_out), s = rowsum(W'), d = 0.5 (W beta_out + bias)
 //   matrix 5 (gate): W' = bf16(0.5 W gamma_in),  s = rowsum(W'), d = 0.5 (W beta_in + bias)
 struct PackArgs {
   const void* w[6];
@@ -68,20 +68,23 @@ __global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* pa
   const float bb[4] = {b.x, b.y, b.z, b.w};
   float s = 0.f, d = 0.f;
   uint16_t o[4];
-  // The prologue's matrices meet an fp16 x_hat, so they are fp16 (three more mantissa bits than bf16;
-  // |0.5 W| is far from 65504). The epilogue's matrices meet raw bf16 activations and both MMA operands
-  // must share one 16-bit format, so they are bf16 and carry the folded LayerNorm.
+  // Both operands of an MMA share one 16-bit format. Matrices 0..3 meet the fp16 x_hat and matrix 4 the
+  // fp16 t tile, so they are fp16 (three more mantissa bits than bf16; |0.5 W gamma| is far from 65504).
+  // Matrix 5 meets the module's raw bf16 input, so it is bf16.
   const bool fold = m >= 4;
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
-    if (fold) {
-      const __nv_bfloat16 v = __float2bfloat16_rn(0.5f * w[t] * gg[t]);
-      o[t] = __bfloat16_as_ushort(v);
-      s += __bfloat162float(v);
-      d = fmaf(w[t], bb[t], d);
+    const float v = fold ? 0.5f * w[t] * gg[t] : 0.5f * w[t];
+    if (m == 5) {
+      const __nv_bfloat16 r = __float2bfloat16_rn(v);
+      o[t] = __bfloat16_as_ushort(r);
+      s += __bfloat162float(r);
     } else {
-      o[t] = __half_as_ushort(__float2half_rn(0.5f * w[t]));
+      const __half r = __float2half_rn(v);
+      o[t] = __half_as_ushort(r);
+      s += __half2float(r);
     }
+    if (fold) d = fmaf(w[t], bb[t], d);
   }
   if (gw == 0) {
     reinterpret_cast<float4*>(packed + kPackedLnOff)[lane] = g;
@@ -383,8 +386,6 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
   p.d1 = reinterpret_cast<const float*>(static_cast<const uint8_t*>(packed) + kPackedD1Off);
   p.ln_w = reinterpret_cast<const float*>(static_cast<const uint8_t*>(packed) + kPackedLnOff);
   p.ln_b = p.ln_w + 128;
-  p.left_out = static_cast<__nv_bfloat16*>(left);
-  p.right_out = static_cast<__nv_bfloat16*>(right);
   p.eps = eps_in;
   p.status = status;
   const int grid = p.num_tiles < info.sms ? p.num_tiles : info.sms;
@@ -506,7 +507,7 @@ int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, voi
   p.num_tiles = static_cast<int>(nrows) * p.tiles_per_row;
   p.c3 = reinterpret_cast<const float4*>(static_cast<const uint8_t*>(packed) + kPackedC3Off);
   p.eps_in = eps_in;
-  p.eps_out = eps_out;
+  p.eps_out = eps_out * (kTriScale * kTriScale);  // tri arrives scaled by kTriScale
   p.residual = residual;
   p.status = status;
   rc = set_smem(epilogue_kernel, kEpiSmemBytes);

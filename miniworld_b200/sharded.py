@@ -61,7 +61,7 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
     def _buffers(self, N: int, rows: int, device: torch.device):
         key = (N, rows, device)
         if self._bufs is None or self._bufs[0] != key:
-            plane = lambda r: torch.empty(1, r, D, N, dtype=torch.bfloat16, device=device)  # noqa: E731
+            plane = lambda r: torch.empty(1, r, D, N, dtype=torch.float16, device=device)  # noqa: E731
             bufs = dict(
                 packed=F_.aligned_empty(F_.packed_bytes(), device),
                 status=torch.zeros(16, dtype=torch.int32, device=device),

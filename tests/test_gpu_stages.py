@@ -32,14 +32,22 @@ def _nan_bf16(*shape):
     return torch.full(shape, float("nan"), dtype=torch.bfloat16, device=DEV)
 
 
+def _nan_f16(*shape):
+    """NaN-poisoned fp16 buffer (the intermediates left / right / tri are fp16; tri is scaled by 2^-4)."""
+    return torch.full(shape, float("nan"), dtype=torch.float16, device=DEV)
+
+
+TRI_SCALE = 0.0625
+
+
 @pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
 def test_pack_weights(wdtype):
     p = rand_params(3, dtype=wdtype)
     biases = {"to_left_gate": torch.full((128,), 1.0), "to_gate": torch.linspace(-1, 1, 128)}
     packed = _packed(p, {k: v.to(DEV) for k, v in biases.items()})
     mats = torch.cat([
-        packed[: 4 * 32768].view(torch.float16).view(4, 128, 128).float().cpu(),  # prologue matrices: fp16
-        packed[4 * 32768 : 6 * 32768].view(torch.bfloat16).view(2, 128, 128).float().cpu(),  # epilogue: bf16
+        packed[: 5 * 32768].view(torch.float16).view(5, 128, 128).float().cpu(),  # fp16: meet fp16 activations
+        packed[5 * 32768 : 6 * 32768].view(torch.bfloat16).view(1, 128, 128).float().cpu(),  # gate: meets bf16 z
     ])
     d1 = packed[6 * 32768 : 6 * 32768 + 2048].view(torch.float32).view(4, 128).cpu()
     c3 = packed[6 * 32768 + 2048 : 6 * 32768 + 4096].view(torch.float32).view(128, 4).cpu()
@@ -51,7 +59,7 @@ def test_pack_weights(wdtype):
         gamma = p["ln_out.weight"] if name == "to_out" else p["ln_pair.weight"]
         beta = p["ln_out.bias"] if name == "to_out" else p["ln_pair.bias"]
         folded = m >= 4  # the prologue applies the input LayerNorm affine itself
-        want = (0.5 * w * gamma[None, :]).to(torch.bfloat16).float() if folded else (0.5 * w).to(torch.float16).float()
+        want = (0.5 * w * gamma[None, :]).to(torch.bfloat16 if name == "to_gate" else torch.float16).float() if folded else (0.5 * w).to(torch.float16).float()
         assert torch.equal(mats[m], want), name
         d = 0.5 * ((w @ beta if folded else 0.0) + biases.get(name, torch.zeros(128)))
         s = want.sum(1)
@@ -69,21 +77,22 @@ def test_pack_weights(wdtype):
 @pytest.mark.parametrize("B,N", [(1, 16), (2, 64), (1, 136), (1, 256), (1, 384), (1, 200)])
 def test_contract_matches_einsum(B, N, outgoing):
     g = torch.Generator().manual_seed(100 + N)
-    left = torch.randn(B, N, 128, N, generator=g).to(torch.bfloat16).to(DEV)
-    right = torch.randn(B, N, 128, N, generator=g).to(torch.bfloat16).to(DEV)
-    tri = _nan_bf16(B, N, 128, N)
+    left = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    right = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    tri = _nan_f16(B, N, 128, N)
     st = _status()
     F_.contract(left, right, tri, st, B, N, 0, N, outgoing)
     F_.check_status(st, "contract")
     lf, rf = left.float(), right.float()
     # row-plane [b, row, h, col]
     ref = torch.einsum("bihk,bjhk->bihj", lf, rf) if outgoing else torch.einsum("bkhi,bkhj->bihj", lf, rf)
-    assert torch.isfinite(tri.float()).all()
-    rel = oracle.rel_frobenius(tri.float().cpu(), ref.cpu())
-    assert rel < 3e-3, rel  # bf16 rounding of the stored result
-    # elementwise: within one bf16 ulp of the fp32 result
-    err = (tri.float() - ref).abs()
-    tol = ref.abs() * 2**-7 + 1e-3
+    got = tri.float() / TRI_SCALE
+    assert torch.isfinite(got).all()
+    rel = oracle.rel_frobenius(got.cpu(), ref.cpu())
+    assert rel < 4e-4, rel  # fp16 rounding of the stored result
+    # elementwise: within one fp16 ulp of the fp32 result
+    err = (got - ref).abs()
+    tol = ref.abs() * 2**-10 + 2e-3
     assert bool((err <= tol).all()), float((err - tol).max())
 
 
@@ -92,12 +101,12 @@ def test_contract_row_range(outgoing):
     """A row range of the output (what one rank of a row-sharded run computes) equals the slice of the full result."""
     B, N, r0, rows = 1, 192, 64, 72
     g = torch.Generator().manual_seed(7)
-    left = torch.randn(B, N, 128, N, generator=g).to(torch.bfloat16).to(DEV)
-    right = torch.randn(B, N, 128, N, generator=g).to(torch.bfloat16).to(DEV)
-    full = _nan_bf16(B, N, 128, N)
+    left = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    right = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    full = _nan_f16(B, N, 128, N)
     st = _status()
     F_.contract(left, right, full, st, B, N, 0, N, outgoing)
-    part = _nan_bf16(B, rows, 128, N)
+    part = _nan_f16(B, rows, 128, N)
     a_in = left[:, r0 : r0 + rows].contiguous() if outgoing else left
     F_.contract(a_in, right, part, st, B, N, r0, rows, outgoing)
     F_.check_status(st, "contract")
@@ -124,7 +133,7 @@ def test_prologue_matches_oracle(B, N, mask_kind):
     st_ref = oracle.trimul_forward_stages(z, p, mask, pair_mask=pair_mask)
     packed = _packed(p)
     zd = z.to(DEV)
-    left, right = _nan_bf16(B, N, 128, N), _nan_bf16(B, N, 128, N)
+    left, right = _nan_f16(B, N, 128, N), _nan_f16(B, N, 128, N)
     st = _status()
     F_.prologue(zd, packed, left, right, st, token_mask=mask, pair_mask=pair_mask, row_begin=0, eps_in=1e-5)
     F_.check_status(st, "prologue")
@@ -138,8 +147,8 @@ def test_prologue_matches_oracle(B, N, mask_kind):
             assert bool((got == 0).all())
             continue
         rel = oracle.rel_frobenius(got, ref)
-        assert rel < 6e-3, (name, rel)
-        assert oracle.max_abs(got, ref) < 6e-2, name
+        assert rel < 1.5e-3, (name, rel)  # fp16 x_hat / weights / output, tanh.approx gate
+        assert oracle.max_abs(got, ref) < 1e-2, name
 
 
 def test_prologue_row_range_and_eps():
@@ -151,15 +160,15 @@ def test_prologue_row_range_and_eps():
     mask = torch.rand(B, N, generator=g) > 0.25
     packed = _packed(p)
     st = _status()
-    full_l, full_r = _nan_bf16(B, N, 128, N), _nan_bf16(B, N, 128, N)
+    full_l, full_r = _nan_f16(B, N, 128, N), _nan_f16(B, N, 128, N)
     F_.prologue(z.to(DEV), packed, full_l, full_r, st, token_mask=mask, eps_in=0.03)
-    part_l, part_r = _nan_bf16(B, rows, 128, N), _nan_bf16(B, rows, 128, N)
+    part_l, part_r = _nan_f16(B, rows, 128, N), _nan_f16(B, rows, 128, N)
     F_.prologue(z[:, r0 : r0 + rows].contiguous().to(DEV), packed, part_l, part_r, st, token_mask=mask, row_begin=r0, eps_in=0.03)
     F_.check_status(st, "prologue")
     assert torch.equal(part_l, full_l[:, r0 : r0 + rows])
     assert torch.equal(part_r, full_r[:, r0 : r0 + rows])
     ref = oracle.trimul_forward_stages(z, p, mask, eps_in=0.03)
-    assert oracle.rel_frobenius(from_row_plane(full_l.float().cpu()), ref.left) < 6e-3
+    assert oracle.rel_frobenius(from_row_plane(full_l.float().cpu()), ref.left) < 1.5e-3
 
 
 @pytest.mark.parametrize("residual", [True, False])
@@ -179,7 +188,8 @@ def test_epilogue_matches_torch(B, N, residual):
     packed = _packed(p)
     y = _nan_bf16(B, N, N, 128)
     st = _status()
-    F_.epilogue(to_row_plane(tri).to(DEV), z.to(DEV), packed, y, st, eps_in=eps_in, eps_out=eps_out, residual=residual)
+    tri_dev = (to_row_plane(tri).float() * TRI_SCALE).to(torch.float16).to(DEV)  # what the contraction stores
+    F_.epilogue(tri_dev, z.to(DEV), packed, y, st, eps_in=eps_in, eps_out=eps_out, residual=residual)
     F_.check_status(st, "epilogue")
     got = y.float().cpu()
     assert torch.isfinite(got).all()

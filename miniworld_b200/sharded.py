@@ -95,11 +95,12 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
         has_bias = bool(self._biases) and any(self._biases.get(k) is not None for k in F_.BIAS_ORDER[:4])
         F_.prologue(z, b["packed"], b["left"], b["right"], b["status"], token_mask=mask, row_begin=begin,
                     eps_in=float(self.ln_pair.eps), has_bias=has_bias)
-        dist.all_gather_into_tensor(b["right_all"], b["right"], group=self.group)
+        # B = 1: gather on [rows, 128, N] views so that the rank-major concatenation is the row dimension
+        dist.all_gather_into_tensor(b["right_all"].view(N, D, N), b["right"].view(rows, D, N), group=self.group)
         if self.outgoing:
             F_.contract(b["left"], b["right_all"], b["tri"], b["status"], 1, N, begin, rows, True)
         else:
-            dist.all_gather_into_tensor(b["left_all"], b["left"], group=self.group)
+            dist.all_gather_into_tensor(b["left_all"].view(N, D, N), b["left"].view(rows, D, N), group=self.group)
             F_.contract(b["left_all"], b["right_all"], b["tri"], b["status"], 1, N, begin, rows, False)
         y = torch.empty_like(z)
         F_.epilogue(b["tri"], z, b["packed"], y, b["status"], eps_in=float(self.ln_pair.eps),

@@ -1,0 +1,148 @@
+"""Host-side logic that needs no GPU: module surface (constructor, state_dict, aliases, dtype policy, loud errors),
+synthetic workloads, shard planning, and the row-sharded collective schedule on two gloo ranks."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import miniworld_b200 as mw
+from miniworld_b200 import sharded, synthetic
+from oracle import trimul_oracle as oracle
+from tests.helpers import rand_params
+
+REFERENCE_KEYS = [
+    "ln_pair.weight", "ln_pair.bias", "to_left.weight", "to_left_gate.weight", "to_right.weight",
+    "to_right_gate.weight", "ln_out.weight", "ln_out.bias", "to_gate.weight", "to_out.weight",
+]
+
+
+def test_state_dict_layout_matches_the_reference_module():
+    m = mw.TriangleMultiplication(128)
+    assert list(m.state_dict().keys()) == REFERENCE_KEYS
+    assert all(v.shape == (128, 128) for k, v in m.state_dict().items() if k.startswith("to_"))
+    # the reference zero-initialises the two output linears
+    assert float(m.to_gate.weight.abs().max()) == 0.0 and float(m.to_out.weight.abs().max()) == 0.0
+    m.load_state_dict(rand_params(1))
+    m2 = mw.TriangleMultiplication(128, outgoing=False, implementation="miniworld", p_drop=0.25)
+    m2.load_state_dict(m.state_dict())
+    assert not m2.outgoing and m2.p_drop == 0.25
+
+
+def test_layernorm_affine_stays_fp32_and_linears_follow_the_module_dtype():
+    m = mw.TriangleMultiplication(128).to(torch.bfloat16)
+    assert m.ln_pair.weight.dtype == torch.float32 and m.ln_out.bias.dtype == torch.float32
+    assert m.to_left.weight.dtype == torch.bfloat16
+    m.ln_pair.eps = 0.03  # mutable attribute read at call time
+    assert m.ln_pair.eps == 0.03
+
+
+def test_openfold_alias_round_trip():
+    p = rand_params(2)
+    of = mw.to_openfold_state_dict(p)
+    assert set(of) == {
+        "layer_norm_in.weight", "layer_norm_in.bias", "linear_a_p.weight", "linear_a_g.weight", "linear_b_p.weight",
+        "linear_b_g.weight", "layer_norm_out.weight", "layer_norm_out.bias", "linear_g.weight", "linear_z.weight",
+    }
+    back = mw.from_openfold_state_dict(of)
+    assert list(back) == list(p) and all(torch.equal(back[k], p[k]) for k in p)
+    of["linear_g.bias"] = torch.ones(128)
+    with pytest.raises(KeyError):
+        mw.from_openfold_state_dict(of)
+    m = mw.TriangleMultiplicationIncoming(128, residual=False)
+    assert not m.outgoing and not m.residual
+
+
+def test_unsupported_configurations_raise():
+    with pytest.raises(NotImplementedError):
+        mw.TriangleMultiplication(64)
+    with pytest.raises(NotImplementedError):
+        mw.TriangleMultiplication(128, d_hidden=256)
+    with pytest.raises(ValueError):
+        mw.TriangleMultiplication(128, implementation="cuequivariance")
+    m = mw.TriangleMultiplication(128)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        m(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16))  # no CPU implementation, no fallback
+    m.p_drop = 0.1
+    m.train()
+    with pytest.raises(NotImplementedError):
+        m(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError):
+        mw.TriangleMultiplication(128).eval()(torch.zeros(1, 8, 8, 128), torch.ones(1, 8, 8, dtype=torch.bool))
+
+
+def test_synthetic_workloads_are_deterministic_and_shaped():
+    a = synthetic.make_workload("n384", seed=3, n_override=32)
+    b = synthetic.make_workload("n384", seed=3, n_override=32)
+    assert torch.equal(a.z, b.z) and torch.equal(a.mask, b.mask)
+    assert a.z.dtype == torch.bfloat16 and a.z.shape == (1, 32, 32, 128)
+    assert int((~a.mask).sum()) == 3  # last ~10 % of the tokens padded
+    c = synthetic.make_workload("batch8x256", seed=0, n_override=16)
+    assert c.z.shape[0] == 8 and bool(c.mask[:, 0].all())  # tails padded, heads valid
+    d = synthetic.make_workload("cpu128", seed=0, n_override=8)
+    assert d.z.dtype == torch.float32 and d.directions == ("outgoing",)
+    f = synthetic.flops(1, 768)
+    assert abs(f["contraction"] - 115.96e9) < 1e8 and abs(f["projection"] - 115.96e9) < 1e8
+    assert synthetic.pass_bytes(1, 768) == 150994944
+
+
+def test_shard_planning():
+    assert [sharded.row_range(768, 4, r) for r in range(4)] == [(0, 192), (192, 192), (384, 192), (576, 192)]
+    with pytest.raises(ValueError):
+        sharded.row_range(100, 8, 0)
+    with pytest.raises(ValueError):
+        sharded.row_range(768, 4, 4)
+    parts = [sharded.shard_batch(8, 3, r) for r in range(3)]
+    assert parts == [(0, 3), (3, 3), (6, 2)]
+    assert sum(c for _, c in parts) == 8
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _row_sharded_worker(rank, world, port, outgoing, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        N = 16
+        p = rand_params(5)
+        g = torch.Generator().manual_seed(11)
+        z = torch.randn(1, N, N, 128, generator=g).to(torch.bfloat16)
+        mask = torch.rand(1, N, generator=g) > 0.2
+        begin, rows = sharded.row_range(N, world, rank)
+        # the schedule of RowShardedTriangleMultiplication.forward with the oracle's stages standing in for
+        # the three kernels: local prologue -> all-gather of the contracted operand(s) -> local contraction
+        full = oracle.trimul_forward_stages(z, p, mask, outgoing=outgoing)
+        left_loc = full.left[:, begin : begin + rows].permute(0, 1, 3, 2).contiguous()   # row-plane [1, rows, H, N]
+        right_loc = full.right[:, begin : begin + rows].permute(0, 1, 3, 2).contiguous()
+        right_all = torch.empty(1, N, 128, N)
+        dist.all_gather_into_tensor(right_all.view(N, 128, N), right_loc.view(rows, 128, N))
+        if outgoing:
+            tri = torch.einsum("bihk,bjhk->bihj", left_loc, right_all)
+        else:
+            left_all = torch.empty(1, N, 128, N)
+            dist.all_gather_into_tensor(left_all.view(N, 128, N), left_loc.view(rows, 128, N))
+            tri = torch.einsum("bkhi,bkhj->bihj", left_all[..., begin : begin + rows], right_all)
+        want = full.tri[:, begin : begin + rows].permute(0, 1, 3, 2)
+        ret[rank] = float((tri - want).abs().max())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("outgoing", [True, False])
+def test_row_sharded_schedule_on_two_gloo_ranks(outgoing):
+    """The gathered row-plane tensor is the full operand with no repacking, and each rank's rows of the
+    contraction equal the unsharded result (world_size 2, gloo, CPU)."""
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_row_sharded_worker, args=(world, port, outgoing, ret), nprocs=world, join=True)
+        assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)

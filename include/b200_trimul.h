@@ -48,6 +48,7 @@ extern "C" {
 #define B200_TRIMUL_E_WORKSPACE (-5)   /* workspace too small */
 #define B200_TRIMUL_E_CUDA (-6)        /* a CUDA runtime / driver call failed; see b200_trimul_last_cuda_error */
 #define B200_TRIMUL_E_DEVICE (-7)      /* not an sm_100 device */
+#define B200_TRIMUL_E_TOO_LARGE (-8)   /* b200_trimul_forward_static: B * N * N above its fixed limit */
 
 /* Library version (major * 100 + minor). */
 int b200_trimul_version(void);
@@ -121,6 +122,29 @@ int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_ga
                         const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask, void* y,
                         void* workspace, size_t workspace_bytes, int B, int N, int d_pair, int d_hidden,
                         int direction, float eps_in, float eps_out, int residual, void* cuda_stream);
+
+/*
+ * The same forward for callers that cannot give the library a workspace because they cannot allocate device
+ * memory at all: a server whose pool already owns the whole GPU (a late cudaMalloc fails, or stalls a
+ * latency-critical loop by synchronising the device), or a plug-in whose host forbids allocation after start-up.
+ * It has no counterpart in the reference, whose engine allocates its intermediates through PyTorch.
+ *
+ * The scratch is a 12.2 MiB array inside the library image, present on every GPU that loads the library until
+ * the process exits. Limit: B * N * N <= 16384 pair cells (one 128-token sample, four 64-token samples, ...);
+ * anything larger returns B200_TRIMUL_E_TOO_LARGE before any device work is issued. The function itself calls
+ * no allocator of any kind. Its first call on a device looks up the array's device address, so make that
+ * call before starting a stream capture. Every call on a device uses the same array, which keeps the previous
+ * call's contents: the status words are cleared on entry and all other regions are overwritten before they are
+ * read, but two calls that overlap on the GPU race on it - issue them on one stream, or serialise them.
+ * `device_status_out` (may be null) receives the device address of the status word for b200_trimul_read_status.
+ */
+int b200_trimul_forward_static(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
+                               const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                               const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                               const float* ln_out_b, const void* const* bias_opt, const uint8_t* token_mask,
+                               const uint8_t* pair_mask, void* y, int B, int N, int d_pair, int d_hidden,
+                               int direction, float eps_in, float eps_out, int residual, int** device_status_out,
+                               void* cuda_stream);
 
 /* Zero the status words at the start of a workspace (asynchronous). */
 int b200_trimul_clear_status(int* status, void* cuda_stream);

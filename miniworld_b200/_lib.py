@@ -49,6 +49,15 @@ SIGNATURES = {
         + [c_int] * 5
         + [c_float, c_float, c_int, c_void_p],
     ),
+    "b200_trimul_forward_static": (
+        c_int,
+        [c_void_p] * 7
+        + [c_int]
+        + [c_void_p] * 4
+        + [POINTER(c_void_p), c_void_p, c_void_p, c_void_p]
+        + [c_int] * 5
+        + [c_float, c_float, c_int, POINTER(c_void_p), c_void_p],
+    ),
     "b200_trimul_clear_status": (c_int, [c_void_p, c_void_p]),
     "b200_trimul_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
 }

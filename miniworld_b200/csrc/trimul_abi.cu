@@ -248,6 +248,8 @@ const char* b200_trimul_strerror(int code) {
     case B200_TRIMUL_E_WORKSPACE: return "workspace too small";
     case B200_TRIMUL_E_CUDA: return "CUDA call failed (see b200_trimul_last_cuda_error)";
     case B200_TRIMUL_E_DEVICE: return "device is not sm_100";
+    case B200_TRIMUL_E_TOO_LARGE:
+      return "problem does not fit the built-in scratch of b200_trimul_forward_static (B * N * N <= 16384)";
     case kDevTimeoutProducer: return "device: copy producer gave up waiting";
     case kDevTimeoutMma: return "device: MMA issuer gave up waiting";
     case kDevTimeoutEpilogue: return "device: epilogue gave up waiting";
@@ -557,3 +559,74 @@ int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_ga
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Forward for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot hand it a workspace: an inference server whose memory pool already
+// owns all of HBM (a late cudaMalloc fails, and even a successful one synchronises the whole device in
+// the middle of a latency-critical loop), or a plug-in running under a host program that forbids
+// allocation after start-up. For them the scratch of a small forward lives in the library image itself:
+// a file-scope device array, reserved on every GPU that loads the library until the process exits.
+//
+// Host code may not treat the array's name as a device address (it is only a host-side handle of the
+// symbol), so the address is looked up with cudaGetSymbolAddress once per device, with that device
+// current, the first time the entry point runs there; that first call should therefore be made before
+// any stream capture begins. All calls on a device share the one array: it keeps whatever the last call
+// left in it, the status words are cleared at the start of every call, everything else is overwritten
+// before it is read, and two calls that overlap on the GPU (different streams, or different host
+// threads) race on it.
+namespace trimul {
+
+constexpr long long kStaticMaxCells = 16384;  // B * N * N, e.g. one 128-token sample or four 64-token ones
+constexpr size_t kStaticPlaneBytes = static_cast<size_t>(kStaticMaxCells) * kC * 2;  // 4 MiB per intermediate
+constexpr size_t kStaticWorkspaceBytes = kStatusBytes + kPackedBytes + 3 * kStaticPlaneBytes;
+constexpr size_t kStaticScratchBytes = kStaticWorkspaceBytes + 1024;  // slack to reach 1024-byte alignment
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];  // 12.2 MiB per GPU
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_static_mutex;
+static void* g_static_ptr[kMaxDevices] = {};
+
+// Device address of the scratch on the current device, rounded up to 1024 bytes (set up on first use).
+static int static_scratch(void** out) {
+  int dev = 0;
+  TRIMUL_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return B200_TRIMUL_E_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* raw = nullptr;
+    TRIMUL_CUDA(cudaGetSymbolAddress(&raw, g_static_scratch));
+    if (raw == nullptr) return B200_TRIMUL_E_CUDA;
+    const uintptr_t a = (reinterpret_cast<uintptr_t>(raw) + 1023u) & ~static_cast<uintptr_t>(1023u);
+    g_static_ptr[dev] = reinterpret_cast<void*>(a);
+  }
+  *out = g_static_ptr[dev];
+  return B200_TRIMUL_OK;
+}
+
+}  // namespace trimul
+
+extern "C" int b200_trimul_forward_static(const void* z, const void* w_left, const void* w_left_gate,
+                                          const void* w_right, const void* w_right_gate, const void* w_gate,
+                                          const void* w_out, int weight_dtype, const float* ln_in_w,
+                                          const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,
+                                          const void* const* bias_opt, const uint8_t* token_mask,
+                                          const uint8_t* pair_mask, void* y, int B, int N, int d_pair, int d_hidden,
+                                          int direction, float eps_in, float eps_out, int residual,
+                                          int** device_status_out, void* cuda_stream) {
+  if (!z || !y) return B200_TRIMUL_E_NULL;
+  size_t need = 0;
+  int rc = b200_trimul_workspace_bytes(B, N, d_pair, d_hidden, direction, &need);
+  if (rc != B200_TRIMUL_OK) return rc;
+  if (static_cast<long long>(B) * N * N > kStaticMaxCells || need > kStaticWorkspaceBytes) return B200_TRIMUL_E_TOO_LARGE;
+  void* scratch = nullptr;
+  rc = static_scratch(&scratch);
+  if (rc != B200_TRIMUL_OK) return rc;
+  if (device_status_out != nullptr) *device_status_out = static_cast<int*>(scratch);
+  return b200_trimul_forward(z, w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out, weight_dtype, ln_in_w,
+                             ln_in_b, ln_out_w, ln_out_b, bias_opt, token_mask, pair_mask, y, scratch,
+                             kStaticWorkspaceBytes, B, N, d_pair, d_hidden, direction, eps_in, eps_out, residual,
+                             cuda_stream);
+}

@@ -235,7 +235,7 @@ contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int n0 = nt * BN;
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
-      const bool got = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevTimeoutEpilogue);
+      const bool got = mbar_wait_warp(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevTimeoutEpilogue);
       if (!named_bar_and(1, 128, got)) break;  // the four warps leave together or not at all
       tc_fence_after();
       const uint32_t t_acc = tmem_base + acc * kAccStride + (static_cast<uint32_t>(q * 32) << 16);

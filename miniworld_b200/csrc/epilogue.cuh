@@ -58,14 +58,18 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
   const uint32_t xchg_base = const_base + kEpiConstBytes;
   const uint32_t bar_base = xchg_base + 2 * kEpiXchgBytes;
   float4* const_ptr = reinterpret_cast<float4*>(smem + kEpiWBytes + 2 * kEpiStageBytes);
-  // barriers: w_full, tile_full[2], tile_empty[2], acc_full[2], acc_empty[2]
+  // barriers: w_full, t_full[2], z_full[2], t_empty[2], z_empty[2], acc_full[2], acc_empty[2].
+  // The t tile and the z tile of a stage are filled and released separately: t is dead as soon as the output
+  // statistics and the P MMAs are done, so the next t tile streams in while the epilogue still works on z.
   const uint32_t w_full = bar_base;
-  auto tile_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto tile_empty = [&](int s) { return bar_base + 8u * (3 + s); };
-  auto acc_full = [&](int s) { return bar_base + 8u * (5 + s); };
-  auto acc_empty = [&](int s) { return bar_base + 8u * (7 + s); };
+  auto t_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto z_full = [&](int s) { return bar_base + 8u * (3 + s); };
+  auto t_empty = [&](int s) { return bar_base + 8u * (5 + s); };
+  auto z_empty = [&](int s) { return bar_base + 8u * (7 + s); };
+  auto acc_full = [&](int s) { return bar_base + 8u * (9 + s); };
+  auto acc_empty = [&](int s) { return bar_base + 8u * (11 + s); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kEpiWBytes + 2 * kEpiStageBytes + kEpiConstBytes +
-                                                    2 * kEpiXchgBytes + 8 * 9);
+                                                    2 * kEpiXchgBytes + 8 * 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -74,8 +78,10 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(tile_full(s), 1);
-      mbar_init(tile_empty(s), 1);
+      mbar_init(t_full(s), 1);
+      mbar_init(z_full(s), 1);
+      mbar_init(t_empty(s), 1);
+      mbar_init(z_empty(s), 1);
       mbar_init(acc_full(s), 1);
       mbar_init(acc_empty(s), 8);
     }
@@ -112,20 +118,24 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
 #pragma unroll
         for (int kh = 0; kh < 2; ++kh)
           tma_load_2d(wo_base + m * 32768 + kh * 16384, &map_w, w_full, kh * 64, (4 + m) * 128);
-      int it = 0;
+      int it = 0, t_issued = 0, z_issued = 0;
       for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(tile_empty(s), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
         const int row = tile / p.tiles_per_row;
         const int j0 = (tile - row * p.tiles_per_row) * 128;
         const uint32_t ts = stage_base + s * kEpiStageBytes;
         const uint32_t zs = ts + 32768;
-        mbar_arrive_expect_tx(tile_full(s), kEpiStageBytes);
-        tma_load_3d(ts, &map_t, tile_full(s), j0, 0, row);
-        tma_load_3d(ts + 16384, &map_t, tile_full(s), j0 + 64, 0, row);
-        tma_load_3d(zs, &map_z, tile_full(s), 0, j0, row);
-        tma_load_3d(zs + 16384, &map_z, tile_full(s), 64, j0, row);
+        if (!mbar_wait(t_empty(s), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
+        mbar_arrive_expect_tx(t_full(s), 32768);
+        tma_load_3d(ts, &map_t, t_full(s), j0, 0, row);
+        tma_load_3d(ts + 16384, &map_t, t_full(s), j0 + 64, 0, row);
+        ++t_issued;
+        if (!mbar_wait(z_empty(s), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
+        mbar_arrive_expect_tx(z_full(s), 32768);
+        tma_load_3d(zs, &map_z, z_full(s), 0, j0, row);
+        tma_load_3d(zs + 16384, &map_z, z_full(s), 64, j0, row);
+        ++z_issued;
       }
       // Drain every copy this thread started before the CTA may exit.
       {
@@ -137,13 +147,17 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
           }
         }
       }
-      for (int back = 1; back <= 2 && back <= it; ++back) {
-        const int j = it - back;
-        const long long t0 = clock64();
-        while (!mbar_try_wait(tile_full(j & 1), (j >> 1) & 1)) {
-          if (clock64() - t0 > kWaitLimitCycles) {
-            atomicCAS(p.status, 0, kDevTimeoutDrain);
-            break;
+      for (int which = 0; which < 2; ++which) {
+        const int issued = which == 0 ? t_issued : z_issued;
+        for (int back = 1; back <= 2 && back <= issued; ++back) {
+          const int j = issued - back;
+          const uint32_t bar = which == 0 ? t_full(j & 1) : z_full(j & 1);
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar, (j >> 1) & 1)) {
+            if (clock64() - t0 > kWaitLimitCycles) {
+              atomicCAS(p.status, 0, kDevTimeoutDrain);
+              break;
+            }
           }
         }
       }
@@ -158,7 +172,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(tile_full(s), ph, abort_flag, p.status, kDevTimeoutMma)) break;
+        if (!mbar_wait(t_full(s), ph, abort_flag, p.status, kDevTimeoutMma)) break;
         if (!mbar_wait(acc_empty(s), ph ^ 1u, abort_flag, p.status, kDevTimeoutMma)) break;
         tc_fence_after();
         const uint32_t ts = stage_base + s * kEpiStageBytes;
@@ -171,6 +185,8 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
           const uint64_t db = umma_desc_kmajor(wo_base + (ks >> 2) * 16384) + static_cast<uint64_t>((ks & 3) * 2);
           umma_bf16(d_p, da, db, idesc_p, ks != 0 ? 1u : 0u);
         }
+        if (!mbar_wait(z_full(s), ph, abort_flag, p.status, kDevTimeoutMma)) break;
+        tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t da = umma_desc_kmajor(zs + (ks >> 2) * 16384) + static_cast<uint64_t>((ks & 3) * 2);
@@ -208,7 +224,32 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       const int row = tile / p.tiles_per_row;
       const int j0 = (tile - row * p.tiles_per_row) * 128;
       {
-        const bool got = mbar_wait(tile_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
+        const bool got = mbar_wait_warp(t_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
+        if (!named_bar_and(bar_id, 256, got)) break;
+      }
+      // ---- output partial statistics: two adjacent positions, 32 channels of the t tile
+      {
+        float2 pv = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
+#pragma unroll 8
+        for (int hh = 0; hh < 32; ++hh) {
+          const int h = hq * 32 + hh;
+          uint32_t raw;
+          asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw) : "r"(tcol + h * 128 + ((tchunk ^ (h & 7)) << 4)));
+          const float2 x = f16x2_to_float2(raw);
+          if (hh == 0) pv = x;
+          const float2 d = __fadd2_rn(x, make_float2(-pv.x, -pv.y));
+          s1 = __fadd2_rn(s1, d);
+          s2 = __ffma2_rn(d, d, s2);
+        }
+        const float mean0 = pv.x + s1.x * (1.0f / 32.0f), mean1 = pv.y + s1.y * (1.0f / 32.0f);
+        const float m20 = fmaxf(s2.x - s1.x * s1.x * (1.0f / 32.0f), 0.f);
+        const float m21 = fmaxf(s2.y - s1.y * s1.y * (1.0f / 32.0f), 0.f);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(xout + (hq * 128 + 2 * pp) * 8), "f"(mean0),
+                     "f"(m20), "f"(mean1), "f"(m21)
+                     : "memory");
+      }
+      {
+        const bool got = mbar_wait_warp(z_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
         if (!named_bar_and(bar_id, 256, got)) break;
       }
       // ---- input partial statistics over this thread's 64 channels of its z row (kept for the residual)
@@ -239,27 +280,6 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
         const float m2 = fmaxf(a2 - a1 * a1 * (1.0f / 64.0f), 0.f);
         asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xin + (half * 128 + pos) * 8), "f"(mean), "f"(m2) : "memory");
       }
-      // ---- output partial statistics: two adjacent positions, 32 channels of the t tile
-      {
-        float2 pv = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
-#pragma unroll 8
-        for (int hh = 0; hh < 32; ++hh) {
-          const int h = hq * 32 + hh;
-          uint32_t raw;
-          asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw) : "r"(tcol + h * 128 + ((tchunk ^ (h & 7)) << 4)));
-          const float2 x = f16x2_to_float2(raw);
-          if (hh == 0) pv = x;
-          const float2 d = __fadd2_rn(x, make_float2(-pv.x, -pv.y));
-          s1 = __fadd2_rn(s1, d);
-          s2 = __ffma2_rn(d, d, s2);
-        }
-        const float mean0 = pv.x + s1.x * (1.0f / 32.0f), mean1 = pv.y + s1.y * (1.0f / 32.0f);
-        const float m20 = fmaxf(s2.x - s1.x * s1.x * (1.0f / 32.0f), 0.f);
-        const float m21 = fmaxf(s2.y - s1.y * s1.y * (1.0f / 32.0f), 0.f);
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(xout + (hq * 128 + 2 * pp) * 8), "f"(mean0),
-                     "f"(m20), "f"(mean1), "f"(m21)
-                     : "memory");
-      }
       named_bar_sync(bar_id, 256);
       // ---- merge the partials of this thread's position (equal-sized groups: mean of means, M2 + n * spread)
       float rs_in, nmr_in, rs_out, nmr_out;
@@ -289,49 +309,51 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       const float2 rs_out2 = make_float2(rs_out, rs_out), nmr_out2 = make_float2(nmr_out, nmr_out);
 
       {
-        const bool got = mbar_wait(acc_full(grp), ph, abort_flag, p.status, kDevTimeoutEpilogue);
+        const bool got = mbar_wait_warp(acc_full(grp), ph, abort_flag, p.status, kDevTimeoutEpilogue);
         if (!named_bar_and(bar_id, 256, got)) break;
       }
       tc_fence_after();
+      // every thread is past its output statistics (barrier above) and the P MMAs are complete: t is dead
+      if (store_thread) mbar_arrive(t_empty(grp));
+      // 8 chunks of 8 channels; the TMEM loads of chunk cc+1 are in flight while chunk cc is finished
+      uint32_t vp[2][8], vg[2][8];
+      tmem_ld8(t_p, vp[0]);
+      tmem_ld8(t_g, vg[0]);
 #pragma unroll
-      for (int c16 = 0; c16 < 4; ++c16) {  // fully unrolled so that zr[] stays in registers
-        uint32_t vp[16], vg[16];
-        tmem_ld16(t_p + c16 * 16, vp);
-        tmem_ld16(t_g + c16 * 16, vg);
+      for (int cc = 0; cc < 8; ++cc) {  // fully unrolled so that zr[] and the two register sets stay in registers
         tmem_ld_wait();
-        if (c16 == 3) {
+        if (cc < 7) {
+          tmem_ld8(t_p + (cc + 1) * 8, vp[(cc + 1) & 1]);
+          tmem_ld8(t_g + (cc + 1) * 8, vg[(cc + 1) & 1]);
+        } else {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty(grp));
         }
+        uint32_t o[4];
+        const uint32_t zz[4] = {zr[cc].x, zr[cc].y, zr[cc].z, zr[cc].w};
 #pragma unroll
-        for (int c8 = 0; c8 < 2; ++c8) {
-          const int cc = c16 * 2 + c8;  // 16-byte chunk inside this thread's 64 channels
-          uint32_t o[4];
-          const uint32_t zz[4] = {zr[cc].x, zr[cc].y, zr[cc].z, zr[cc].w};
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const int pair = half * 32 + cc * 4 + t;  // channel pair index 0..63
-            float4 cg, co;
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                         : "=f"(cg.x), "=f"(cg.y), "=f"(cg.z), "=f"(cg.w)
-                         : "r"(const_base + pair * 32));
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                         : "=f"(co.x), "=f"(co.y), "=f"(co.z), "=f"(co.w)
-                         : "r"(const_base + pair * 32 + 16));
-            const float2 accg = make_float2(__uint_as_float(vg[c8 * 8 + 2 * t]), __uint_as_float(vg[c8 * 8 + 2 * t + 1]));
-            const float2 accp = make_float2(__uint_as_float(vp[c8 * 8 + 2 * t]), __uint_as_float(vp[c8 * 8 + 2 * t + 1]));
-            const float2 g2 = __ffma2_rn(accg, rs_in2, __ffma2_rn(nmr_in2, make_float2(cg.x, cg.y), make_float2(cg.z, cg.w)));
-            const float2 hp = __ffma2_rn(accp, rs_out2, __ffma2_rn(nmr_out2, make_float2(co.x, co.y), make_float2(co.z, co.w)));
-            const float2 th = make_float2(tanh_approx(g2.x), tanh_approx(g2.y));
-            float2 u = __ffma2_rn(th, hp, hp);
-            if (p.residual) u = __fadd2_rn(u, bf16x2_to_float2(zz[t]));
-            o[t] = pack_bf16x2(u);
-          }
-          const uint32_t addr = zrow + ((cc ^ (pos & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                       : "memory");
+        for (int t = 0; t < 4; ++t) {
+          const int pair = half * 32 + cc * 4 + t;  // channel pair index 0..63
+          float4 cg, co;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(cg.x), "=f"(cg.y), "=f"(cg.z), "=f"(cg.w)
+                       : "r"(const_base + pair * 32));
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(co.x), "=f"(co.y), "=f"(co.z), "=f"(co.w)
+                       : "r"(const_base + pair * 32 + 16));
+          const float2 accg = make_float2(__uint_as_float(vg[cc & 1][2 * t]), __uint_as_float(vg[cc & 1][2 * t + 1]));
+          const float2 accp = make_float2(__uint_as_float(vp[cc & 1][2 * t]), __uint_as_float(vp[cc & 1][2 * t + 1]));
+          const float2 g2 = __ffma2_rn(accg, rs_in2, __ffma2_rn(nmr_in2, make_float2(cg.x, cg.y), make_float2(cg.z, cg.w)));
+          const float2 hp = __ffma2_rn(accp, rs_out2, __ffma2_rn(nmr_out2, make_float2(co.x, co.y), make_float2(co.z, co.w)));
+          const float2 th = make_float2(tanh_approx(g2.x), tanh_approx(g2.y));
+          float2 u = __ffma2_rn(th, hp, hp);
+          if (p.residual) u = __fadd2_rn(u, bf16x2_to_float2(zz[t]));
+          o[t] = pack_bf16x2(u);
         }
+        const uint32_t addr = zrow + ((cc ^ (pos & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                     : "memory");
       }
       fence_proxy_async_smem();
       named_bar_sync(bar_id, 256);
@@ -340,7 +362,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
         tma_store_3d(&map_y, zs + 16384, 64, j0, row);
         bulk_commit();
         bulk_wait_read<0>();
-        mbar_arrive(tile_empty(grp));
+        mbar_arrive(z_empty(grp));
       }
     }
     if (store_thread) bulk_wait<0>();

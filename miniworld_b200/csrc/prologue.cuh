@@ -243,7 +243,7 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
         valid = inside && mi != 0u && mj != 0u && mp != 0u;
       }
 
-      const bool got = mbar_wait(z_full(s), ph, abort_flag, p.status, kDevTimeoutStats);
+      const bool got = mbar_wait_warp(z_full(s), ph, abort_flag, p.status, kDevTimeoutStats);
       if (!named_bar_and(2, 256, got)) break;
 
       const uint32_t zs = z_base + s * kProZBytes;
@@ -330,7 +330,7 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int row = tile / p.tiles_per_row;
       const int j0 = (tile - row * p.tiles_per_row) * 128;
-      const bool got = mbar_wait(acc_full(set), it & 1, abort_flag, p.status, kDevTimeoutEpilogue);
+      const bool got = mbar_wait_warp(acc_full(set), it & 1, abort_flag, p.status, kDevTimeoutEpilogue);
       if (!named_bar_and(bar_id, 256, got)) break;
       tc_fence_after();
       const uint32_t ring = ring_base + e * kProRingBytes;

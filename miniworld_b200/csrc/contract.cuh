@@ -28,6 +28,7 @@ struct ContractParams {
   int num_kb;     // 64-deep k blocks
   int a_col_off;  // incoming only: first output row, as a column offset into a's inner dimension
   int n_cols;     // output columns (N)
+  int m_rows;     // output rows of this call
   int* status;
 };
 

@@ -7,6 +7,7 @@
 #include <mutex>
 
 #include "contract.cuh"
+#include "contract_pair.cuh"
 #include "epilogue.cuh"
 #include "prologue.cuh"
 
@@ -230,6 +231,20 @@ static int launch_contract(const CUtensorMap& ma, const CUtensorMap& mb, const C
   return B200_TRIMUL_OK;
 }
 
+template <int BN, bool INCOMING>
+static int launch_contract_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mt,
+                                const ContractParams& p, int sms, cudaStream_t stream) {
+  auto kernel = contract_pair_kernel<BN, INCOMING>;
+  constexpr int smem = PairSmem<BN>::kTotal;
+  int rc = set_smem(kernel, smem);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const long long tiles = static_cast<long long>(p.planes) * p.m_tiles * p.n_tiles;
+  const long long pairs = tiles < sms / 2 ? tiles : sms / 2;
+  kernel<<<static_cast<int>(2 * pairs), kContractThreads, smem, stream>>>(ma, mb, mt, p);  // clusters of two CTAs
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
+}
+
 }  // namespace trimul
 
 using namespace trimul;
@@ -417,7 +432,10 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
   rc = device_info(&info);
   if (rc != B200_TRIMUL_OK) return rc;
   const bool incoming = direction == B200_TRIMUL_INCOMING;
-  const int bn = choose_bn(N);
+  // CTA pairs work on 256-row tiles: used when that pads the rows by at most a quarter.
+  const int pair_rows = (rows + 255) / 256 * 256;
+  const bool use_pair = rows >= 256 && (pair_rows - rows) * 4 <= rows;
+  const int bn = use_pair ? ((N + 255) / 256 * 256 <= (N + 127) / 128 * 128 ? 256 : 128) : choose_bn(N);
   const uint64_t n64 = static_cast<uint64_t>(N);
   const uint64_t row_stride = kC * n64 * 2;  // bytes between consecutive pair rows
   const uint64_t h_stride = n64 * 2;
@@ -435,7 +453,7 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
   {
     const uint64_t dims[4] = {n64, n64, static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
     const uint64_t strides[3] = {row_stride, h_stride, n64 * row_stride};
-    const uint32_t box_out[4] = {64, static_cast<uint32_t>(bn), 1, 1};
+    const uint32_t box_out[4] = {64, static_cast<uint32_t>(use_pair ? bn / 2 : bn), 1, 1};  // a CTA of a pair loads half
     const uint32_t box_in[4] = {64, 64, 1, 1};
     rc = make_map(&map_b, right, 4, dims, strides, incoming ? box_in : box_out);
     if (rc != B200_TRIMUL_OK) return rc;
@@ -450,13 +468,22 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
   ContractParams p;
   p.H = kC;
   p.planes = B * kC;
-  p.m_tiles = (rows + kBM - 1) / kBM;
+  p.m_tiles = use_pair ? pair_rows / 256 : (rows + kBM - 1) / kBM;
+  p.m_rows = rows;
   p.n_tiles = (N + bn - 1) / bn;
   p.num_kb = (N + kBK - 1) / kBK;
   p.a_col_off = incoming ? row_begin : 0;
   p.n_cols = N;
   p.status = status;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (use_pair) {
+    if (!incoming) {
+      if (bn == 256) return launch_contract_pair<256, false>(map_a, map_b, map_t, p, info.sms, stream);
+      return launch_contract_pair<128, false>(map_a, map_b, map_t, p, info.sms, stream);
+    }
+    if (bn == 256) return launch_contract_pair<256, true>(map_a, map_b, map_t, p, info.sms, stream);
+    return launch_contract_pair<128, true>(map_a, map_b, map_t, p, info.sms, stream);
+  }
   if (!incoming) {
     if (bn == 256) return launch_contract<256, false>(map_a, map_b, map_t, p, info.sms, stream);
     if (bn == 192) return launch_contract<192, false>(map_a, map_b, map_t, p, info.sms, stream);

@@ -235,17 +235,19 @@ def trimul_forward(
     workspace: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
     check: bool = False,
+    weights: Optional["_Weights"] = None,
 ) -> torch.Tensor:
     """One module forward on one GPU. ``z`` [B,N,N,128] bf16; ``mask`` Bool[B,N] or None; returns ``out``.
 
     ``workspace`` (uint8, 1024-aligned, at least :func:`workspace_bytes`) is allocated when not given.
-    ``check=True`` synchronises and raises if a device-side wait gave up.
+    ``check=True`` synchronises and raises if a device-side wait gave up. ``weights`` is an already validated
+    :class:`_Weights` of the same parameters (it only holds pointers: the values are packed on the GPU in every call).
     """
     B, N = _check_z(z)
     if z.shape[1] != N:
         raise RuntimeError(f"pair tensor must be square in its token dims, got {tuple(z.shape)}")
     dev = z.device
-    w = _Weights(params, biases, dev)
+    w = weights if weights is not None else _Weights(params, biases, dev)
     need = workspace_bytes(B, N, outgoing)
     if workspace is None:
         workspace = aligned_empty(need, dev)

@@ -109,6 +109,7 @@ class TriangleMultiplication(nn.Module):
         nn.init.zeros_(self.to_out.weight)
         self._biases: Optional[dict] = None
         self._workspace: Optional[torch.Tensor] = None
+        self._wcache = None  # (key, validated parameter pointers); the values themselves are re-read every call
 
     # ------------------------------------------------------------------ dtype handling
     def _apply(self, fn, recurse=True):
@@ -118,6 +119,7 @@ class TriangleMultiplication(nn.Module):
                 if p.dtype != torch.float32:
                     p.data = p.data.to(torch.float32)
         self._workspace = None
+        self._wcache = None
         return self
 
     def set_biases(self, biases: Optional[dict]) -> None:
@@ -126,6 +128,15 @@ class TriangleMultiplication(nn.Module):
         They are not parameters and are not part of the ``state_dict`` (the reference module has none).
         """
         self._biases = None if not biases else dict(biases)
+        self._wcache = None
+
+    def _weights(self, device: torch.device):
+        """Validated parameter pointers, rebuilt only when a parameter tensor was replaced, moved or re-typed."""
+        params = self._params()
+        key = tuple((v.data_ptr(), v.dtype, v.device, v.is_contiguous()) for v in params.values()) + (device,)
+        if self._wcache is None or self._wcache[0] != key:
+            self._wcache = (key, F_._Weights(params, self._biases, device))
+        return self._wcache[1]
 
     def _params(self) -> dict:
         return {
@@ -194,6 +205,7 @@ class TriangleMultiplication(nn.Module):
                 biases=self._biases,
                 workspace=self._get_workspace(B, Np, z.device),
                 check=self.check_status,
+                weights=self._weights(z.device),
             )
         if pad:
             y = y[:, :N, :N].contiguous()

@@ -58,7 +58,7 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
         self.group = group
         self._bufs = None
 
-    def _buffers(self, N: int, rows: int, device: torch.device):
+    def _scratch(self, N: int, rows: int, device: torch.device):
         key = (N, rows, device)
         if self._bufs is None or self._bufs[0] != key:
             plane = lambda r: torch.empty(1, r, D, N, dtype=torch.float16, device=device)  # noqa: E731
@@ -89,7 +89,7 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
             raise RuntimeError(f"rank {rank} of {world} owns {count} rows of N={N}, got {rows}")
         z = pair_rows.detach().to(torch.bfloat16).contiguous()
         dev = z.device
-        b = self._buffers(N, rows, dev)
+        b = self._scratch(N, rows, dev)
         F_.pack_weights(self._params(), b["packed"], self._biases)
         b["status"].zero_()
         has_bias = bool(self._biases) and any(self._biases.get(k) is not None for k in F_.BIAS_ORDER[:4])

@@ -163,3 +163,52 @@ def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
 
 def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
     return float((a.detach().to(torch.float64) - b.detach().to(torch.float64)).abs().max())
+
+
+def trimul_forward_rows(
+    z: torch.Tensor,
+    params: dict,
+    mask: Optional[torch.Tensor],
+    rows,
+    *,
+    outgoing: bool = True,
+    eps_in: float = 1e-5,
+    eps_out: float = 1e-5,
+    residual: bool = True,
+    row_chunk: int = 64,
+) -> torch.Tensor:
+    """Module output for a few pair rows ``rows`` of a large problem (B = 1), fp32, without forming the whole
+    contraction: left/right are built for every cell (O(N^2)) in row chunks, the O(N^3) step only for ``rows``.
+
+    Same arithmetic as :func:`trimul_forward_stages`; used to check the N = 2048 workload at full size.
+    Returns ``[len(rows), N, C]``.
+    """
+    p = {k: v.detach().to(torch.float32) for k, v in params.items()}
+    assert z.shape[0] == 1
+    N, C = z.shape[1], z.shape[3]
+    H = p["to_left.weight"].shape[0]
+    m = None if mask is None else mask[0].to(torch.bool)
+    left = torch.empty(N, N, H, dtype=torch.float32)
+    right = torch.empty(N, N, H, dtype=torch.float32)
+    for r0 in range(0, N, row_chunk):
+        zf = z[0, r0 : r0 + row_chunk].to(torch.float32)
+        x = F.layer_norm(zf, (C,), p["ln_pair.weight"], p["ln_pair.bias"], eps_in)
+        l = torch.sigmoid(x @ p["to_left_gate.weight"].T) * (x @ p["to_left.weight"].T)
+        r = torch.sigmoid(x @ p["to_right_gate.weight"].T) * (x @ p["to_right.weight"].T)
+        if m is not None:
+            v = (m[r0 : r0 + row_chunk, None] & m[None, :])[..., None].to(torch.float32)
+            l, r = l * v, r * v
+        left[r0 : r0 + row_chunk] = l
+        right[r0 : r0 + row_chunk] = r
+    out = []
+    for i in rows:
+        if outgoing:
+            tri = torch.einsum("kd,jkd->jd", left[i], right)  # t[i,j,d] = sum_k left[i,k,d] right[j,k,d]
+        else:
+            tri = torch.einsum("kd,kjd->jd", left[:, i], right)  # t[i,j,d] = sum_k left[k,i,d] right[k,j,d]
+        zf = z[0, i].to(torch.float32)
+        x = F.layer_norm(zf, (C,), p["ln_pair.weight"], p["ln_pair.bias"], eps_in)
+        tn = F.layer_norm(tri, (H,), p["ln_out.weight"], p["ln_out.bias"], eps_out)
+        upd = torch.sigmoid(x @ p["to_gate.weight"].T) * (tn @ p["to_out.weight"].T)
+        out.append(zf + upd if residual else upd)
+    return torch.stack(out)

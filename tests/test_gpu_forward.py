@@ -211,3 +211,43 @@ def test_errors_are_loud():
     zz = torch.zeros(1, 16, 16, 128, dtype=torch.bfloat16, device=DEV, requires_grad=True)
     with pytest.raises(NotImplementedError):
         m(zz, None)
+
+
+def test_large_complex_workload_full_size_rows():
+    """BASELINE workload 4 (B = 1, N = 2048, 4 chains, 5 % of tokens masked) at full size: a sample of pair rows is
+    compared with the oracle (which forms the O(N^3) contraction only for those rows), both directions; plus the
+    size-independent identity that an all-invalid mask returns the input."""
+    w = make_workload("complex2048", seed=0)
+    rows = [0, 511, 512, 1300, 2047]
+    zd, md = w.z.to(DEV), w.mask.to(DEV)
+    for direction in w.directions:
+        outgoing = direction == "outgoing"
+        m = _module(w.params, outgoing)
+        with torch.no_grad():
+            y = m(zd, md)
+        ref = oracle.trimul_forward_rows(w.z, w.params, w.mask, rows, outgoing=outgoing)
+        got = y[0, rows].float().cpu()
+        assert torch.isfinite(y.float()).all()
+        assert_module_parity(got, ref, w.z[0, rows], f"complex2048 {direction} rows")
+        del y
+    p0 = dict(w.params)
+    p0["ln_out.bias"] = torch.zeros(128)
+    m = _module(p0, True)
+    with torch.no_grad():
+        y = m(zd, torch.zeros_like(md))
+    assert torch.equal(y, zd)
+
+
+def test_fp32_workload_is_served_through_bf16():
+    """BASELINE workload 0 (fp32, N = 128, all-ones mask, outgoing) is a CPU configuration of the reference; the
+    module takes the fp32 tensor, rounds it to bf16 once, and returns fp32. Checked against the oracle evaluated on
+    the same rounded input and weights."""
+    w = make_workload("cpu128", seed=0)
+    p16 = {k: (v.to(torch.bfloat16) if k.startswith("to_") else v) for k, v in w.params.items()}
+    z16 = w.z.to(torch.bfloat16)
+    ref = oracle.trimul_forward(z16, p16, w.mask, outgoing=True)
+    m = _module(p16, True)
+    with torch.no_grad():
+        y = m(w.z.to(DEV), w.mask.to(DEV))
+    assert y.dtype == torch.float32
+    assert_module_parity(y, ref, z16, "cpu128")

@@ -25,7 +25,7 @@ NVCC_FLAGS = [
 
 
 def _sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "b200_trimul.h"]
+    return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.inc")) + [PKG_DIR.parent / "include" / "b200_trimul.h"]
 
 
 def is_stale() -> bool:

@@ -370,7 +370,7 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(kC), static_cast<uint64_t>(N), static_cast<uint64_t>(B) * rows};
     const uint64_t strides[2] = {kC * 2ull, static_cast<uint64_t>(N) * kC * 2ull};
-    const uint32_t box[3] = {64, 128, 1};
+    const uint32_t box[3] = {64, 64, 1};  // each CTA of a pair loads 64 of a tile's 128 positions
     rc = make_map(&map_z, z, 3, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
   }
@@ -405,16 +405,17 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
   p.ln_b = p.ln_w + 128;
   p.eps = eps_in;
   p.status = status;
-  const int grid = p.num_tiles < info.sms ? p.num_tiles : info.sms;
+  const int pairs = p.num_tiles < info.sms / 2 ? p.num_tiles : info.sms / 2;
+  const int grid = 2 * pairs;  // clusters of two CTAs: CTA 0 produces `left`, CTA 1 `right`
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (has_bias) {
     rc = set_smem(prologue_kernel<true>, kProSmemBytes);
     if (rc != B200_TRIMUL_OK) return rc;
-    prologue_kernel<true><<<grid, kPrologueThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, p);
+    prologue_kernel<true><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, p);
   } else {
     rc = set_smem(prologue_kernel<false>, kProSmemBytes);
     if (rc != B200_TRIMUL_OK) return rc;
-    prologue_kernel<false><<<grid, kPrologueThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, p);
+    prologue_kernel<false><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, p);
   }
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;

@@ -103,6 +103,17 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
                          int direction, int* status, void* cuda_stream);
 
 /*
+ * Stage 2, partial form for the incoming direction when the pair rows k are spread over several GPUs:
+ * left / right: [B, k_rows, 128, N] fp16, the k_rows pair rows this GPU holds (any contiguous slab of k);
+ * tri_partial: [B, N, 128, N] fp16 = 2^-4 * sum over those k of left[k, :, i] * right[k, :, j] for ALL (i, j).
+ * Summing the partials of all slabs (a reduce-scatter over GPUs) gives the `tri` of b200_trimul_contract.
+ * No reference counterpart: the reference runs this module on one GPU only
+ * (docs/archive/trimul-fusion/inference.md:17 is the single-GPU bmm this replaces).
+ */
+int b200_trimul_contract_partial(const void* left, const void* right, void* tri_partial, int B, int N, int k_rows,
+                                 int* status, void* cuda_stream);
+
+/*
  * Stage 3: output LayerNorm + output projection + sigmoid output gate (+ residual) for `rows` rows.
  * tri: [B, rows, 128, N] fp16 as written by stage 2; z, y: [B, rows, N, 128] bf16. y may alias z.
  */

@@ -421,12 +421,16 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
   return B200_TRIMUL_OK;
 }
 
-int b200_trimul_contract(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
-                         int direction, int* status, void* cuda_stream) {
+// Contraction for output rows row_begin .. row_begin+rows-1. `k_rows` only matters for the incoming direction: the
+// number of pair rows k that left / right hold and the sum runs over (N for the full update, a rank's own rows for a
+// partial sum).
+static int contract_impl(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
+                         int k_rows, int direction, int* status, void* cuda_stream) {
   if (!left || !right || !tri || !status) return B200_TRIMUL_E_NULL;
   int rc = check_bn(B, N);
   if (rc != B200_TRIMUL_OK) return rc;
   if (rows < 1 || row_begin < 0 || row_begin + rows > N) return B200_TRIMUL_E_SHAPE;
+  if (k_rows < 1 || k_rows > N) return B200_TRIMUL_E_SHAPE;
   if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING) return B200_TRIMUL_E_SHAPE;
   if (!aligned(left, 16) || !aligned(right, 16) || !aligned(tri, 16)) return B200_TRIMUL_E_ALIGN;
   DeviceInfo info;
@@ -440,7 +444,8 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
   const uint64_t n64 = static_cast<uint64_t>(N);
   const uint64_t row_stride = kC * n64 * 2;  // bytes between consecutive pair rows
   const uint64_t h_stride = n64 * 2;
-  const uint64_t left_rows = incoming ? n64 : static_cast<uint64_t>(rows);
+  const uint64_t left_rows = incoming ? static_cast<uint64_t>(k_rows) : static_cast<uint64_t>(rows);
+  const uint64_t right_rows = incoming ? static_cast<uint64_t>(k_rows) : n64;
 
   CUtensorMap map_a, map_b, map_t;
   {
@@ -452,8 +457,8 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
     if (rc != B200_TRIMUL_OK) return rc;
   }
   {
-    const uint64_t dims[4] = {n64, n64, static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
-    const uint64_t strides[3] = {row_stride, h_stride, n64 * row_stride};
+    const uint64_t dims[4] = {n64, right_rows, static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
+    const uint64_t strides[3] = {row_stride, h_stride, right_rows * row_stride};
     const uint32_t box_out[4] = {64, static_cast<uint32_t>(use_pair ? bn / 2 : bn), 1, 1};  // a CTA of a pair loads half
     const uint32_t box_in[4] = {64, 64, 1, 1};
     rc = make_map(&map_b, right, 4, dims, strides, incoming ? box_in : box_out);
@@ -472,7 +477,7 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
   p.m_tiles = use_pair ? pair_rows / 256 : (rows + kBM - 1) / kBM;
   p.m_rows = rows;
   p.n_tiles = (N + bn - 1) / bn;
-  p.num_kb = (N + kBK - 1) / kBK;
+  p.num_kb = ((incoming ? k_rows : N) + kBK - 1) / kBK;  // rows past k_rows read as zero (TMA out-of-bounds fill)
   p.a_col_off = incoming ? row_begin : 0;
   p.n_cols = N;
   p.status = status;
@@ -493,6 +498,16 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
   if (bn == 256) return launch_contract<256, true>(map_a, map_b, map_t, p, info.sms, stream);
   if (bn == 192) return launch_contract<192, true>(map_a, map_b, map_t, p, info.sms, stream);
   return launch_contract<128, true>(map_a, map_b, map_t, p, info.sms, stream);
+}
+
+int b200_trimul_contract(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
+                         int direction, int* status, void* cuda_stream) {
+  return contract_impl(left, right, tri, B, N, row_begin, rows, N, direction, status, cuda_stream);
+}
+
+int b200_trimul_contract_partial(const void* left, const void* right, void* tri_partial, int B, int N, int k_rows,
+                                 int* status, void* cuda_stream) {
+  return contract_impl(left, right, tri_partial, B, N, 0, N, k_rows, B200_TRIMUL_INCOMING, status, cuda_stream);
 }
 
 int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows,

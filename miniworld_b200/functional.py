@@ -186,6 +186,18 @@ def contract(
     _lib.check(rc, "b200_trimul_contract")
 
 
+def contract_partial(
+    left: torch.Tensor, right: torch.Tensor, tri_partial: torch.Tensor, status: torch.Tensor, B: int, N: int, k_rows: int
+) -> None:
+    """Incoming-direction partial sum over the ``k_rows`` pair rows held in ``left`` / ``right`` ([B, k_rows, 128, N]):
+    ``tri_partial`` [B, N, 128, N] covers every (i, j); the partials of all row slabs add up to the full ``tri``."""
+    with torch.cuda.device(tri_partial.device):
+        rc = _lib.load().b200_trimul_contract_partial(
+            _ptr(left), _ptr(right), _ptr(tri_partial), B, N, k_rows, _ptr(status), _stream(tri_partial.device)
+        )
+    _lib.check(rc, "b200_trimul_contract_partial")
+
+
 def epilogue(
     tri: torch.Tensor,
     z: torch.Tensor,

@@ -7,9 +7,14 @@ Two schemes, neither present in the reference (it only has data-parallel trainin
   contracted operand(s), which are all-gathered into local HBM (NCCL) and then read by local TMA loads; no
   kernel ever loads from a peer's memory.
     outgoing  t[i in I_r, j] = sum_k a[i,k] b[j,k]     -> all-gather of ``right`` (rows j)
-    incoming  t[i in I_r, j] = sum_k a[k,i] b[k,j]     -> all-gather of ``left`` and ``right`` (rows k);
-                                                           the rank uses columns I_r of ``left``
-  The row-plane layout [rows, H, N] makes the gathered tensor [P, N/P, H, N] == [N, H, N] with no repacking.
+    incoming  t[i, j] = sum_r sum_{k in I_r} a[k,i] b[k,j] -> every rank sums over the rows k it owns, for ALL
+                                                           (i, j), and a reduce-scatter over i adds the partial
+                                                           sums (one tensor crosses the links instead of two).
+                                                           ``incoming="gather"`` selects the older scheme, an
+                                                           all-gather of ``left`` and ``right`` (rows k), which is
+                                                           bit-identical to the single-GPU forward.
+  The row-plane layout [rows, H, N] makes the gathered tensor [P, N/P, H, N] == [N, H, N] with no repacking, and
+  the partial-sum tensor [N, H, N] splits into the ranks' row blocks the same way.
 * :func:`shard_batch` - plain batch data parallelism for B > 1: samples are independent, no collective.
 """
 
@@ -53,22 +58,28 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
     ``rank*N/P ...`` of ``pair + update``. Every rank must call it (it contains a collective).
     """
 
-    def __init__(self, d_pair: int = D, d_hidden: Optional[int] = None, outgoing: bool = True, group=None, **kw):
+    def __init__(self, d_pair: int = D, d_hidden: Optional[int] = None, outgoing: bool = True, group=None,
+                 incoming: str = "reduce", **kw):
         super().__init__(d_pair, d_hidden, outgoing=outgoing, **kw)
+        if incoming not in ("reduce", "gather"):
+            raise ValueError(f"incoming must be 'reduce' or 'gather', got {incoming!r}")
         self.group = group
+        self.incoming_scheme = incoming
         self._bufs = None
 
     def _scratch(self, N: int, rows: int, device: torch.device):
         key = (N, rows, device)
         if self._bufs is None or self._bufs[0] != key:
             plane = lambda r: torch.empty(1, r, D, N, dtype=torch.float16, device=device)  # noqa: E731
+            gather = self.outgoing or self.incoming_scheme == "gather"
             bufs = dict(
                 packed=F_.aligned_empty(F_.packed_bytes(), device),
                 status=torch.zeros(16, dtype=torch.int32, device=device),
                 left=plane(rows),
                 right=plane(rows),
-                right_all=plane(N),
-                left_all=None if self.outgoing else plane(N),
+                right_all=plane(N) if gather else None,
+                left_all=plane(N) if gather and not self.outgoing else None,
+                tri_partial=None if gather else plane(N),
                 tri=plane(rows),
             )
             self._bufs = (key, bufs)
@@ -96,12 +107,18 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
         F_.prologue(z, b["packed"], b["left"], b["right"], b["status"], token_mask=mask, row_begin=begin,
                     eps_in=float(self.ln_pair.eps), has_bias=has_bias)
         # B = 1: gather on [rows, 128, N] views so that the rank-major concatenation is the row dimension
-        dist.all_gather_into_tensor(b["right_all"].view(N, D, N), b["right"].view(rows, D, N), group=self.group)
         if self.outgoing:
+            dist.all_gather_into_tensor(b["right_all"].view(N, D, N), b["right"].view(rows, D, N), group=self.group)
             F_.contract(b["left"], b["right_all"], b["tri"], b["status"], 1, N, begin, rows, True)
-        else:
+        elif self.incoming_scheme == "gather":
+            dist.all_gather_into_tensor(b["right_all"].view(N, D, N), b["right"].view(rows, D, N), group=self.group)
             dist.all_gather_into_tensor(b["left_all"].view(N, D, N), b["left"].view(rows, D, N), group=self.group)
             F_.contract(b["left_all"], b["right_all"], b["tri"], b["status"], 1, N, begin, rows, False)
+        else:
+            # partial sum over this rank's rows k for every (i, j), then the ranks' partials are added row block
+            # by row block (fp16 sums of values already scaled by 2^-4)
+            F_.contract_partial(b["left"], b["right"], b["tri_partial"], b["status"], 1, N, rows)
+            dist.reduce_scatter_tensor(b["tri"].view(rows, D, N), b["tri_partial"].view(N, D, N), group=self.group)
         y = torch.empty_like(z)
         F_.epilogue(b["tri"], z, b["packed"], y, b["status"], eps_in=float(self.ln_pair.eps),
                     eps_out=float(self.ln_out.eps), residual=self.residual)

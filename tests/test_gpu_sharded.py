@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, outgoing, N, ret):
+def _worker(rank, world, port, outgoing, incoming, N, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -41,7 +41,7 @@ def _worker(rank, world, port, outgoing, N, ret):
         full = mw.TriangleMultiplication(128, outgoing=outgoing, check_status=True)
         full.load_state_dict(p)
         full = full.to(dev).to(torch.bfloat16).eval()
-        shard = sharded.RowShardedTriangleMultiplication(128, outgoing=outgoing, check_status=True)
+        shard = sharded.RowShardedTriangleMultiplication(128, outgoing=outgoing, incoming=incoming, check_status=True)
         shard.load_state_dict(p)
         shard = shard.to(dev).to(torch.bfloat16).eval()
         with torch.no_grad():
@@ -54,16 +54,20 @@ def _worker(rank, world, port, outgoing, N, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("outgoing", [True, False])
-def test_row_sharded_equals_single_gpu(outgoing):
+@pytest.mark.parametrize("outgoing,incoming", [(True, "reduce"), (False, "gather"), (False, "reduce")])
+def test_row_sharded_equals_single_gpu(outgoing, incoming):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world, N = 2, 256
     port = _free_port()
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(world, port, outgoing, N, ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, outgoing, incoming, N, ret), nprocs=world, join=True)
         assert len(ret) == world
         for rank, (same, err) in ret.items():
-            # same kernels, same k order: the rows a rank computes are bit-identical to the unsharded forward
-            assert same, (rank, err)
+            if outgoing or incoming == "gather":
+                # same kernels, same k order: the rows a rank computes are bit-identical to the unsharded forward
+                assert same, (rank, err)
+            else:
+                # partial sums rounded to fp16 per rank: a few bf16 output roundings may differ
+                assert err <= 0.0625, (rank, err)

@@ -113,6 +113,35 @@ def test_contract_row_range(outgoing):
     assert torch.equal(part, full[:, r0 : r0 + rows])
 
 
+@pytest.mark.parametrize("N,slabs", [(192, [(0, 96), (96, 96)]), (200, [(0, 72), (72, 40), (112, 88)]), (384, [(0, 384)])])
+def test_contract_partial_sums_to_full(N, slabs):
+    """Incoming partial sums over slabs of the pair rows k (what the ranks of a k-sharded run compute) add up to the
+    full contraction; a single slab covering every k is bit-identical to it."""
+    B = 1
+    g = torch.Generator().manual_seed(11 + N)
+    left = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    right = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    st = _status()
+    full = _nan_f16(B, N, 128, N)
+    F_.contract(left, right, full, st, B, N, 0, N, False)
+    acc = torch.zeros(B, N, 128, N, dtype=torch.float32, device=DEV)
+    for k0, kr in slabs:
+        part = _nan_f16(B, N, 128, N)
+        F_.contract_partial(left[:, k0 : k0 + kr].contiguous(), right[:, k0 : k0 + kr].contiguous(), part, st, B, N, kr)
+        assert torch.isfinite(part.float()).all()
+        ref = torch.einsum("bkhi,bkhj->bihj", left[:, k0 : k0 + kr].float(), right[:, k0 : k0 + kr].float())
+        err = (part.float() / TRI_SCALE - ref).abs()
+        tol = ref.abs() * 2**-10 + 2e-3
+        assert bool((err <= tol).all()), float((err - tol).max())
+        acc += part.float()
+    F_.check_status(st, "contract_partial")
+    if len(slabs) == 1:
+        assert torch.equal(part, full)
+    else:
+        rel = oracle.rel_frobenius(acc.cpu(), full.float().cpu())
+        assert rel < 6e-4, rel  # one fp16 rounding per slab
+
+
 @pytest.mark.parametrize("mask_kind", ["none", "tail", "holes", "all_invalid", "pair"])
 @pytest.mark.parametrize("B,N", [(1, 16), (2, 40), (1, 128), (1, 200)])
 def test_prologue_matches_oracle(B, N, mask_kind):

@@ -106,7 +106,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _row_sharded_worker(rank, world, port, outgoing, ret):
+def _row_sharded_worker(rank, world, port, scheme, ret):
+    outgoing = scheme == "outgoing"
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -118,15 +119,21 @@ def _row_sharded_worker(rank, world, port, outgoing, ret):
         mask = torch.rand(1, N, generator=g) > 0.2
         begin, rows = sharded.row_range(N, world, rank)
         # the schedule of RowShardedTriangleMultiplication.forward with the oracle's stages standing in for
-        # the three kernels: local prologue -> all-gather of the contracted operand(s) -> local contraction
+        # the three kernels: local prologue -> all-gather of the contracted operand(s) -> local contraction, or
+        # (incoming, "reduce") local partial contraction over the rank's rows k -> reduce-scatter over i
         full = oracle.trimul_forward_stages(z, p, mask, outgoing=outgoing)
         left_loc = full.left[:, begin : begin + rows].permute(0, 1, 3, 2).contiguous()   # row-plane [1, rows, H, N]
         right_loc = full.right[:, begin : begin + rows].permute(0, 1, 3, 2).contiguous()
         right_all = torch.empty(1, N, 128, N)
-        dist.all_gather_into_tensor(right_all.view(N, 128, N), right_loc.view(rows, 128, N))
-        if outgoing:
+        if scheme == "incoming_reduce":
+            partial = torch.einsum("bkhi,bkhj->bihj", left_loc, right_loc).contiguous()  # all (i, j), own k
+            tri = torch.empty(1, rows, 128, N)
+            dist.reduce_scatter_tensor(tri.view(rows, 128, N), partial.view(N, 128, N))
+        elif outgoing:
+            dist.all_gather_into_tensor(right_all.view(N, 128, N), right_loc.view(rows, 128, N))
             tri = torch.einsum("bihk,bjhk->bihj", left_loc, right_all)
         else:
+            dist.all_gather_into_tensor(right_all.view(N, 128, N), right_loc.view(rows, 128, N))
             left_all = torch.empty(1, N, 128, N)
             dist.all_gather_into_tensor(left_all.view(N, 128, N), left_loc.view(rows, 128, N))
             tri = torch.einsum("bkhi,bkhj->bihj", left_all[..., begin : begin + rows], right_all)
@@ -136,13 +143,14 @@ def _row_sharded_worker(rank, world, port, outgoing, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("outgoing", [True, False])
-def test_row_sharded_schedule_on_two_gloo_ranks(outgoing):
-    """The gathered row-plane tensor is the full operand with no repacking, and each rank's rows of the
-    contraction equal the unsharded result (world_size 2, gloo, CPU)."""
+@pytest.mark.parametrize("scheme", ["outgoing", "incoming_gather", "incoming_reduce"])
+def test_row_sharded_schedule_on_two_gloo_ranks(scheme):
+    """The gathered row-plane tensor is the full operand with no repacking, the partial-sum tensor splits into the
+    ranks' row blocks the same way, and each rank's rows of the contraction equal the unsharded result
+    (world_size 2, gloo, CPU)."""
     world = 2
     port = _free_port()
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_row_sharded_worker, args=(world, port, outgoing, ret), nprocs=world, join=True)
+        mp.spawn(_row_sharded_worker, args=(world, port, scheme, ret), nprocs=world, join=True)
         assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)

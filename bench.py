@@ -388,13 +388,18 @@ def run_b200(args):
             "config": {"workload": args.workload, "B": B, "N": N, "d_pair": 128, "d_hidden": 128,
                        "step": "outgoing forward + incoming forward (2 module forwards)",
                        "cells_per_step": cells_per_step,
-                       "parallelism": "single GPU" if world == 1 else f"row-sharded over {world} GPUs, NCCL all-gather",
+                       "parallelism": "single GPU" if world == 1 else (
+                           f"row-sharded over {world} GPUs, transport {mods['outgoing'].transport}: outgoing = prologue "
+                           "writes `right` into every GPU's copy, incoming = partial sums over the local rows k + "
+                           "reduce over the ranks"),
                        "l2": "inputs and intermediates (604 MB at N=768) exceed the 126 MB L2; no flush"},
             "e2e": {"value": cells_per_step / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "pinned host z -> device, two module forwards, y -> pinned host, every step; two device "
                            "input buffers so copies overlap the neighbouring steps' kernels"},
-            "gpu_launches": 8 * args.steps,
+            # this repository's kernels per step: (pack, prologue, contraction, epilogue) x 2 directions, plus the
+            # peer-reading reduce kernel of the incoming direction on the p2p transport
+            "gpu_launches": (9 if world > 1 and mods["outgoing"].transport == "p2p" else 8) * args.steps,
             "clocks": clocks,
         }
         if stages_ms is not None:

@@ -114,6 +114,27 @@ int b200_trimul_contract_partial(const void* left, const void* right, void* tri_
                                  int* status, void* cuda_stream);
 
 /*
+ * Multi-GPU forms (pair rows spread over the GPUs of one node, B = 1). No reference counterpart: the reference
+ * runs this module on one GPU only; these replace the NCCL all-gather / reduce-scatter a row-sharded run would
+ * otherwise place between the stages.
+ *
+ * b200_trimul_prologue_push: stage 1 for this GPU's rows, with `right` written straight into the gathered copies
+ * [N, 128, N] fp16 of every GPU: `right_all` is this GPU's copy, right_all_peers[0 .. n_peers-1] (n_peers <= 7)
+ * are the other GPUs' copies mapped into this process (peer memory). Local row r lands at row row_begin + r.
+ * `left` stays local, [rows, 128, N]. The peers may read their copy once this call's kernel has completed on this
+ * GPU and they have been told so (a stream-ordered collective, an event): the caller provides that ordering.
+ *
+ * b200_trimul_reduce_partials: tri[rows, 128, N] = sum over s of partials[s][row_begin .. row_begin+rows-1], where
+ * partials[s] (s < n_src <= 8) is the [N, 128, N] fp16 output of b200_trimul_contract_partial on GPU s (local or
+ * peer memory). fp32 sums in the order given, one saturating fp16 rounding.
+ */
+int b200_trimul_prologue_push(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
+                              void* left, void* right_all, void* const* right_all_peers, int n_peers, int N,
+                              int row_begin, int rows, float eps_in, int has_bias, int* status, void* cuda_stream);
+int b200_trimul_reduce_partials(void* tri, const void* const* partials, int n_src, int N, int row_begin, int rows,
+                                void* cuda_stream);
+
+/*
  * Stage 3: output LayerNorm + output projection + sigmoid output gate (+ residual) for `rows` rows.
  * tri: [B, rows, 128, N] fp16 as written by stage 2; z, y: [B, rows, N, 128] bf16. y may alias z.
  */

@@ -40,6 +40,14 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     ),
+    "b200_trimul_prologue_push": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    ),
+    "b200_trimul_reduce_partials": (
+        c_int,
+        [c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p],
+    ),
     "b200_trimul_epilogue": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],

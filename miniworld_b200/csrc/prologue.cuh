@@ -58,6 +58,17 @@ struct PrologueParams {
   const float* ln_b;          // [128] LayerNorm beta
   float eps;
   int* status;
+  int right_row_shift;  // added to the row coordinate of every store of `right` (see PushMaps)
+};
+
+// Extra destinations of `right`, used when the pair rows are spread over several GPUs: each map describes a
+// whole [N rows][128][N] buffer - this GPU's own gathered copy is `map_r`, the others are the peers' copies in
+// their memory - and a tile of local row r lands at row r + right_row_shift in every one of them. The stores are
+// plain (non-multicast) TMA stores; over NVLink they replace a separate all-gather pass.
+constexpr int kMaxPush = 7;
+struct PushMaps {
+  CUtensorMap m[kMaxPush];
+  int count;
 };
 
 constexpr int kProThreads = 864;
@@ -74,8 +85,8 @@ constexpr int kProSmemBytes =
 template <bool HAS_BIAS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kProThreads, 1)
 prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_w,
-                     const __grid_constant__ CUtensorMap map_l, const __grid_constant__ CUtensorMap map_r,
-                     const PrologueParams p) {
+                const __grid_constant__ CUtensorMap map_l, const __grid_constant__ CUtensorMap map_r,
+                     const __grid_constant__ PushMaps push, const PrologueParams p) {
   constexpr int S = kProStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;

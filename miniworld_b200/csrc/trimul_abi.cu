@@ -118,6 +118,50 @@ __global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* pa
   }
 }
 
+// Sum of the incoming-direction partial results of several GPUs for the rows one GPU owns:
+// tri[e] = sum_s src[s][e] over `count` 16-byte groups of eight fp16 values, fp32 accumulation in source order,
+// one saturating rounding. Sources may be peer memory: they are read with plain 16-byte loads.
+constexpr int kMaxReduceSrc = 8;
+struct ReduceSrc {
+  const uint4* p[kMaxReduceSrc];
+  int n;
+};
+
+__device__ __forceinline__ uint32_t pack_sat(float a, float b) {
+  return pack_f16x2(make_float2(fminf(fmaxf(a, -65504.f), 65504.f), fminf(fmaxf(b, -65504.f), 65504.f)));
+}
+
+__global__ void __launch_bounds__(512) reduce_partials_kernel(const ReduceSrc src, uint4* __restrict__ tri, size_t count) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t e = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < count; e += stride) {
+    float acc[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) acc[t] = 0.f;
+    uint4 v[kMaxReduceSrc];
+#pragma unroll
+    for (int s = 0; s < kMaxReduceSrc; ++s)
+      if (s < src.n) v[s] = src.p[s][e];  // all loads in flight before the first use
+#pragma unroll
+    for (int s = 0; s < kMaxReduceSrc; ++s) {
+      if (s < src.n) {
+        const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = f16x2_to_float2(w[t]);
+          acc[2 * t] += f.x;
+          acc[2 * t + 1] += f.y;
+        }
+      }
+    }
+    uint4 o;
+    o.x = pack_sat(acc[0], acc[1]);
+    o.y = pack_sat(acc[2], acc[3]);
+    o.z = pack_sat(acc[4], acc[5]);
+    o.w = pack_sat(acc[6], acc[7]);
+    tri[e] = o;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host helpers
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -354,10 +398,14 @@ int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const 
   return B200_TRIMUL_OK;
 }
 
-int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
-                         void* left, void* right, int B, int N, int row_begin, int rows, float eps_in, int has_bias,
-                         int* status, void* cuda_stream) {
+// `right` is [B, rows, 128, N] when n_push < 0. Otherwise (B = 1) it is this GPU's gathered copy [N, 128, N] and
+// push_dst[0 .. n_push-1] are the other GPUs' copies: local row r is written to row row_begin + r of each.
+static int prologue_impl(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
+                         void* left, void* right, void* const* push_dst, int n_push, int B, int N, int row_begin,
+                         int rows, float eps_in, int has_bias, int* status, void* cuda_stream) {
   if (!z || !packed || !left || !right || !status) return B200_TRIMUL_E_NULL;
+  const bool gathered = n_push >= 0;
+  if (gathered && (B != 1 || n_push > kMaxPush || (n_push > 0 && !push_dst))) return B200_TRIMUL_E_SHAPE;
   int rc = check_bn(B, N);
   if (rc != B200_TRIMUL_OK) return rc;
   if (rows < 1 || row_begin < 0 || row_begin + rows > N) return B200_TRIMUL_E_SHAPE;
@@ -367,6 +415,8 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
   if (rc != B200_TRIMUL_OK) return rc;
 
   CUtensorMap map_z, map_w, map_l, map_r;
+  PushMaps push;
+  push.count = gathered ? n_push : 0;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(kC), static_cast<uint64_t>(N), static_cast<uint64_t>(B) * rows};
     const uint64_t strides[2] = {kC * 2ull, static_cast<uint64_t>(N) * kC * 2ull};
@@ -381,8 +431,15 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
     const uint32_t box[3] = {64, 128, 1};
     rc = make_map(&map_l, left, 3, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
-    rc = make_map(&map_r, right, 3, dims, strides, box);
+    const uint64_t dims_all[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(kC), static_cast<uint64_t>(N)};
+    rc = make_map(&map_r, right, 3, gathered ? dims_all : dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
+    for (int d = 0; d < (gathered ? n_push : 0); ++d) {
+      if (!push_dst[d]) return B200_TRIMUL_E_NULL;
+      if (!aligned(push_dst[d], 16)) return B200_TRIMUL_E_ALIGN;
+      rc = make_map(&push.m[d], push_dst[d], 3, dims_all, strides, box);
+      if (rc != B200_TRIMUL_OK) return rc;
+    }
   }
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(kC), 6ull * 128};
@@ -405,20 +462,36 @@ int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token
   p.ln_b = p.ln_w + 128;
   p.eps = eps_in;
   p.status = status;
+  p.right_row_shift = gathered ? row_begin : 0;
   const int pairs = p.num_tiles < info.sms / 2 ? p.num_tiles : info.sms / 2;
   const int grid = 2 * pairs;  // clusters of two CTAs: CTA 0 produces `left`, CTA 1 `right`
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (has_bias) {
     rc = set_smem(prologue_kernel<true>, kProSmemBytes);
     if (rc != B200_TRIMUL_OK) return rc;
-    prologue_kernel<true><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, p);
+    prologue_kernel<true><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, push, p);
   } else {
     rc = set_smem(prologue_kernel<false>, kProSmemBytes);
     if (rc != B200_TRIMUL_OK) return rc;
-    prologue_kernel<false><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, p);
+    prologue_kernel<false><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, push, p);
   }
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
+}
+
+int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
+                         void* left, void* right, int B, int N, int row_begin, int rows, float eps_in, int has_bias,
+                         int* status, void* cuda_stream) {
+  return prologue_impl(z, packed, token_mask, pair_mask, left, right, nullptr, -1, B, N, row_begin, rows, eps_in,
+                       has_bias, status, cuda_stream);
+}
+
+int b200_trimul_prologue_push(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
+                              void* left, void* right_all, void* const* right_all_peers, int n_peers, int N,
+                              int row_begin, int rows, float eps_in, int has_bias, int* status, void* cuda_stream) {
+  if (n_peers < 0) return B200_TRIMUL_E_SHAPE;
+  return prologue_impl(z, packed, token_mask, pair_mask, left, right_all, right_all_peers, n_peers, 1, N, row_begin,
+                       rows, eps_in, has_bias, status, cuda_stream);
 }
 
 // Contraction for output rows row_begin .. row_begin+rows-1. `k_rows` only matters for the incoming direction: the
@@ -508,6 +581,36 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
 int b200_trimul_contract_partial(const void* left, const void* right, void* tri_partial, int B, int N, int k_rows,
                                  int* status, void* cuda_stream) {
   return contract_impl(left, right, tri_partial, B, N, 0, N, k_rows, B200_TRIMUL_INCOMING, status, cuda_stream);
+}
+
+int b200_trimul_reduce_partials(void* tri, const void* const* partials, int n_src, int N, int row_begin, int rows,
+                                void* cuda_stream) {
+  if (!tri || !partials) return B200_TRIMUL_E_NULL;
+  if (n_src < 1 || n_src > kMaxReduceSrc) return B200_TRIMUL_E_SHAPE;
+  int rc = check_bn(1, N);
+  if (rc != B200_TRIMUL_OK) return rc;
+  if (rows < 1 || row_begin < 0 || row_begin + rows > N) return B200_TRIMUL_E_SHAPE;
+  if (!aligned(tri, 16)) return B200_TRIMUL_E_ALIGN;
+  DeviceInfo info;
+  rc = device_info(&info);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const size_t row_bytes = static_cast<size_t>(kC) * N * 2;  // a multiple of 16: N is a multiple of 8
+  ReduceSrc src;
+  src.n = n_src;
+  for (int s = 0; s < kMaxReduceSrc; ++s) {
+    if (s < n_src) {
+      if (!partials[s]) return B200_TRIMUL_E_NULL;
+      if (!aligned(partials[s], 16)) return B200_TRIMUL_E_ALIGN;
+      src.p[s] = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(partials[s]) + row_bytes * row_begin);
+    } else {
+      src.p[s] = nullptr;
+    }
+  }
+  const size_t count = row_bytes * rows / 16;
+  const int grid = info.sms * 4;
+  reduce_partials_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(cuda_stream)>>>(src, static_cast<uint4*>(tri), count);
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
 }
 
 int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows,

@@ -167,6 +167,50 @@ def prologue(
     _lib.check(rc, "b200_trimul_prologue")
 
 
+def _ptr_array(tensors):
+    arr = (ctypes.c_void_p * max(len(tensors), 1))()
+    for i, t in enumerate(tensors):
+        arr[i] = t.data_ptr()
+    return arr
+
+
+def prologue_push(
+    z: torch.Tensor,
+    packed: torch.Tensor,
+    left: torch.Tensor,
+    right_all: torch.Tensor,
+    right_all_peers: list,
+    status: torch.Tensor,
+    token_mask: Optional[torch.Tensor] = None,
+    row_begin: int = 0,
+    eps_in: float = 1e-5,
+    has_bias: bool = False,
+) -> None:
+    """Stage 1 for the rows ``z`` [1, rows, N, 128] of one GPU of a row-sharded run: ``left`` [1, rows, 128, N] stays
+    local, ``right`` goes to rows row_begin.. of ``right_all`` [1, N, 128, N] and of every tensor in
+    ``right_all_peers`` (the other GPUs' gathered copies, mapped into this process)."""
+    B, N = _check_z(z)
+    if B != 1:
+        raise RuntimeError("prologue_push is the row-sharded form: B must be 1")
+    rows = int(z.shape[1])
+    tm = as_mask_u8(token_mask, z.device)
+    peers = _ptr_array(right_all_peers)
+    with torch.cuda.device(z.device):
+        rc = _lib.load().b200_trimul_prologue_push(
+            _ptr(z), _ptr(packed), _ptr(tm), None, _ptr(left), _ptr(right_all), peers, len(right_all_peers), N, row_begin,
+            rows, float(eps_in), int(bool(has_bias)), _ptr(status), _stream(z.device),
+        )
+    _lib.check(rc, "b200_trimul_prologue_push")
+
+
+def reduce_partials(tri: torch.Tensor, partials: list, N: int, row_begin: int, rows: int) -> None:
+    """``tri`` [1, rows, 128, N] = sum of rows row_begin.. of every ``partials[s]`` [1, N, 128, N] (local or peer memory)."""
+    srcs = _ptr_array(partials)
+    with torch.cuda.device(tri.device):
+        rc = _lib.load().b200_trimul_reduce_partials(_ptr(tri), srcs, len(partials), N, row_begin, rows, _stream(tri.device))
+    _lib.check(rc, "b200_trimul_reduce_partials")
+
+
 def contract(
     left: torch.Tensor,
     right: torch.Tensor,

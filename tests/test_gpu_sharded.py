@@ -1,6 +1,8 @@
-"""Row-sharded forward on two GPUs (NCCL) against the single-GPU forward. Skipped with fewer than two GPUs.
+"""Row-sharded forward on two GPUs against the single-GPU forward, with both transports: NCCL collectives between
+the kernels, and the kernels storing to / loading from the peer GPU's memory. Skipped with fewer than two GPUs.
 
-Child processes, one per GPU; NVLS is switched off for the library and the kernels only read local memory.
+Child processes, one per GPU; NVLS is switched off for the library, the peer accesses are plain (non-multicast)
+TMA stores and 16-byte loads, and no kernel waits on another GPU.
 """
 
 import os
@@ -22,7 +24,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, outgoing, incoming, N, ret):
+def _worker(rank, world, port, outgoing, incoming, transport, N, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -41,28 +43,34 @@ def _worker(rank, world, port, outgoing, incoming, N, ret):
         full = mw.TriangleMultiplication(128, outgoing=outgoing, check_status=True)
         full.load_state_dict(p)
         full = full.to(dev).to(torch.bfloat16).eval()
-        shard = sharded.RowShardedTriangleMultiplication(128, outgoing=outgoing, incoming=incoming, check_status=True)
+        shard = sharded.RowShardedTriangleMultiplication(128, outgoing=outgoing, incoming=incoming, transport=transport,
+                                                         check_status=True)
         shard.load_state_dict(p)
         shard = shard.to(dev).to(torch.bfloat16).eval()
         with torch.no_grad():
             want = full(z.to(dev), mask.to(dev))[:, begin : begin + rows]
-            for _ in range(2):  # second call reuses the buffers
+            for _ in range(3):  # later calls reuse the buffers (the p2p transport alternates between two)
                 got = shard(z[:, begin : begin + rows].contiguous().to(dev), mask.to(dev))
+        assert shard.transport == transport
         torch.cuda.synchronize()
         ret[rank] = (bool(torch.equal(got, want)), float((got.float() - want.float()).abs().max()))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("outgoing,incoming", [(True, "reduce"), (False, "gather"), (False, "reduce")])
-def test_row_sharded_equals_single_gpu(outgoing, incoming):
+@pytest.mark.parametrize(
+    "outgoing,incoming,transport",
+    [(True, "reduce", "nccl"), (False, "gather", "nccl"), (False, "reduce", "nccl"), (True, "reduce", "p2p"),
+     (False, "reduce", "p2p")],
+)
+def test_row_sharded_equals_single_gpu(outgoing, incoming, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world, N = 2, 256
     port = _free_port()
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(world, port, outgoing, incoming, N, ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, outgoing, incoming, transport, N, ret), nprocs=world, join=True)
         assert len(ret) == world
         for rank, (same, err) in ret.items():
             if outgoing or incoming == "gather":

@@ -355,10 +355,13 @@ def run_b200(args):
         achieved = fl["contraction"] / (t_contract * 1e-3) / 1e12
         P = synthetic.pass_bytes(B, N)
         roofline = {
-            "kernel": "contract_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+            "kernel": "contract_pair_kernel" if N >= 256 else "contract_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
             "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
             "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
-            "flops_per_launch": fl["contraction"], "traffic": None,
+            "flops_per_launch": fl["contraction"],
+            # dram__bytes_read.sum + dram__bytes_write.sum of one contraction launch, from the ncu capture of this
+            # workload summarised under profiles/; not captured for the other workloads
+            "traffic": 422.9e6 if args.workload == "crop768" else None,
             "timed": "separate loop of K steps, CUDA events around each stage on the launching stream",
             "other_kernels": {
                 "prologue_kernel": {"bound": "hbm", "algorithmic_bytes": 3 * P,

@@ -135,6 +135,29 @@ int b200_trimul_reduce_partials(void* tri, const void* const* partials, int n_sr
                                 void* cuda_stream);
 
 /*
+ * Channel-sharded multi-GPU form (B = 1, P GPUs, P divides 128, N/P a multiple of 32, N >= 256): GPU g contracts
+ * the 128/P channels of group g for ALL rows, so each GPU sends 1/P of its operands and receives 1/P of the result
+ * instead of (P-1)/P of an operand. No reference counterpart (single-GPU module). The three stages store directly
+ * into the destination GPUs' buffers (plain TMA stores; peer memory mapped into the calling process for the other
+ * GPUs); the caller orders stage s on all GPUs before stage s+1 on any (stream-ordered collective or events).
+ *
+ * b200_trimul_prologue_channels: stage 1 for this GPU's rows row_begin .. row_begin+rows-1. left_groups[g] /
+ *   right_groups[g] (g < groups = P): GPU g's operand buffers [N, 128/P, N] fp16; this call fills rows row_begin.. .
+ * b200_trimul_contract_channels: stage 2 on GPU `group`: left_group / right_group are its [N, 128/P, N] buffers,
+ *   complete once every GPU's stage 1 has finished. tri_owners[s] (s < groups): GPU s's buffer
+ *   [P, N/P, 128/P, N] fp16; rows s*N/P .. of the result go to slab `group` of tri_owners[s].
+ * b200_trimul_epilogue_groups: stage 3 for this GPU's rows; tri_groups is its [P, rows, 128/P, N] buffer, complete
+ *   once every GPU's stage 2 has finished; z / y: [rows, N, 128] bf16.
+ */
+int b200_trimul_prologue_channels(const void* z, const void* packed, const uint8_t* token_mask, void* const* left_groups,
+                                  void* const* right_groups, int groups, int N, int row_begin, int rows, float eps_in,
+                                  int has_bias, int* status, void* cuda_stream);
+int b200_trimul_contract_channels(const void* left_group, const void* right_group, void* const* tri_owners, int groups,
+                                  int group, int N, int direction, int* status, void* cuda_stream);
+int b200_trimul_epilogue_groups(const void* tri_groups, const void* z, const void* packed, void* y, int N, int rows,
+                                int groups, float eps_in, float eps_out, int residual, int* status, void* cuda_stream);
+
+/*
  * Stage 3: output LayerNorm + output projection + sigmoid output gate (+ residual) for `rows` rows.
  * tri: [B, rows, 128, N] fp16 as written by stage 2; z, y: [B, rows, N, 128] bf16. y may alias z.
  */

@@ -48,6 +48,18 @@ SIGNATURES = {
         c_int,
         [c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p],
     ),
+    "b200_trimul_prologue_channels": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    ),
+    "b200_trimul_contract_channels": (
+        c_int,
+        [c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
+    "b200_trimul_epilogue_groups": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],
+    ),
     "b200_trimul_epilogue": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],

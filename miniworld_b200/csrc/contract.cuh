@@ -32,6 +32,18 @@ struct ContractParams {
   int* status;
 };
 
+// Output destinations of the channel-sharded multi-GPU form (CTA-pair kernel only): output row r belongs to GPU
+// r / rows_per_owner, and every box_rows-row slice of a finished tile is stored (plain TMA store, peer memory over
+// NVLink for the other GPUs) into that owner's buffer [rows_per_owner][channels][N] at row r % rows_per_owner.
+// n == 0: one destination, the `tri` tensor map of the call.
+constexpr int kMaxOwners = 8;
+struct TriOwners {
+  CUtensorMap m[kMaxOwners];
+  int n;
+  int rows_per_owner;
+  int box_rows;  // 128, 64 or 32; divides rows_per_owner
+};
+
 constexpr int kContractThreads = 192;
 constexpr int kContractStages = 4;
 constexpr int kBM = 128;

@@ -31,7 +31,8 @@ struct PairSmem {
 template <int BN, bool INCOMING>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kContractThreads, 1)
 contract_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const __grid_constant__ CUtensorMap map_t, const ContractParams p) {
+                     const __grid_constant__ CUtensorMap map_t, const __grid_constant__ TriOwners own,
+                     const ContractParams p) {
   using L = PairSmem<BN>;
   constexpr int S = kPairStages;
   constexpr uint32_t kTmemCols = (2 * BN > 256) ? 512u : 256u;
@@ -254,7 +255,15 @@ contract_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         named_bar_sync(1, 128);
         if (store_thread) {
           const int col0 = n0 + g * 64;
-          if (col0 < p.n_cols && m0 < p.m_rows) tma_store_4d(&map_t, buf, col0, m0, hh, bb);
+          if (own.n == 0) {
+            if (col0 < p.n_cols && m0 < p.m_rows) tma_store_4d(&map_t, buf, col0, m0, hh, bb);
+          } else if (col0 < p.n_cols) {
+            // each slice of rows to the GPU that owns those rows (a slice never straddles two owners)
+            for (int r0 = 0; r0 < kBM && m0 + r0 < p.m_rows; r0 += own.box_rows) {
+              const int owner = (m0 + r0) / own.rows_per_owner;
+              tma_store_4d(&own.m[owner], buf + r0 * 128, col0, m0 + r0 - owner * own.rows_per_owner, hh, 0);
+            }
+          }
           bulk_commit();
         }
       }

@@ -128,8 +128,10 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
         const uint32_t zs = ts + 32768;
         if (!mbar_wait(t_empty(s), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
         mbar_arrive_expect_tx(t_full(s), 32768);
-        tma_load_3d(ts, &map_t, t_full(s), j0, 0, row);
-        tma_load_3d(ts + 16384, &map_t, t_full(s), j0 + 64, 0, row);
+        // 4-d map (column, channel in group, channel group, row): one group of 128 channels on one GPU, 128/P
+        // channels per group when the contraction was sharded by channels; the box covers every group
+        tma_load_4d(ts, &map_t, t_full(s), j0, 0, 0, row);
+        tma_load_4d(ts + 16384, &map_t, t_full(s), j0 + 64, 0, 0, row);
         ++t_issued;
         if (!mbar_wait(z_empty(s), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
         mbar_arrive_expect_tx(z_full(s), 32768);

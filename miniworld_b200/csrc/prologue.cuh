@@ -58,17 +58,23 @@ struct PrologueParams {
   const float* ln_b;          // [128] LayerNorm beta
   float eps;
   int* status;
-  int right_row_shift;  // added to the row coordinate of every store of `right` (see PushMaps)
 };
 
-// Extra destinations of `right`, used when the pair rows are spread over several GPUs: each map describes a
-// whole [N rows][128][N] buffer - this GPU's own gathered copy is `map_r`, the others are the peers' copies in
-// their memory - and a tile of local row r lands at row r + right_row_shift in every one of them. The stores are
-// plain (non-multicast) TMA stores; over NVLink they replace a separate all-gather pass.
-constexpr int kMaxPush = 7;
-struct PushMaps {
-  CUtensorMap m[kMaxPush];
-  int count;
+// Where the outputs go. Each output has a list of destination tensor maps; a finished tile [128 channels][128
+// positions] of local row r is stored to every destination d of its list at row r + row_shift, taking the
+// channels d * smem_step / 128 ... of the staging tile (smem_step = 0: every destination gets all 128 channels).
+//   one GPU:            one destination per output, the [B*rows, 128, N] buffers, row_shift 0
+//   rows over GPUs:     `right` additionally to the peers' gathered copies [N, 128, N] (row_shift = first local row)
+//   channels over GPUs: destination d = the GPU that contracts channel group d; it receives the 128/P channels of
+//                       its group for this GPU's rows, in its [N, 128/P, N] buffer (smem_step = 128/P channel rows)
+// Peer destinations are plain (non-multicast) TMA stores over NVLink; they replace a separate collective pass.
+constexpr int kMaxDst = 8;
+struct OutputMaps {
+  CUtensorMap left[kMaxDst];
+  CUtensorMap right[kMaxDst];
+  int n_left, n_right;
+  int step_left, step_right;    // bytes between the destinations' channel slices in a 16 KiB half staging tile
+  int shift_left, shift_right;  // added to the row coordinate
 };
 
 constexpr int kProThreads = 864;
@@ -85,8 +91,7 @@ constexpr int kProSmemBytes =
 template <bool HAS_BIAS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kProThreads, 1)
 prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_w,
-                const __grid_constant__ CUtensorMap map_l, const __grid_constant__ CUtensorMap map_r,
-                     const __grid_constant__ PushMaps push, const PrologueParams p) {
+                const __grid_constant__ OutputMaps out, const PrologueParams p) {
   constexpr int S = kProStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -130,8 +135,8 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
     fence_mbar_init();
     prefetch_tmap(&map_z);
     prefetch_tmap(&map_w);
-    prefetch_tmap(&map_l);
-    prefetch_tmap(&map_r);
+    prefetch_tmap(&out.left[0]);
+    prefetch_tmap(&out.right[0]);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), 512);

@@ -277,14 +277,14 @@ static int launch_contract(const CUtensorMap& ma, const CUtensorMap& mb, const C
 
 template <int BN, bool INCOMING>
 static int launch_contract_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mt,
-                                const ContractParams& p, int sms, cudaStream_t stream) {
+                                const TriOwners& own, const ContractParams& p, int sms, cudaStream_t stream) {
   auto kernel = contract_pair_kernel<BN, INCOMING>;
   constexpr int smem = PairSmem<BN>::kTotal;
   int rc = set_smem(kernel, smem);
   if (rc != B200_TRIMUL_OK) return rc;
   const long long tiles = static_cast<long long>(p.planes) * p.m_tiles * p.n_tiles;
   const long long pairs = tiles < sms / 2 ? tiles : sms / 2;
-  kernel<<<static_cast<int>(2 * pairs), kContractThreads, smem, stream>>>(ma, mb, mt, p);  // clusters of two CTAs
+  kernel<<<static_cast<int>(2 * pairs), kContractThreads, smem, stream>>>(ma, mb, mt, own, p);  // clusters of two CTAs
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
 }
@@ -398,25 +398,29 @@ int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const 
   return B200_TRIMUL_OK;
 }
 
-// `right` is [B, rows, 128, N] when n_push < 0. Otherwise (B = 1) it is this GPU's gathered copy [N, 128, N] and
-// push_dst[0 .. n_push-1] are the other GPUs' copies: local row r is written to row row_begin + r of each.
+// Where stage 1 writes (see OutputMaps): kLocal - left / right are [B, rows, 128, N]; kGatherRight (B = 1) - left is
+// [rows, 128, N], every right destination a gathered copy [N, 128, N]; kChannels (B = 1) - destination d of either
+// output is the [N, 128/n, N] buffer of the GPU that contracts channel group d.
+enum PrologueMode { kLocal, kGatherRight, kChannels };
+
 static int prologue_impl(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
-                         void* left, void* right, void* const* push_dst, int n_push, int B, int N, int row_begin,
-                         int rows, float eps_in, int has_bias, int* status, void* cuda_stream) {
-  if (!z || !packed || !left || !right || !status) return B200_TRIMUL_E_NULL;
-  const bool gathered = n_push >= 0;
-  if (gathered && (B != 1 || n_push > kMaxPush || (n_push > 0 && !push_dst))) return B200_TRIMUL_E_SHAPE;
+                         void* const* left_dst, int n_left, void* const* right_dst, int n_right, PrologueMode mode,
+                         int B, int N, int row_begin, int rows, float eps_in, int has_bias, int* status,
+                         void* cuda_stream) {
+  if (!z || !packed || !left_dst || !right_dst || !status) return B200_TRIMUL_E_NULL;
+  if (n_left < 1 || n_left > kMaxDst || n_right < 1 || n_right > kMaxDst) return B200_TRIMUL_E_SHAPE;
+  if (mode != kLocal && B != 1) return B200_TRIMUL_E_SHAPE;
+  if (mode == kChannels && (n_left != n_right || kC % n_left != 0 || (kC / n_left) % 8 != 0)) return B200_TRIMUL_E_SHAPE;
   int rc = check_bn(B, N);
   if (rc != B200_TRIMUL_OK) return rc;
   if (rows < 1 || row_begin < 0 || row_begin + rows > N) return B200_TRIMUL_E_SHAPE;
-  if (!aligned(z, 16) || !aligned(left, 16) || !aligned(right, 16) || !aligned(packed, 1024)) return B200_TRIMUL_E_ALIGN;
+  if (!aligned(z, 16) || !aligned(packed, 1024)) return B200_TRIMUL_E_ALIGN;
   DeviceInfo info;
   rc = device_info(&info);
   if (rc != B200_TRIMUL_OK) return rc;
 
-  CUtensorMap map_z, map_w, map_l, map_r;
-  PushMaps push;
-  push.count = gathered ? n_push : 0;
+  CUtensorMap map_z, map_w;
+  OutputMaps out;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(kC), static_cast<uint64_t>(N), static_cast<uint64_t>(B) * rows};
     const uint64_t strides[2] = {kC * 2ull, static_cast<uint64_t>(N) * kC * 2ull};
@@ -425,21 +429,30 @@ static int prologue_impl(const void* z, const void* packed, const uint8_t* token
     if (rc != B200_TRIMUL_OK) return rc;
   }
   {
-    // outputs, row-plane: [B * rows][128 channels][N columns]
-    const uint64_t dims[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(kC), static_cast<uint64_t>(B) * rows};
-    const uint64_t strides[2] = {static_cast<uint64_t>(N) * 2ull, static_cast<uint64_t>(N) * kC * 2ull};
-    const uint32_t box[3] = {64, 128, 1};
-    rc = make_map(&map_l, left, 3, dims, strides, box);
-    if (rc != B200_TRIMUL_OK) return rc;
-    const uint64_t dims_all[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(kC), static_cast<uint64_t>(N)};
-    rc = make_map(&map_r, right, 3, gathered ? dims_all : dims, strides, box);
-    if (rc != B200_TRIMUL_OK) return rc;
-    for (int d = 0; d < (gathered ? n_push : 0); ++d) {
-      if (!push_dst[d]) return B200_TRIMUL_E_NULL;
-      if (!aligned(push_dst[d], 16)) return B200_TRIMUL_E_ALIGN;
-      rc = make_map(&push.m[d], push_dst[d], 3, dims_all, strides, box);
+    // outputs, row-plane: [rows][channels][N columns]
+    const uint64_t n64 = static_cast<uint64_t>(N);
+    const uint64_t ch = mode == kChannels ? static_cast<uint64_t>(kC / n_left) : static_cast<uint64_t>(kC);
+    const uint64_t strides[2] = {n64 * 2ull, n64 * ch * 2ull};
+    const uint32_t box[3] = {64, static_cast<uint32_t>(ch), 1};
+    const uint64_t dims_local[3] = {n64, ch, static_cast<uint64_t>(B) * rows};
+    const uint64_t dims_all[3] = {n64, ch, n64};
+    for (int d = 0; d < n_left; ++d) {
+      if (!left_dst[d]) return B200_TRIMUL_E_NULL;
+      if (!aligned(left_dst[d], 16)) return B200_TRIMUL_E_ALIGN;
+      rc = make_map(&out.left[d], left_dst[d], 3, mode == kChannels ? dims_all : dims_local, strides, box);
       if (rc != B200_TRIMUL_OK) return rc;
     }
+    for (int d = 0; d < n_right; ++d) {
+      if (!right_dst[d]) return B200_TRIMUL_E_NULL;
+      if (!aligned(right_dst[d], 16)) return B200_TRIMUL_E_ALIGN;
+      rc = make_map(&out.right[d], right_dst[d], 3, mode == kLocal ? dims_local : dims_all, strides, box);
+      if (rc != B200_TRIMUL_OK) return rc;
+    }
+    out.n_left = n_left;
+    out.n_right = n_right;
+    out.step_left = out.step_right = mode == kChannels ? static_cast<int>(ch) * 128 : 0;
+    out.shift_left = mode == kChannels ? row_begin : 0;
+    out.shift_right = mode == kLocal ? 0 : row_begin;
   }
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(kC), 6ull * 128};
@@ -462,18 +475,17 @@ static int prologue_impl(const void* z, const void* packed, const uint8_t* token
   p.ln_b = p.ln_w + 128;
   p.eps = eps_in;
   p.status = status;
-  p.right_row_shift = gathered ? row_begin : 0;
   const int pairs = p.num_tiles < info.sms / 2 ? p.num_tiles : info.sms / 2;
   const int grid = 2 * pairs;  // clusters of two CTAs: CTA 0 produces `left`, CTA 1 `right`
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (has_bias) {
     rc = set_smem(prologue_kernel<true>, kProSmemBytes);
     if (rc != B200_TRIMUL_OK) return rc;
-    prologue_kernel<true><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, push, p);
+    prologue_kernel<true><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, out, p);
   } else {
     rc = set_smem(prologue_kernel<false>, kProSmemBytes);
     if (rc != B200_TRIMUL_OK) return rc;
-    prologue_kernel<false><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, map_l, map_r, push, p);
+    prologue_kernel<false><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, out, p);
   }
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
@@ -482,30 +494,48 @@ static int prologue_impl(const void* z, const void* packed, const uint8_t* token
 int b200_trimul_prologue(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
                          void* left, void* right, int B, int N, int row_begin, int rows, float eps_in, int has_bias,
                          int* status, void* cuda_stream) {
-  return prologue_impl(z, packed, token_mask, pair_mask, left, right, nullptr, -1, B, N, row_begin, rows, eps_in,
-                       has_bias, status, cuda_stream);
+  void* l[1] = {left};
+  void* r[1] = {right};
+  return prologue_impl(z, packed, token_mask, pair_mask, l, 1, r, 1, kLocal, B, N, row_begin, rows, eps_in, has_bias,
+                       status, cuda_stream);
 }
 
 int b200_trimul_prologue_push(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
                               void* left, void* right_all, void* const* right_all_peers, int n_peers, int N,
                               int row_begin, int rows, float eps_in, int has_bias, int* status, void* cuda_stream) {
-  if (n_peers < 0) return B200_TRIMUL_E_SHAPE;
-  return prologue_impl(z, packed, token_mask, pair_mask, left, right_all, right_all_peers, n_peers, 1, N, row_begin,
-                       rows, eps_in, has_bias, status, cuda_stream);
+  if (n_peers < 0 || n_peers > kMaxDst - 1 || (n_peers > 0 && !right_all_peers)) return B200_TRIMUL_E_SHAPE;
+  void* l[1] = {left};
+  void* r[kMaxDst] = {right_all};
+  for (int d = 0; d < n_peers; ++d) r[1 + d] = right_all_peers[d];
+  return prologue_impl(z, packed, token_mask, pair_mask, l, 1, r, 1 + n_peers, kGatherRight, 1, N, row_begin, rows,
+                       eps_in, has_bias, status, cuda_stream);
+}
+
+int b200_trimul_prologue_channels(const void* z, const void* packed, const uint8_t* token_mask, void* const* left_groups,
+                                  void* const* right_groups, int groups, int N, int row_begin, int rows, float eps_in,
+                                  int has_bias, int* status, void* cuda_stream) {
+  return prologue_impl(z, packed, token_mask, nullptr, left_groups, groups, right_groups, groups, kChannels, 1, N,
+                       row_begin, rows, eps_in, has_bias, status, cuda_stream);
 }
 
 // Contraction for output rows row_begin .. row_begin+rows-1. `k_rows` only matters for the incoming direction: the
 // number of pair rows k that left / right hold and the sum runs over (N for the full update, a rank's own rows for a
-// partial sum).
-static int contract_impl(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
-                         int k_rows, int direction, int* status, void* cuda_stream) {
-  if (!left || !right || !tri || !status) return B200_TRIMUL_E_NULL;
+// partial sum). `channels` is the channel count of the operands (128, or a group of 128/P in the channel-sharded
+// form). With n_owners > 0 (all rows, B = 1) the result does not go to `tri` but, row block by row block, to
+// owner_dst[s] + slot * (N/n_owners) * channels * N * 2 bytes: slot `slot` of GPU s's [n_owners][N/n_owners][channels][N].
+static int contract_impl(const void* left, const void* right, void* tri, void* const* owner_dst, int n_owners, int slot,
+                         int channels, int B, int N, int row_begin, int rows, int k_rows, int direction, int* status,
+                         void* cuda_stream) {
+  if (!left || !right || !status) return B200_TRIMUL_E_NULL;
+  if (n_owners == 0 && !tri) return B200_TRIMUL_E_NULL;
+  if (n_owners < 0 || n_owners > kMaxOwners || (n_owners > 0 && !owner_dst)) return B200_TRIMUL_E_SHAPE;
+  if (channels < 8 || channels > kC || channels % 8 != 0) return B200_TRIMUL_E_SHAPE;
   int rc = check_bn(B, N);
   if (rc != B200_TRIMUL_OK) return rc;
   if (rows < 1 || row_begin < 0 || row_begin + rows > N) return B200_TRIMUL_E_SHAPE;
   if (k_rows < 1 || k_rows > N) return B200_TRIMUL_E_SHAPE;
   if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING) return B200_TRIMUL_E_SHAPE;
-  if (!aligned(left, 16) || !aligned(right, 16) || !aligned(tri, 16)) return B200_TRIMUL_E_ALIGN;
+  if (!aligned(left, 16) || !aligned(right, 16) || (tri && !aligned(tri, 16))) return B200_TRIMUL_E_ALIGN;
   DeviceInfo info;
   rc = device_info(&info);
   if (rc != B200_TRIMUL_OK) return rc;
@@ -515,14 +545,15 @@ static int contract_impl(const void* left, const void* right, void* tri, int B, 
   const bool use_pair = rows >= 256 && (pair_rows - rows) * 4 <= rows;
   const int bn = use_pair ? ((N + 255) / 256 * 256 <= (N + 127) / 128 * 128 ? 256 : 128) : choose_bn(N);
   const uint64_t n64 = static_cast<uint64_t>(N);
-  const uint64_t row_stride = kC * n64 * 2;  // bytes between consecutive pair rows
+  const uint64_t ch64 = static_cast<uint64_t>(channels);
+  const uint64_t row_stride = ch64 * n64 * 2;  // bytes between consecutive pair rows
   const uint64_t h_stride = n64 * 2;
   const uint64_t left_rows = incoming ? static_cast<uint64_t>(k_rows) : static_cast<uint64_t>(rows);
   const uint64_t right_rows = incoming ? static_cast<uint64_t>(k_rows) : n64;
 
   CUtensorMap map_a, map_b, map_t;
   {
-    const uint64_t dims[4] = {n64, left_rows, static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
+    const uint64_t dims[4] = {n64, left_rows, ch64, static_cast<uint64_t>(B)};
     const uint64_t strides[3] = {row_stride, h_stride, left_rows * row_stride};
     const uint32_t box_out[4] = {64, 128, 1, 1};
     const uint32_t box_in[4] = {64, 64, 1, 1};
@@ -530,23 +561,45 @@ static int contract_impl(const void* left, const void* right, void* tri, int B, 
     if (rc != B200_TRIMUL_OK) return rc;
   }
   {
-    const uint64_t dims[4] = {n64, right_rows, static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
+    const uint64_t dims[4] = {n64, right_rows, ch64, static_cast<uint64_t>(B)};
     const uint64_t strides[3] = {row_stride, h_stride, right_rows * row_stride};
     const uint32_t box_out[4] = {64, static_cast<uint32_t>(use_pair ? bn / 2 : bn), 1, 1};  // a CTA of a pair loads half
     const uint32_t box_in[4] = {64, 64, 1, 1};
     rc = make_map(&map_b, right, 4, dims, strides, incoming ? box_in : box_out);
     if (rc != B200_TRIMUL_OK) return rc;
   }
-  {
-    const uint64_t dims[4] = {n64, static_cast<uint64_t>(rows), static_cast<uint64_t>(kC), static_cast<uint64_t>(B)};
+  TriOwners own;
+  own.n = n_owners;
+  own.rows_per_owner = 0;
+  own.box_rows = 128;
+  if (n_owners == 0) {
+    const uint64_t dims[4] = {n64, static_cast<uint64_t>(rows), ch64, static_cast<uint64_t>(B)};
     const uint64_t strides[3] = {row_stride, h_stride, static_cast<uint64_t>(rows) * row_stride};
     const uint32_t box[4] = {64, 128, 1, 1};
     rc = make_map(&map_t, tri, 4, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
+  } else {
+    // only the CTA-pair kernel stores per owner; every 32-row slice must belong to one owner
+    if (!use_pair || B != 1 || row_begin != 0 || rows != N || slot < 0 || slot >= n_owners) return B200_TRIMUL_E_SHAPE;
+    if (N % n_owners != 0 || (N / n_owners) % 32 != 0) return B200_TRIMUL_E_SHAPE;
+    const int rpo = N / n_owners;
+    own.rows_per_owner = rpo;
+    own.box_rows = rpo % 128 == 0 ? 128 : (rpo % 64 == 0 ? 64 : 32);
+    const uint64_t dims[4] = {n64, static_cast<uint64_t>(rpo), ch64, 1};
+    const uint64_t strides[3] = {row_stride, h_stride, static_cast<uint64_t>(rpo) * row_stride};
+    const uint32_t box[4] = {64, static_cast<uint32_t>(own.box_rows), 1, 1};
+    for (int s2 = 0; s2 < n_owners; ++s2) {
+      if (!owner_dst[s2]) return B200_TRIMUL_E_NULL;
+      if (!aligned(owner_dst[s2], 16)) return B200_TRIMUL_E_ALIGN;
+      uint8_t* base = static_cast<uint8_t*>(owner_dst[s2]) + static_cast<size_t>(slot) * rpo * row_stride;
+      rc = make_map(&own.m[s2], base, 4, dims, strides, box);
+      if (rc != B200_TRIMUL_OK) return rc;
+    }
+    map_t = own.m[0];  // unused by the kernel in this form, but a valid descriptor
   }
   ContractParams p;
-  p.H = kC;
-  p.planes = B * kC;
+  p.H = channels;
+  p.planes = B * channels;
   p.m_tiles = use_pair ? pair_rows / 256 : (rows + kBM - 1) / kBM;
   p.m_rows = rows;
   p.n_tiles = (N + bn - 1) / bn;
@@ -557,11 +610,11 @@ static int contract_impl(const void* left, const void* right, void* tri, int B, 
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (use_pair) {
     if (!incoming) {
-      if (bn == 256) return launch_contract_pair<256, false>(map_a, map_b, map_t, p, info.sms, stream);
-      return launch_contract_pair<128, false>(map_a, map_b, map_t, p, info.sms, stream);
+      if (bn == 256) return launch_contract_pair<256, false>(map_a, map_b, map_t, own, p, info.sms, stream);
+      return launch_contract_pair<128, false>(map_a, map_b, map_t, own, p, info.sms, stream);
     }
-    if (bn == 256) return launch_contract_pair<256, true>(map_a, map_b, map_t, p, info.sms, stream);
-    return launch_contract_pair<128, true>(map_a, map_b, map_t, p, info.sms, stream);
+    if (bn == 256) return launch_contract_pair<256, true>(map_a, map_b, map_t, own, p, info.sms, stream);
+    return launch_contract_pair<128, true>(map_a, map_b, map_t, own, p, info.sms, stream);
   }
   if (!incoming) {
     if (bn == 256) return launch_contract<256, false>(map_a, map_b, map_t, p, info.sms, stream);
@@ -575,12 +628,20 @@ static int contract_impl(const void* left, const void* right, void* tri, int B, 
 
 int b200_trimul_contract(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
                          int direction, int* status, void* cuda_stream) {
-  return contract_impl(left, right, tri, B, N, row_begin, rows, N, direction, status, cuda_stream);
+  return contract_impl(left, right, tri, nullptr, 0, 0, kC, B, N, row_begin, rows, N, direction, status, cuda_stream);
 }
 
 int b200_trimul_contract_partial(const void* left, const void* right, void* tri_partial, int B, int N, int k_rows,
                                  int* status, void* cuda_stream) {
-  return contract_impl(left, right, tri_partial, B, N, 0, N, k_rows, B200_TRIMUL_INCOMING, status, cuda_stream);
+  return contract_impl(left, right, tri_partial, nullptr, 0, 0, kC, B, N, 0, N, k_rows, B200_TRIMUL_INCOMING, status,
+                       cuda_stream);
+}
+
+int b200_trimul_contract_channels(const void* left_group, const void* right_group, void* const* tri_owners, int groups,
+                                  int group, int N, int direction, int* status, void* cuda_stream) {
+  if (groups < 1 || groups > kMaxOwners || kC % groups != 0) return B200_TRIMUL_E_SHAPE;
+  return contract_impl(left_group, right_group, nullptr, tri_owners, groups, group, kC / groups, 1, N, 0, N, N, direction,
+                       status, cuda_stream);
 }
 
 int b200_trimul_reduce_partials(void* tri, const void* const* partials, int n_src, int N, int row_begin, int rows,
@@ -613,9 +674,12 @@ int b200_trimul_reduce_partials(void* tri, const void* const* partials, int n_sr
   return B200_TRIMUL_OK;
 }
 
-int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows,
+// `groups` = 1: tri is [B*rows][128][N]. groups = P (B = 1): tri is [P][rows][128/P][N], channel group g of every row
+// in slab g (what the channel-sharded contraction of GPU g stored there).
+static int epilogue_impl(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows, int groups,
                          float eps_in, float eps_out, int residual, int* status, void* cuda_stream) {
   if (!tri || !z || !packed || !y || !status) return B200_TRIMUL_E_NULL;
+  if (groups < 1 || groups > 8 || kC % groups != 0 || (groups > 1 && B != 1)) return B200_TRIMUL_E_SHAPE;
   int rc = check_bn(B, N);
   if (rc != B200_TRIMUL_OK) return rc;
   if (rows < 1 || rows > N) return B200_TRIMUL_E_SHAPE;
@@ -628,10 +692,11 @@ int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, voi
 
   CUtensorMap map_t, map_z, map_y, map_w;
   {
-    const uint64_t dims[3] = {n64, static_cast<uint64_t>(kC), nrows};
-    const uint64_t strides[2] = {n64 * 2, kC * n64 * 2};
-    const uint32_t box[3] = {64, 128, 1};
-    rc = make_map(&map_t, tri, 3, dims, strides, box);
+    const uint64_t cg = static_cast<uint64_t>(kC / groups);
+    const uint64_t dims[4] = {n64, cg, static_cast<uint64_t>(groups), nrows};
+    const uint64_t strides[3] = {n64 * 2, nrows * cg * n64 * 2, cg * n64 * 2};
+    const uint32_t box[4] = {64, static_cast<uint32_t>(cg), static_cast<uint32_t>(groups), 1};
+    rc = make_map(&map_t, tri, 4, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
   }
   {
@@ -665,6 +730,16 @@ int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, voi
                                                                                                        map_w, p);
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
+}
+
+int b200_trimul_epilogue(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows,
+                         float eps_in, float eps_out, int residual, int* status, void* cuda_stream) {
+  return epilogue_impl(tri, z, packed, y, B, N, rows, 1, eps_in, eps_out, residual, status, cuda_stream);
+}
+
+int b200_trimul_epilogue_groups(const void* tri_groups, const void* z, const void* packed, void* y, int N, int rows,
+                                int groups, float eps_in, float eps_out, int residual, int* status, void* cuda_stream) {
+  return epilogue_impl(tri_groups, z, packed, y, 1, N, rows, groups, eps_in, eps_out, residual, status, cuda_stream);
 }
 
 int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,

@@ -262,6 +262,71 @@ def epilogue(
     _lib.check(rc, "b200_trimul_epilogue")
 
 
+def prologue_channels(
+    z: torch.Tensor,
+    packed: torch.Tensor,
+    left_groups: list,
+    right_groups: list,
+    status: torch.Tensor,
+    token_mask: Optional[torch.Tensor] = None,
+    row_begin: int = 0,
+    eps_in: float = 1e-5,
+    has_bias: bool = False,
+) -> None:
+    """Stage 1 of the channel-sharded form for the rows ``z`` [1, rows, N, 128]: channel group g of ``left`` / ``right``
+    goes to rows row_begin.. of ``left_groups[g]`` / ``right_groups[g]`` ([1, N, 128/P, N], on the GPU that contracts
+    group g; peer memory for the other GPUs)."""
+    B, N = _check_z(z)
+    if B != 1 or len(left_groups) != len(right_groups):
+        raise RuntimeError("prologue_channels: B must be 1 and both outputs need one buffer per channel group")
+    tm = as_mask_u8(token_mask, z.device)
+    lg, rg = _ptr_array(left_groups), _ptr_array(right_groups)
+    with torch.cuda.device(z.device):
+        rc = _lib.load().b200_trimul_prologue_channels(
+            _ptr(z), _ptr(packed), _ptr(tm), lg, rg, len(left_groups), N, row_begin, int(z.shape[1]), float(eps_in),
+            int(bool(has_bias)), _ptr(status), _stream(z.device),
+        )
+    _lib.check(rc, "b200_trimul_prologue_channels")
+
+
+def contract_channels(
+    left_group: torch.Tensor, right_group: torch.Tensor, tri_owners: list, group: int, status: torch.Tensor, N: int,
+    outgoing: bool,
+) -> None:
+    """Stage 2 of the channel-sharded form on the GPU that owns channel group ``group``: ``left_group`` /
+    ``right_group`` [1, N, 128/P, N]; rows s*N/P.. of the result go to slab ``group`` of ``tri_owners[s]``
+    ([P, N/P, 128/P, N] on GPU s)."""
+    owners = _ptr_array(tri_owners)
+    with torch.cuda.device(left_group.device):
+        rc = _lib.load().b200_trimul_contract_channels(
+            _ptr(left_group), _ptr(right_group), owners, len(tri_owners), group, N,
+            _lib.OUTGOING if outgoing else _lib.INCOMING, _ptr(status), _stream(left_group.device),
+        )
+    _lib.check(rc, "b200_trimul_contract_channels")
+
+
+def epilogue_groups(
+    tri_groups: torch.Tensor,
+    z: torch.Tensor,
+    packed: torch.Tensor,
+    y: torch.Tensor,
+    status: torch.Tensor,
+    groups: int,
+    eps_in: float = 1e-5,
+    eps_out: float = 1e-5,
+    residual: bool = True,
+) -> None:
+    """Stage 3 of the channel-sharded form: ``tri_groups`` [P, rows, 128/P, N] holds this GPU's rows, one slab per
+    channel group."""
+    B, N = _check_z(z)
+    with torch.cuda.device(z.device):
+        rc = _lib.load().b200_trimul_epilogue_groups(
+            _ptr(tri_groups), _ptr(z), _ptr(packed), _ptr(y), N, int(z.shape[1]), groups, float(eps_in), float(eps_out),
+            int(bool(residual)), _ptr(status), _stream(z.device),
+        )
+    _lib.check(rc, "b200_trimul_epilogue_groups")
+
+
 def read_status(status: torch.Tensor) -> int:
     """Synchronise the current stream and return the device status word (0 = ok)."""
     out = c_int(0)

@@ -1,28 +1,35 @@
 """Multi-GPU forms of the triangle multiplicative update (one process per GPU, ``torch.distributed``).
 
-Two schemes, neither present in the reference (it only has data-parallel training):
+Neither is present in the reference (it only has data-parallel training):
 
-* :class:`RowShardedTriangleMultiplication` - the pair tensor is sharded by rows ``i`` (B = 1). The prologue
-  and the epilogue are local to the rows a rank owns. The contraction needs the other ranks' rows of the
-  contracted operand(s), which are all-gathered into local HBM (NCCL) and then read by local TMA loads; no
-  kernel ever loads from a peer's memory.
-    outgoing  t[i in I_r, j] = sum_k a[i,k] b[j,k]     -> all-gather of ``right`` (rows j)
-    incoming  t[i, j] = sum_r sum_{k in I_r} a[k,i] b[k,j] -> every rank sums over the rows k it owns, for ALL
-                                                           (i, j), and a reduce-scatter over i adds the partial
-                                                           sums (one tensor crosses the links instead of two).
-                                                           ``incoming="gather"`` selects the older scheme, an
-                                                           all-gather of ``left`` and ``right`` (rows k), which is
-                                                           bit-identical to the single-GPU forward.
-  The row-plane layout [rows, H, N] makes the gathered tensor [P, N/P, H, N] == [N, H, N] with no repacking, and
-  the partial-sum tensor [N, H, N] splits into the ranks' row blocks the same way.
+* :class:`RowShardedTriangleMultiplication` - the pair tensor is sharded by rows ``i`` (B = 1): every rank passes
+  and gets back its rows. The prologue and the epilogue are local to those rows; the contraction in between needs
+  data of the other ranks, and there are two ways to split it:
 
-  Two transports move those tensors. ``"nccl"``: ``all_gather_into_tensor`` / ``reduce_scatter_tensor`` between the
-  kernels. ``"p2p"``: the kernels themselves use the other GPUs' memory (buffers from torch's symmetric memory,
-  mapped into every process) - the prologue's TMA stores write each tile of ``right`` into every GPU's gathered
-  copy as it is produced, and a reduce kernel reads the peers' partial sums with plain loads; the only collective
-  left is a one-element all-reduce that orders "my kernel has finished" before "the peers read / I read". No
-  kernel waits on another GPU, and no load is a multicast load. Two buffers alternate between calls, so a rank
-  that runs ahead writes the buffer its peers are not reading.
+  ``contraction="rows"`` - each rank contracts for its own output rows.
+    outgoing  t[i in I_r, j] = sum_k a[i,k] b[j,k]          -> every rank needs all rows j of ``right``
+    incoming  t[i, j] = sum_r sum_{k in I_r} a[k,i] b[k,j]  -> every rank sums over the rows k it owns, for ALL
+                                                               (i, j), and the partial sums are added per row
+                                                               block (one tensor crosses the links, not two).
+                                                               ``incoming="gather"`` selects the older scheme, an
+                                                               all-gather of ``left`` and ``right`` (rows k), which
+                                                               is bit-identical to the single-GPU forward.
+    Per direction every rank sends or receives (P-1)/P of one [N, 128, N] tensor.
+
+  ``contraction="channels"`` - rank g contracts the 128/P channels of group g for ALL rows (channels play the role
+    the heads play in sequence-parallel attention). Each rank sends (P-1)/P of its own 1/P of ``left`` and ``right``
+    and receives as much, then sends (P-1)/P of its 1/P of the result: about 3/P of a tensor per direction, less
+    than the row scheme from P = 4 on, and bit-identical to the single-GPU forward.
+
+  Two transports. ``"p2p"``: the kernels themselves use the other GPUs' memory (buffers from torch's symmetric
+  memory, mapped into every process) - the prologue's and the contraction's TMA stores write each tile into the
+  buffer of the GPU that needs it as the tile is produced, and (row scheme, incoming) a reduce kernel reads the
+  peers' partial sums with plain loads; the only collective left is a one-element all-reduce that orders "my
+  kernel has finished" before "the peers read / I read". No kernel waits on another GPU, and no load is a multicast
+  load. Two sets of buffers alternate between calls, so a rank that runs ahead writes the set its peers are not
+  reading. ``"nccl"`` (row scheme only): ``all_gather_into_tensor`` / ``reduce_scatter_tensor`` between the
+  kernels; the row-plane layout [rows, H, N] makes the gathered tensor [P, N/P, H, N] == [N, H, N] with no
+  repacking, and the partial-sum tensor splits into the ranks' row blocks the same way.
 * :func:`shard_batch` - plain batch data parallelism for B > 1: samples are independent, no collective.
 """
 
@@ -59,6 +66,20 @@ def shard_batch(batch: int, world: int, rank: int) -> tuple[int, int]:
     return begin, count
 
 
+def channels_feasible(n: int, world: int) -> bool:
+    """Whether the channel-sharded contraction can run: P divides 128 into groups of at least 8 channels, every
+    32-row slice of the result has one owner, and the CTA-pair contraction kernel (the one that stores per owner)
+    is the kernel chosen for N rows (N >= 256 padded to 256-row tiles by at most a quarter)."""
+    if world < 2 or D % world != 0 or D // world < 8 or n % world != 0 or (n // world) % 32 != 0:
+        return False
+    return n >= 256 and ((-n) % 256) * 4 <= n
+
+
+def choose_contraction(n: int, world: int) -> str:
+    """Fewer bytes per rank: the row scheme moves (P-1)/P of a tensor per direction, the channel scheme 3(P-1)/P^2."""
+    return "channels" if world >= 4 and channels_feasible(n, world) else "rows"
+
+
 class RowShardedTriangleMultiplication(TriangleMultiplication):
     """Same parameters and state_dict as :class:`TriangleMultiplication`; ``forward`` takes the local rows.
 
@@ -67,23 +88,35 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
     """
 
     def __init__(self, d_pair: int = D, d_hidden: Optional[int] = None, outgoing: bool = True, group=None,
-                 incoming: str = "reduce", transport: str = "auto", **kw):
+                 incoming: str = "reduce", transport: str = "auto", contraction: str = "auto", **kw):
         super().__init__(d_pair, d_hidden, outgoing=outgoing, **kw)
         if incoming not in ("reduce", "gather"):
             raise ValueError(f"incoming must be 'reduce' or 'gather', got {incoming!r}")
         if transport not in ("auto", "p2p", "nccl"):
             raise ValueError(f"transport must be 'auto', 'p2p' or 'nccl', got {transport!r}")
+        if contraction not in ("auto", "rows", "channels"):
+            raise ValueError(f"contraction must be 'auto', 'rows' or 'channels', got {contraction!r}")
+        if contraction == "channels" and transport == "nccl":
+            raise ValueError("the channel-sharded contraction stores into peer memory: it needs transport 'p2p'")
         self.group = group
         self.incoming_scheme = incoming
-        self.transport = "nccl" if (not outgoing and incoming == "gather") else transport
+        self.transport = "nccl" if (contraction != "channels" and not outgoing and incoming == "gather") else transport
+        self.contraction = contraction
+        self._explicit = transport == "p2p" or contraction == "channels"  # asked for by name: no silent fallback
         self._bufs = None
         self._sym = None
         self._calls = 0
 
-    def _symmetric(self, N: int, device: torch.device):
-        """Two [1, N, 128, N] fp16 buffers in symmetric memory with every rank's view of them, or None (NCCL path).
+    # ------------------------------------------------------------------ buffers
+    def _symmetric(self, N: int, world: int, device: torch.device):
+        """Two sets of fp16 buffers in symmetric memory, each entry the list of every rank's view of one buffer, or
+        None (NCCL path). Settles ``self.transport`` and ``self.contraction``.
 
         Collective: every rank allocates and exchanges handles on the first call for a given N."""
+        if self.contraction == "auto":
+            self.contraction = choose_contraction(N, world) if self.transport != "nccl" else "rows"
+        if self.contraction == "channels" and not channels_feasible(N, world):
+            raise RuntimeError(f"the channel-sharded contraction cannot run for N={N} on {world} GPUs")
         if self.transport == "nccl":
             return None
         if self._sym is not None and self._sym[0] == (N, device):
@@ -91,48 +124,61 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
         import torch.distributed._symmetric_memory as symm_mem
 
         group = self.group if self.group is not None else dist.group.WORLD
-        world = dist.get_world_size(group)
+        rows, cg = N // world, D // world
+        if self.contraction == "channels":
+            shapes = {"left": (1, N, cg, N), "right": (1, N, cg, N), "tri": (world, rows, cg, N)}
+        else:
+            shapes = {"full": (1, N, D, N)}  # gathered `right` (outgoing) or the partial sums (incoming)
         ok = torch.ones(1, device=device)
-        views, owners = [], []
+        sets, owners = [], []
         try:
             for _ in range(2):
-                t = symm_mem.empty(N * D * N, dtype=torch.float16, device=device)
-                hdl = symm_mem.rendezvous(t, group)
-                owners.append((t, hdl))  # the views below do not keep the allocation alive
-                views.append([hdl.get_buffer(r, (1, N, D, N), torch.float16) for r in range(world)])
+                views = {}
+                for name, shape in shapes.items():
+                    numel = 1
+                    for s in shape:
+                        numel *= s
+                    t = symm_mem.empty(numel, dtype=torch.float16, device=device)
+                    hdl = symm_mem.rendezvous(t, group)
+                    owners.append((t, hdl))  # the views below do not keep the allocation alive
+                    views[name] = [hdl.get_buffer(r, shape, torch.float16) for r in range(world)]
+                sets.append(views)
         except Exception as exc:  # no peer access between the GPUs, or no symmetric memory in this build
-            if self.transport == "p2p":
-                raise RuntimeError(f"transport='p2p' needs torch symmetric memory between the ranks: {exc!r}") from exc
+            if self._explicit:
+                raise RuntimeError(f"transport 'p2p' needs torch symmetric memory between the ranks: {exc!r}") from exc
             ok.zero_()
         dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)  # all ranks take the same path
         if float(ok.item()) == 0.0:
             self.transport = "nccl"
+            self.contraction = "rows"
             self._sym = None
             return None
         self.transport = "p2p"
-        self._sym = ((N, device), views, owners)
-        return views
+        self._sym = ((N, device), sets, owners)
+        return sets
 
     def _scratch(self, N: int, rows: int, device: torch.device):
         key = (N, rows, device)
         if self._bufs is None or self._bufs[0] != key:
             plane = lambda r: torch.empty(1, r, D, N, dtype=torch.float16, device=device)  # noqa: E731
             nccl = self.transport == "nccl"
+            channels = self.contraction == "channels"
             gather = nccl and (self.outgoing or self.incoming_scheme == "gather")
             bufs = dict(
                 flag=torch.zeros(1, device=device),
                 packed=F_.aligned_empty(F_.packed_bytes(), device),
                 status=torch.zeros(16, dtype=torch.int32, device=device),
-                left=plane(rows),
-                right=plane(rows),
+                left=None if channels else plane(rows),
+                right=None if channels else plane(rows),
                 right_all=plane(N) if gather else None,
                 left_all=plane(N) if gather and not self.outgoing else None,
                 tri_partial=plane(N) if nccl and not gather else None,
-                tri=plane(rows),
+                tri=None if channels else plane(rows),
             )
             self._bufs = (key, bufs)
         return self._bufs[1]
 
+    # ------------------------------------------------------------------ forward
     def forward(self, pair_rows: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         if torch.is_grad_enabled() and pair_rows.requires_grad:
             raise NotImplementedError("backward is not implemented")
@@ -148,27 +194,36 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
             raise RuntimeError(f"rank {rank} of {world} owns {count} rows of N={N}, got {rows}")
         z = pair_rows.detach().to(torch.bfloat16).contiguous()
         dev = z.device
-        sym = self._symmetric(N, dev)  # settles the transport before the scratch buffers are sized
+        sym = self._symmetric(N, world, dev)  # settles transport and contraction before the scratch is sized
         b = self._scratch(N, rows, dev)
         F_.pack_weights(self._params(), b["packed"], self._biases)
         b["status"].zero_()
         has_bias = bool(self._biases) and any(self._biases.get(k) is not None for k in F_.BIAS_ORDER[:4])
         pro = dict(token_mask=mask, row_begin=begin, eps_in=float(self.ln_pair.eps), has_bias=has_bias)
-        if sym is not None:
-            self._tri_p2p(z, b, sym, pro, N, begin, rows, world, rank)
-        else:
-            self._tri_nccl(z, b, pro, N, begin, rows)
+        epi = dict(eps_in=float(self.ln_pair.eps), eps_out=float(self.ln_out.eps), residual=self.residual)
         y = torch.empty_like(z)
-        F_.epilogue(b["tri"], z, b["packed"], y, b["status"], eps_in=float(self.ln_pair.eps),
-                    eps_out=float(self.ln_out.eps), residual=self.residual)
+        if sym is None:
+            self._tri_nccl(z, b, pro, N, begin, rows)
+            F_.epilogue(b["tri"], z, b["packed"], y, b["status"], **epi)
+        else:
+            bufs = sym[self._calls & 1]  # every rank makes the same number of calls, so all pick the same set
+            self._calls += 1
+            if self.contraction == "channels":
+                F_.prologue_channels(z, b["packed"], bufs["left"], bufs["right"], b["status"], **pro)
+                dist.all_reduce(b["flag"], group=self.group)  # every rank's rows have landed in every group's operands
+                F_.contract_channels(bufs["left"][rank], bufs["right"][rank], bufs["tri"], rank, b["status"], N,
+                                     self.outgoing)
+                dist.all_reduce(b["flag"], group=self.group)  # every group's result has landed at the row owners
+                F_.epilogue_groups(bufs["tri"][rank], z, b["packed"], y, b["status"], world, **epi)
+            else:
+                self._tri_p2p(z, b, bufs["full"], pro, N, begin, rows, world, rank)
+                F_.epilogue(b["tri"], z, b["packed"], y, b["status"], **epi)
         if self.check_status:
             F_.check_status(b["status"], "row-sharded trimul")
         return y
 
-    def _tri_p2p(self, z, b, sym, pro, N, begin, rows, world, rank) -> None:
-        """Stages 1 and 2 with the kernels writing to / reading from the peers' memory."""
-        views = sym[self._calls & 1]  # every rank makes the same number of calls, so all pick the same buffer
-        self._calls += 1
+    def _tri_p2p(self, z, b, views, pro, N, begin, rows, world, rank) -> None:
+        """Stages 1 and 2 of the row scheme with the kernels writing to / reading from the peers' memory."""
         mine = views[rank]
         if self.outgoing:
             peers = [views[r] for r in range(world) if r != rank]
@@ -182,8 +237,8 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
             F_.reduce_partials(b["tri"], views, N, begin, rows)  # rank order: the same sum on every run
 
     def _tri_nccl(self, z, b, pro, N, begin, rows) -> None:
-        """Stages 1 and 2 with NCCL collectives between the kernels (B = 1: the collectives work on [rows, 128, N]
-        views, so that the rank-major concatenation is the row dimension)."""
+        """Stages 1 and 2 of the row scheme with NCCL collectives between the kernels (B = 1: the collectives work on
+        [rows, 128, N] views, so that the rank-major concatenation is the row dimension)."""
         F_.prologue(z, b["packed"], b["left"], b["right"], b["status"], **pro)
         if self.outgoing:
             dist.all_gather_into_tensor(b["right_all"].view(N, D, N), b["right"].view(rows, D, N), group=self.group)

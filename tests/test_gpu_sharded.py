@@ -24,7 +24,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, outgoing, incoming, transport, N, ret):
+def _worker(rank, world, port, outgoing, incoming, transport, contraction, N, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -44,14 +44,14 @@ def _worker(rank, world, port, outgoing, incoming, transport, N, ret):
         full.load_state_dict(p)
         full = full.to(dev).to(torch.bfloat16).eval()
         shard = sharded.RowShardedTriangleMultiplication(128, outgoing=outgoing, incoming=incoming, transport=transport,
-                                                         check_status=True)
+                                                         contraction=contraction, check_status=True)
         shard.load_state_dict(p)
         shard = shard.to(dev).to(torch.bfloat16).eval()
         with torch.no_grad():
             want = full(z.to(dev), mask.to(dev))[:, begin : begin + rows]
             for _ in range(3):  # later calls reuse the buffers (the p2p transport alternates between two)
                 got = shard(z[:, begin : begin + rows].contiguous().to(dev), mask.to(dev))
-        assert shard.transport == transport
+        assert shard.transport == transport and shard.contraction == contraction
         torch.cuda.synchronize()
         ret[rank] = (bool(torch.equal(got, want)), float((got.float() - want.float()).abs().max()))
     finally:
@@ -59,21 +59,22 @@ def _worker(rank, world, port, outgoing, incoming, transport, N, ret):
 
 
 @pytest.mark.parametrize(
-    "outgoing,incoming,transport",
-    [(True, "reduce", "nccl"), (False, "gather", "nccl"), (False, "reduce", "nccl"), (True, "reduce", "p2p"),
-     (False, "reduce", "p2p")],
+    "outgoing,incoming,transport,contraction",
+    [(True, "reduce", "nccl", "rows"), (False, "gather", "nccl", "rows"), (False, "reduce", "nccl", "rows"),
+     (True, "reduce", "p2p", "rows"), (False, "reduce", "p2p", "rows"), (True, "reduce", "p2p", "channels"),
+     (False, "reduce", "p2p", "channels")],
 )
-def test_row_sharded_equals_single_gpu(outgoing, incoming, transport):
+def test_row_sharded_equals_single_gpu(outgoing, incoming, transport, contraction):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world, N = 2, 256
     port = _free_port()
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(world, port, outgoing, incoming, transport, N, ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, outgoing, incoming, transport, contraction, N, ret), nprocs=world, join=True)
         assert len(ret) == world
         for rank, (same, err) in ret.items():
-            if outgoing or incoming == "gather":
+            if outgoing or incoming == "gather" or contraction == "channels":
                 # same kernels, same k order: the rows a rank computes are bit-identical to the unsharded forward
                 assert same, (rank, err)
             else:

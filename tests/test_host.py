@@ -106,6 +106,19 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def test_contraction_scheme_choice():
+    # the channel scheme needs P | 128, N/P a multiple of 32 and an N the CTA-pair contraction handles
+    assert sharded.channels_feasible(768, 8) and sharded.channels_feasible(768, 2) and sharded.channels_feasible(2048, 8)
+    assert not sharded.channels_feasible(384, 8)      # 48 rows per rank
+    assert not sharded.channels_feasible(384, 4)      # 384 rows pad to 512: more than a quarter
+    assert not sharded.channels_feasible(768, 3) and not sharded.channels_feasible(128, 2)
+    # fewer bytes per rank from four GPUs on
+    assert sharded.choose_contraction(768, 2) == "rows" and sharded.choose_contraction(768, 4) == "channels"
+    assert sharded.choose_contraction(768, 8) == "channels" and sharded.choose_contraction(384, 8) == "rows"
+    with pytest.raises(ValueError):
+        sharded.RowShardedTriangleMultiplication(128, contraction="channels", transport="nccl")
+
+
 def _row_sharded_worker(rank, world, port, scheme, ret):
     outgoing = scheme == "outgoing"
     os.environ["MASTER_ADDR"] = "127.0.0.1"

@@ -258,7 +258,8 @@ def run_b200(args):
         begin, rows = sharded.row_range(N, world, rank)
         mods = {}
         for direction in ("outgoing", "incoming"):
-            m = sharded.RowShardedTriangleMultiplication(128, outgoing=(direction == "outgoing"))
+            m = sharded.RowShardedTriangleMultiplication(128, outgoing=(direction == "outgoing"),
+                                                         contraction=args.contraction)
             m.load_state_dict(w.params)
             mods[direction] = m.to(dev).to(torch.bfloat16).eval()
         z_host = w.z[:, begin : begin + rows].contiguous().pin_memory()
@@ -391,10 +392,7 @@ def run_b200(args):
             "config": {"workload": args.workload, "B": B, "N": N, "d_pair": 128, "d_hidden": 128,
                        "step": "outgoing forward + incoming forward (2 module forwards)",
                        "cells_per_step": cells_per_step,
-                       "parallelism": "single GPU" if world == 1 else (
-                           f"row-sharded over {world} GPUs, transport {mods['outgoing'].transport}: outgoing = prologue "
-                           "writes `right` into every GPU's copy, incoming = partial sums over the local rows k + "
-                           "reduce over the ranks"),
+                       "parallelism": "single GPU" if world == 1 else describe_sharding(world, mods["outgoing"]),
                        "l2": "inputs and intermediates (604 MB at N=768) exceed the 126 MB L2; no flush"},
             "e2e": {"value": cells_per_step / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -402,7 +400,8 @@ def run_b200(args):
                            "input buffers so copies overlap the neighbouring steps' kernels"},
             # this repository's kernels per step: (pack, prologue, contraction, epilogue) x 2 directions, plus the
             # peer-reading reduce kernel of the incoming direction on the p2p transport
-            "gpu_launches": (9 if world > 1 and mods["outgoing"].transport == "p2p" else 8) * args.steps,
+            "gpu_launches": (9 if world > 1 and mods["outgoing"].transport == "p2p"
+                             and mods["outgoing"].contraction == "rows" else 8) * args.steps,
             "clocks": clocks,
         }
         if stages_ms is not None:
@@ -417,6 +416,18 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def describe_sharding(world: int, module) -> str:
+    """One line for `config.parallelism`: what the sharded module settled on."""
+    head = f"pair rows sharded over {world} GPUs, transport {module.transport}, contraction by {module.contraction}: "
+    if module.contraction == "channels":
+        return head + ("prologue and contraction store each tile into the GPU that needs it (channel groups out, "
+                       "row blocks back)")
+    if module.transport == "p2p":
+        return head + ("outgoing = prologue writes `right` into every GPU's copy, incoming = partial sums over the "
+                       "local rows k + reduce kernel reading the peers")
+    return head + "outgoing = all-gather of `right`, incoming = partial sums + reduce-scatter"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -425,6 +436,8 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--workload", default="crop768", choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--contraction", choices=["auto", "rows", "channels"], default="auto",
+                    help="several GPUs: how the contraction is split (auto: channels from 4 GPUs on)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

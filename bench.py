@@ -134,7 +134,8 @@ def run_reference(args):
     sample = f"{steps} x (outgoing + incoming forward) of the full {args.workload} workload, median"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "warmup": warm, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "B": w.B, "N": w.N, "d_pair": 128, "d_hidden": 128,
                    "step": "outgoing + incoming forward", "cells_per_step": 2 * synthetic.cells(w)},

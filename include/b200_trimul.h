@@ -18,7 +18,7 @@
  *    pointers. Calls are asynchronous on `cuda_stream` and may be issued from any host thread.
  *  - Return value: 0 on success, a negative B200_TRIMUL_E_* code otherwise. Device-side waits are
  *    bounded; if one runs out the kernels finish, and `b200_trimul_read_status` reports a positive
- *    device code (101 producer, 102 MMA issuer, 103 epilogue, 104 statistics, 105 drain).
+ *    device code (101 producer, 102 MMA issuer, 103 epilogue, 104 statistics, 105 drain, 106 barrier between GPUs).
  *  - Intermediate layout ("row-plane"): left / right / tri are [B, rows, 128, N] fp16, i.e. for every
  *    pair row a [channel, column] slab. fp16 (same tensor-core rate as bf16, three more mantissa bits)
  *    is what keeps the bf16 module output inside its max-abs bound; tri holds t * 2^-4, saturated to
@@ -149,6 +149,19 @@ int b200_trimul_reduce_partials(void* tri, const void* const* partials, int n_sr
  * b200_trimul_epilogue_groups: stage 3 for this GPU's rows; tri_groups is its [P, rows, 128/P, N] buffer, complete
  *   once every GPU's stage 2 has finished; z / y: [rows, N, 128] bf16.
  */
+/*
+ * Barrier between the GPUs of a multi-GPU run, on the stream: everything this GPU enqueued before the call has
+ * completed, and every other GPU has reached its call with the same `epoch`, before anything enqueued after it
+ * starts. flags[r] (r < world <= 8) is GPU r's flag array (int32[8], zeroed once before the first barrier) as
+ * mapped into this process (flags[rank] is this GPU's own). `epoch` grows by one per barrier. One tiny kernel: it
+ * writes `epoch` into slot `rank` of every peer's array and polls its own array until every peer's slot has reached
+ * `epoch`; after `timeout_ms` of waiting it gives up, records device code 106 in `status` and returns, so the
+ * context stays usable. No reference counterpart; replaces a one-element NCCL all-reduce (about 20 us) where the
+ * data itself already moves through peer memory.
+ */
+int b200_trimul_peer_barrier(int* const* flags, int rank, int world, int epoch, int timeout_ms, int* status,
+                             void* cuda_stream);
+
 int b200_trimul_prologue_channels(const void* z, const void* packed, const uint8_t* token_mask, void* const* left_groups,
                                   void* const* right_groups, int groups, int N, int row_begin, int rows, float eps_in,
                                   int has_bias, int* status, void* cuda_stream);

@@ -60,6 +60,10 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],
     ),
+    "b200_trimul_peer_barrier": (
+        c_int,
+        [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
     "b200_trimul_epilogue": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],

@@ -22,6 +22,7 @@ enum DeviceStatus : int {
   kDevTimeoutEpilogue = 103,
   kDevTimeoutStats = 104,
   kDevTimeoutDrain = 105,
+  kDevTimeoutPeerBarrier = 106,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

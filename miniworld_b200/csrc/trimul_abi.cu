@@ -162,6 +162,31 @@ __global__ void __launch_bounds__(512) reduce_partials_kernel(const ReduceSrc sr
   }
 }
 
+// Barrier between GPUs through flag arrays in peer memory (see b200_trimul_peer_barrier). Thread t talks to GPU t.
+struct PeerFlags {
+  int* p[8];
+};
+
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerFlags f, int rank, int world, int epoch,
+                                                          long long limit_cycles, int* status) {
+  const int t = threadIdx.x;
+  if (t >= world || t == rank) return;
+  // the kernels before this one on the stream have completed, so their stores to peer memory have been performed
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f.p[t] + rank), "r"(epoch) : "memory");
+  const int* mine = f.p[rank] + t;
+  const long long t0 = clock64();
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v >= epoch) break;
+    if (clock64() - t0 > limit_cycles) {  // bounded: report and leave, the context stays usable
+      atomicCAS(status, 0, kDevTimeoutPeerBarrier);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host helpers
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -314,6 +339,7 @@ const char* b200_trimul_strerror(int code) {
     case kDevTimeoutEpilogue: return "device: epilogue gave up waiting";
     case kDevTimeoutStats: return "device: statistics warps gave up waiting";
     case kDevTimeoutDrain: return "device: copies still in flight at exit";
+    case kDevTimeoutPeerBarrier: return "device: barrier between GPUs gave up waiting for a peer";
     default: return "unknown status";
   }
 }
@@ -642,6 +668,26 @@ int b200_trimul_contract_channels(const void* left_group, const void* right_grou
   if (groups < 1 || groups > kMaxOwners || kC % groups != 0) return B200_TRIMUL_E_SHAPE;
   return contract_impl(left_group, right_group, nullptr, tri_owners, groups, group, kC / groups, 1, N, 0, N, N, direction,
                        status, cuda_stream);
+}
+
+int b200_trimul_peer_barrier(int* const* flags, int rank, int world, int epoch, int timeout_ms, int* status,
+                             void* cuda_stream) {
+  if (!flags || !status) return B200_TRIMUL_E_NULL;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || timeout_ms < 1) return B200_TRIMUL_E_SHAPE;
+  DeviceInfo info;
+  int rc = device_info(&info);
+  if (rc != B200_TRIMUL_OK) return rc;
+  PeerFlags f;
+  for (int r = 0; r < 8; ++r) {
+    f.p[r] = r < world ? flags[r] : nullptr;
+    if (r < world && !f.p[r]) return B200_TRIMUL_E_NULL;
+  }
+  // SM clock cycles at the nominal maximum clock of a B200 (1965 MHz); querying the clock attribute costs about a
+  // millisecond per call, and the limit only has to be of the right order
+  const long long limit = static_cast<long long>(timeout_ms) * 1965000ll;
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(f, rank, world, epoch, limit, status);
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
 }
 
 int b200_trimul_reduce_partials(void* tri, const void* const* partials, int n_src, int N, int row_begin, int rows,

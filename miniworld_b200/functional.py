@@ -327,6 +327,17 @@ def epilogue_groups(
     _lib.check(rc, "b200_trimul_epilogue_groups")
 
 
+def peer_barrier(flags: list, rank: int, epoch: int, status: torch.Tensor, timeout_ms: int = 2000) -> None:
+    """Stream-ordered barrier between the GPUs of a run: ``flags[r]`` is GPU r's int32[8] flag array as mapped into this
+    process (zeroed once), ``epoch`` grows by one per barrier. A wait that runs out records device code 106 in
+    ``status`` (see :func:`check_status`) instead of hanging."""
+    arr = _ptr_array(flags)
+    dev = flags[rank].device
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200_trimul_peer_barrier(arr, rank, len(flags), epoch, int(timeout_ms), _ptr(status), _stream(dev))
+    _lib.check(rc, "b200_trimul_peer_barrier")
+
+
 def read_status(status: torch.Tensor) -> int:
     """Synchronise the current stream and return the device status word (0 = ok)."""
     out = c_int(0)

@@ -24,9 +24,10 @@ Neither is present in the reference (it only has data-parallel training):
   Two transports. ``"p2p"``: the kernels themselves use the other GPUs' memory (buffers from torch's symmetric
   memory, mapped into every process) - the prologue's and the contraction's TMA stores write each tile into the
   buffer of the GPU that needs it as the tile is produced, and (row scheme, incoming) a reduce kernel reads the
-  peers' partial sums with plain loads; the only collective left is a one-element all-reduce that orders "my
-  kernel has finished" before "the peers read / I read". No kernel waits on another GPU, and no load is a multicast
-  load. Two sets of buffers alternate between calls, so a rank that runs ahead writes the set its peers are not
+  peers' partial sums with plain loads; between the stages a one-thread-per-peer barrier kernel exchanges epoch
+  flags through the same peer memory (bounded wait: it reports through the status word instead of hanging) to
+  order "my kernel has finished" before "the peers read / I read". No compute kernel waits on another GPU, and no
+  load is a multicast load. Two sets of buffers alternate between calls, so a rank that runs ahead writes the set its peers are not
   reading. ``"nccl"`` (row scheme only): ``all_gather_into_tensor`` / ``reduce_scatter_tensor`` between the
   kernels; the row-plane layout [rows, H, N] makes the gathered tensor [P, N/P, H, N] == [N, H, N] with no
   repacking, and the partial-sum tensor splits into the ranks' row blocks the same way.
@@ -106,6 +107,8 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
         self._bufs = None
         self._sym = None
         self._calls = 0
+        self._epoch = 0
+        self.barrier_timeout_ms = 2000
 
     # ------------------------------------------------------------------ buffers
     def _symmetric(self, N: int, world: int, device: torch.device):
@@ -130,8 +133,13 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
         else:
             shapes = {"full": (1, N, D, N)}  # gathered `right` (outgoing) or the partial sums (incoming)
         ok = torch.ones(1, device=device)
-        sets, owners = [], []
+        sets, owners, flags = [], [], None
         try:
+            t = symm_mem.empty(8, dtype=torch.int32, device=device)
+            t.zero_()
+            hdl = symm_mem.rendezvous(t, group)
+            owners.append((t, hdl))
+            flags = [hdl.get_buffer(r, (8,), torch.int32) for r in range(world)]
             for _ in range(2):
                 views = {}
                 for name, shape in shapes.items():
@@ -153,9 +161,17 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
             self.contraction = "rows"
             self._sym = None
             return None
+        # (the all-reduce above also orders every rank's zeroing of its flags before any peer's first barrier)
         self.transport = "p2p"
+        self._flags = flags
+        self._epoch = 0
         self._sym = ((N, device), sets, owners)
         return sets
+
+    def _barrier(self, rank: int, status: torch.Tensor) -> None:
+        """Everything enqueued so far has finished on every GPU before anything enqueued next starts."""
+        self._epoch += 1
+        F_.peer_barrier(self._flags, rank, self._epoch, status, self.barrier_timeout_ms)
 
     def _scratch(self, N: int, rows: int, device: torch.device):
         key = (N, rows, device)
@@ -165,7 +181,6 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
             channels = self.contraction == "channels"
             gather = nccl and (self.outgoing or self.incoming_scheme == "gather")
             bufs = dict(
-                flag=torch.zeros(1, device=device),
                 packed=F_.aligned_empty(F_.packed_bytes(), device),
                 status=torch.zeros(16, dtype=torch.int32, device=device),
                 left=None if channels else plane(rows),
@@ -210,10 +225,10 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
             self._calls += 1
             if self.contraction == "channels":
                 F_.prologue_channels(z, b["packed"], bufs["left"], bufs["right"], b["status"], **pro)
-                dist.all_reduce(b["flag"], group=self.group)  # every rank's rows have landed in every group's operands
+                self._barrier(rank, b["status"])  # every rank's rows have landed in every group's operands
                 F_.contract_channels(bufs["left"][rank], bufs["right"][rank], bufs["tri"], rank, b["status"], N,
                                      self.outgoing)
-                dist.all_reduce(b["flag"], group=self.group)  # every group's result has landed at the row owners
+                self._barrier(rank, b["status"])  # every group's result has landed at the row owners
                 F_.epilogue_groups(bufs["tri"][rank], z, b["packed"], y, b["status"], world, **epi)
             else:
                 self._tri_p2p(z, b, bufs["full"], pro, N, begin, rows, world, rank)
@@ -228,12 +243,12 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
         if self.outgoing:
             peers = [views[r] for r in range(world) if r != rank]
             F_.prologue_push(z, b["packed"], b["left"], mine, peers, b["status"], **pro)
-            dist.all_reduce(b["flag"], group=self.group)  # every rank's stores have landed in every copy
+            self._barrier(rank, b["status"])  # every rank's stores have landed in every copy
             F_.contract(b["left"], mine, b["tri"], b["status"], 1, N, begin, rows, True)
         else:
             F_.prologue(z, b["packed"], b["left"], b["right"], b["status"], **pro)
             F_.contract_partial(b["left"], b["right"], mine, b["status"], 1, N, rows)
-            dist.all_reduce(b["flag"], group=self.group)  # every rank's partial sums are complete
+            self._barrier(rank, b["status"])  # every rank's partial sums are complete
             F_.reduce_partials(b["tri"], views, N, begin, rows)  # rank order: the same sum on every run
 
     def _tri_nccl(self, z, b, pro, N, begin, rows) -> None:

@@ -59,3 +59,23 @@ def test_channel_sharded_shape_errors():
         F_.contract_channels(t, t, [t, t, t], 0, st, 256, True)
     with pytest.raises(RuntimeError):  # N / P = 40 is not a multiple of 32
         F_.contract_channels(t, t, [t] * 8, 0, st, 320, True)
+
+
+def test_peer_barrier_passes_when_the_peer_has_arrived_and_times_out_otherwise():
+    """The barrier between GPUs, with local arrays standing in for the peer's: it publishes this GPU's epoch, returns
+    at once when the peer's epoch is already there, and a wait that nothing ends runs out after the given limit
+    with device code 106 in the status word - the context stays usable."""
+    mine = torch.zeros(8, dtype=torch.int32, device=DEV)
+    peer = torch.zeros(8, dtype=torch.int32, device=DEV)
+    st = torch.zeros(16, dtype=torch.int32, device=DEV)
+    mine[1] = 3  # the "peer" (rank 1) reached epoch 3 earlier
+    F_.peer_barrier([mine, peer], 0, 3, st, timeout_ms=1000)
+    assert F_.read_status(st) == 0
+    assert int(peer[0]) == 3  # this GPU's arrival, written into the peer's array
+    F_.peer_barrier([mine, peer], 0, 4, st, timeout_ms=5)  # nobody writes epoch 4 into mine[1]
+    assert F_.read_status(st) == 106
+    with pytest.raises(RuntimeError, match="barrier between GPUs"):
+        F_.check_status(st, "peer barrier")
+    st.zero_()
+    x = torch.ones(4, device=DEV) * 2  # the context still works
+    assert float(x.sum()) == 8.0

@@ -120,7 +120,7 @@ def test_contraction_scheme_choice():
 
 
 def _row_sharded_worker(rank, world, port, scheme, ret):
-    outgoing = scheme == "outgoing"
+    outgoing = scheme in ("outgoing", "channels_outgoing")
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -138,7 +138,24 @@ def _row_sharded_worker(rank, world, port, scheme, ret):
         left_loc = full.left[:, begin : begin + rows].permute(0, 1, 3, 2).contiguous()   # row-plane [1, rows, H, N]
         right_loc = full.right[:, begin : begin + rows].permute(0, 1, 3, 2).contiguous()
         right_all = torch.empty(1, N, 128, N)
-        if scheme == "incoming_reduce":
+        if scheme.startswith("channels"):
+            # channel-sharded contraction; all-to-alls stand in for the stores into the destination GPUs' buffers.
+            # stage 1: channel group g of this rank's rows -> rank g, which ends up with [N, 128/P, N] (rows rank-major)
+            cg = 128 // world
+            ops = []
+            for loc in (left_loc, right_loc):
+                send = loc.view(rows, world, cg, N).permute(1, 0, 2, 3).contiguous()  # [group][rows][cg][N]
+                recv = torch.empty(world, rows, cg, N)
+                dist.all_to_all_single(recv, send)
+                ops.append(recv.view(1, N, cg, N))
+            lg, rg = ops
+            # stage 2 on this rank's channel group for ALL rows; row block s of the result -> slab `rank` of rank s
+            tri_c = torch.einsum("bihk,bjhk->bihj", lg, rg) if outgoing else torch.einsum("bkhi,bkhj->bihj", lg, rg)
+            slabs = torch.empty(world, rows, cg, N)
+            dist.all_to_all_single(slabs, tri_c.view(world, rows, cg, N).contiguous())
+            # stage 3 reads [P, rows, 128/P, N]: slab g holds channel group g of this rank's rows
+            tri = slabs.permute(1, 0, 2, 3).reshape(1, rows, 128, N)
+        elif scheme == "incoming_reduce":
             partial = torch.einsum("bkhi,bkhj->bihj", left_loc, right_loc).contiguous()  # all (i, j), own k
             tri = torch.empty(1, rows, 128, N)
             dist.reduce_scatter_tensor(tri.view(rows, 128, N), partial.view(N, 128, N))
@@ -156,11 +173,13 @@ def _row_sharded_worker(rank, world, port, scheme, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("scheme", ["outgoing", "incoming_gather", "incoming_reduce"])
+@pytest.mark.parametrize("scheme", ["outgoing", "incoming_gather", "incoming_reduce", "channels_outgoing",
+                                    "channels_incoming"])
 def test_row_sharded_schedule_on_two_gloo_ranks(scheme):
     """The gathered row-plane tensor is the full operand with no repacking, the partial-sum tensor splits into the
-    ranks' row blocks the same way, and each rank's rows of the contraction equal the unsharded result
-    (world_size 2, gloo, CPU)."""
+    ranks' row blocks the same way, the channel-group buffers [N, 128/P, N] and [P, rows, 128/P, N] of the
+    channel-sharded form hold what stages 2 and 3 expect, and each rank's rows of the contraction equal the
+    unsharded result (world_size 2, gloo, CPU)."""
     world = 2
     port = _free_port()
     with mp.Manager() as mgr:

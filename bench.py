@@ -315,6 +315,10 @@ def run_b200(args):
     barrier()
     ms_e2e = max_over_ranks(time_events(step_e2e, args.steps, stream, before_end=pipe.drain))
     clocks = sampler.stop() if rank == 0 else None
+    for name, m in mods.items():  # a device-side wait that gave up (bounded waits) must not pass as a result
+        code = m.device_status()
+        if code != 0:
+            raise SystemExit(f"{name} forward reported device status {code}")
 
     # ---- per-stage timing for the roofline (single GPU only: a second K-step loop with events per stage)
     roofline = None

@@ -155,6 +155,13 @@ class TriangleMultiplication(nn.Module):
     def load_openfold_state_dict(self, sd: dict, strict: bool = True):
         return self.load_state_dict(from_openfold_state_dict(sd), strict=strict)
 
+    def device_status(self) -> int:
+        """Synchronise and return the device status word of the last forward: 0, or the 1xx code of a device-side wait
+        that gave up (:func:`miniworld_b200.functional.check_status` raises on it)."""
+        if self._workspace is None:
+            return 0
+        return F_.read_status(self._workspace[:64].view(torch.int32))
+
     def _get_workspace(self, B: int, N: int, device: torch.device) -> torch.Tensor:
         need = F_.workspace_bytes(B, N, self.outgoing)
         ws = self._workspace

@@ -193,6 +193,11 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
             self._bufs = (key, bufs)
         return self._bufs[1]
 
+    def device_status(self) -> int:
+        """Synchronise and return the device status word of the last forward (0, or a 1xx code: 106 = the barrier
+        between GPUs gave up waiting for a peer)."""
+        return 0 if self._bufs is None else F_.read_status(self._bufs[1]["status"])
+
     # ------------------------------------------------------------------ forward
     def forward(self, pair_rows: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         if torch.is_grad_enabled() and pair_rows.requires_grad:

@@ -95,6 +95,25 @@ def test_mask_keeps_output_gate_and_custom_eps(outgoing):
     assert float(upd.abs().max()) > 1e-3
 
 
+@pytest.mark.parametrize("outgoing", [True, False])
+def test_batched_forward_equals_the_per_sample_loop_and_is_deterministic(outgoing):
+    """Samples of a batch are independent (the reference checks batched templates against the per-template loop,
+    tests/test_template_embedder_batching.py:92-104): the batched forward equals the loop bit for bit, and a
+    second call gives the same bits."""
+    p = rand_params(33)
+    m = _module(p, outgoing)
+    g = torch.Generator().manual_seed(34)
+    B, N = 3, 136
+    z = torch.randn(B, N, N, 128, generator=g).to(torch.bfloat16).to(DEV)
+    mask = (torch.rand(B, N, generator=g) > 0.2).to(DEV)
+    with torch.no_grad():
+        y = m(z, mask)
+        again = m(z, mask)
+        loop = torch.cat([m(z[b : b + 1].contiguous(), mask[b : b + 1].contiguous()) for b in range(B)])
+    assert torch.equal(y, again)
+    assert torch.equal(y, loop)
+
+
 def test_zero_gamma_rows():
     """Every third LayerNorm gamma = 0 (docs/archive/engine2-validation-20260923/validate_bidir_reference.py:20-22)."""
     p = rand_params(25)

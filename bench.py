@@ -5,8 +5,11 @@
 Metric: pair cells per second through a TriMul module forward (B*N^2 cells per forward). One step is one
 outgoing forward followed by one incoming forward of the same seeded pair tensor (two module forwards,
 2*B*N^2 cells). At one GPU the workload is the N = 768 inference crop; at N > 1 GPUs (torchrun, one rank per
-GPU) the same pair tensor is row-sharded over the ranks with NCCL all-gathers of the contracted operands, so
-scaling is strong. Rank 0 prints ONE JSON line.
+GPU) the same pair tensor is sharded by rows over the ranks (the kernels store into the other GPUs' buffers
+through peer memory; NCCL collectives only where peer memory cannot be mapped), so scaling is strong; a batched
+workload (`--workload batch8x256`) is split by samples instead. Every multi-GPU line carries `parity`: each rank's
+rows compared with the single-GPU forward of the whole tensor. `extra` holds shorter runs of the other benchmark
+workloads. Rank 0 prints ONE JSON line.
 
 `--impl reference` times the CPU restatement of the reference module (the reference's own implementation
 lives in an un-vendored wheel and cannot be installed offline) on the host cores, on the same workload.
@@ -135,7 +138,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": t * 1e3, "higher_is_better": True,
-        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "B": w.B, "N": w.N, "d_pair": 128, "d_hidden": 128,
                    "step": "outgoing + incoming forward", "cells_per_step": 2 * synthetic.cells(w)},
@@ -204,12 +207,134 @@ class HostPipeline:
         torch.cuda.current_stream(self.dev).wait_event(ev)
 
 
+REPEATS = 5  # every timed K-step region is measured this many times; the median is reported, min and max beside it
+
+
+def _stats(ms_list, steps):
+    per = sorted(m / steps for m in ms_list)
+    return {"median": statistics.median(per), "min": per[0], "max": per[-1], "repeats": len(per)}
+
+
+class Runner:
+    """One workload set up on this rank: the modules, the resident input and the two step functions."""
+
+    def __init__(self, name, world, rank, dev, contraction="auto", on_device=False):
+        import miniworld_b200 as mw
+        from miniworld_b200 import sharded
+
+        self.name, self.world, self.rank, self.dev = name, world, rank, dev
+        if on_device:
+            # large extra workloads: drawn on the device from a fixed seed (the same values on every rank); they are
+            # only compared between this repository's own single-GPU and multi-GPU forwards, never with the CPU oracle
+            B, N, _, _ = synthetic.WORKLOADS[name]
+            gen = torch.Generator(device=dev).manual_seed(1234)
+            cpu_gen = torch.Generator().manual_seed(1234)
+            params = synthetic.make_params(cpu_gen)
+            z_full = torch.randn(B, N, N, 128, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            mask = torch.rand(B, N, generator=gen, device=dev) >= 0.05
+            self.w = synthetic.Workload(name=name, z=z_full, mask=mask, params=params, directions=("outgoing", "incoming"), B=B, N=N)
+        else:
+            self.w = synthetic.make_workload(name, seed=0)
+        w = self.w
+        self.B, self.N = w.B, w.N
+        self.cells_per_step = 2 * synthetic.cells(w)
+        self.mods = {}
+        if world == 1:
+            self.kind = "single"
+            self.parallelism = "single GPU"
+            sl = (slice(None), slice(None))
+        elif w.B > 1:
+            # batch data parallelism: samples are independent, so every rank runs its own samples with the ordinary
+            # module and nothing crosses the links
+            self.kind = "batch"
+            b0, cnt = sharded.shard_batch(w.B, world, rank)
+            self.parallelism = f"batch of {w.B} samples split over {world} GPUs (replicas, no collective)"
+            sl = (slice(b0, b0 + cnt), slice(None))
+            self.local_samples = cnt
+        else:
+            self.kind = "rows"
+            begin, rows = sharded.row_range(w.N, world, rank)
+            sl = (slice(None), slice(begin, begin + rows))
+            self.begin, self.rows = begin, rows
+        for direction in ("outgoing", "incoming"):
+            if self.kind == "rows":
+                m = sharded.RowShardedTriangleMultiplication(128, outgoing=(direction == "outgoing"), contraction=contraction)
+            else:
+                m = mw.TriangleMultiplication(128, outgoing=(direction == "outgoing"))
+            m.load_state_dict(w.params)
+            self.mods[direction] = m.to(dev).to(torch.bfloat16).eval()
+        z_local = w.z[sl[0], sl[1]].contiguous()
+        self.mask = (w.mask if self.kind != "batch" else w.mask[sl[0]]).to(dev)
+        self.empty = z_local.shape[0] == 0
+        if on_device:
+            self.z_host = None
+            self.z = z_local
+        else:
+            self.z_host = z_local.pin_memory()
+            self.z = self.z_host.to(dev, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def step(self):
+        if self.empty:
+            return None
+        with torch.no_grad():
+            self.mods["outgoing"](self.z, self.mask)
+            return self.mods["incoming"](self.z, self.mask)
+
+    def forward_pair(self, zd):
+        with torch.no_grad():
+            self.mods["outgoing"](zd, self.mask)
+            return self.mods["incoming"](zd, self.mask)
+
+    def check_status(self):
+        for name, m in self.mods.items():  # a device-side wait that gave up (bounded waits) must not pass as a result
+            code = m.device_status()
+            if code != 0:
+                raise SystemExit(f"{self.name}: {name} forward reported device status {code}")
+
+    def describe(self):
+        if self.kind == "rows":
+            return describe_sharding(self.world, self.mods["outgoing"])
+        return self.parallelism
+
+    def launches_per_step(self):
+        """This repository's kernels per step: (pack, prologue, contraction, epilogue) x 2 directions; on several GPUs
+        the barrier kernels between the stages and, row scheme, the reduce kernel of the incoming direction."""
+        if self.kind != "rows":
+            return 8
+        m = self.mods["outgoing"]
+        if m.transport != "p2p":
+            return 8
+        return 8 + 4 if m.contraction == "channels" else 8 + 2 + 1
+
+    def parity(self):
+        """Several GPUs, pair rows sharded: this rank's rows of the sharded forward against the same rows of the
+        single-GPU forward of the whole tensor, run here on this GPU. Returns {direction: (bit_identical, max_abs)}."""
+        import miniworld_b200 as mw
+
+        out = {}
+        w = self.w
+        zf = w.z.to(self.dev)
+        mf = w.mask.to(self.dev)
+        for direction in ("outgoing", "incoming"):
+            full = mw.TriangleMultiplication(128, outgoing=(direction == "outgoing"))
+            full.load_state_dict(w.params)
+            full = full.to(self.dev).to(torch.bfloat16).eval()
+            with torch.no_grad():
+                want = full(zf, mf)[:, self.begin : self.begin + self.rows]
+                got = self.mods[direction](self.z, self.mask)
+            torch.cuda.synchronize()
+            same = bool(torch.equal(got, want))
+            err = float((got.float() - want.float()).abs().max())
+            del full, want, got
+            out[direction] = (same, err)
+        return out
+
+
 def run_b200(args):
     import torch.distributed as dist
 
-    import miniworld_b200 as mw
     from miniworld_b200 import functional as F_
-    from miniworld_b200 import sharded
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -222,68 +347,7 @@ def run_b200(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-
-    w = synthetic.make_workload(args.workload, seed=0)
-    B, N = w.B, w.N
-    cells_per_step = 2 * synthetic.cells(w)
     stream = torch.cuda.current_stream(dev)
-
-    if world == 1:
-        mods = {}
-        for direction in ("outgoing", "incoming"):
-            m = mw.TriangleMultiplication(128, outgoing=(direction == "outgoing"))
-            m.load_state_dict(w.params)
-            mods[direction] = m.to(dev).to(torch.bfloat16).eval()
-        z_host = w.z.contiguous().pin_memory()
-        mask = w.mask.to(dev)
-        z = z_host.to(dev, non_blocking=True)
-        y_host = torch.empty_like(z_host).pin_memory()
-        torch.cuda.synchronize()
-
-        def step():
-            with torch.no_grad():
-                mods["outgoing"](z, mask)
-                return mods["incoming"](z, mask)
-
-        def forward_pair(zd):
-            with torch.no_grad():
-                mods["outgoing"](zd, mask)
-                return mods["incoming"](zd, mask)
-
-        pipe = HostPipeline(z_host, y_host, forward_pair, dev)
-        step_e2e = pipe.step
-
-        h2d = z_host.numel() * 2
-        d2h = y_host.numel() * 2
-    else:
-        begin, rows = sharded.row_range(N, world, rank)
-        mods = {}
-        for direction in ("outgoing", "incoming"):
-            m = sharded.RowShardedTriangleMultiplication(128, outgoing=(direction == "outgoing"),
-                                                         contraction=args.contraction)
-            m.load_state_dict(w.params)
-            mods[direction] = m.to(dev).to(torch.bfloat16).eval()
-        z_host = w.z[:, begin : begin + rows].contiguous().pin_memory()
-        mask = w.mask.to(dev)
-        z = z_host.to(dev, non_blocking=True)
-        y_host = torch.empty_like(z_host).pin_memory()
-        torch.cuda.synchronize()
-
-        def step():
-            with torch.no_grad():
-                mods["outgoing"](z, mask)
-                return mods["incoming"](z, mask)
-
-        def forward_pair(zd):
-            with torch.no_grad():
-                mods["outgoing"](zd, mask)
-                return mods["incoming"](zd, mask)
-
-        pipe = HostPipeline(z_host, y_host, forward_pair, dev)
-        step_e2e = pipe.step
-
-        h2d = z_host.numel() * 2
-        d2h = y_host.numel() * 2
 
     def barrier():
         if world > 1:
@@ -297,150 +361,238 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- kernel-resident timing (inputs already in HBM)
+    def timed(fn, steps, before_end=None):
+        """REPEATS measurements of `steps` calls of fn: barrier + synchronize on both sides, CUDA events on the
+        launching stream, the maximum over the ranks for each measurement."""
+        out = []
+        for _ in range(REPEATS):
+            barrier()
+            ms = time_events(fn, steps, stream, before_end=before_end)
+            barrier()
+            out.append(max_over_ranks(ms))
+        return out
+
+    def measure(r: Runner, steps: int, warmup: int, with_graph: bool):
+        for _ in range(max(warmup, 3)):
+            r.step()
+        eager = _stats(timed(r.step, steps), steps)
+        res = {"eager": eager, "ms_per_step": eager["median"], "launch": "eager launches from the module's forward"}
+        if with_graph and not r.empty:
+            # the same K steps replayed from a CUDA graph of one step (same kernels, same arguments): the gaps between
+            # the launches of a step shrink from host-paced to device-paced
+            try:
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(stream)
+                with torch.cuda.stream(side):
+                    r.step()
+                stream.wait_stream(side)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    r.step()
+                for _ in range(3):
+                    graph.replay()
+                g = _stats(timed(graph.replay, steps), steps)
+                res["graph"] = g
+                if g["median"] < res["ms_per_step"]:
+                    res["ms_per_step"], res["launch"] = g["median"], "CUDA graph replay of one step (two module forwards)"
+            except RuntimeError as exc:  # capture not possible in this set-up: keep the eager figure
+                res["launch"] += f" (graph capture failed: {type(exc).__name__})"
+        r.check_status()
+        return res
+
+    def parity_line(r: Runner):
+        """Multi-GPU output parity against the single-GPU forward, agreed over the ranks; raises on a violation."""
+        if r.kind != "rows":
+            return None
+        par = r.parity()
+        line = {}
+        for direction, (same, err) in par.items():
+            t = torch.tensor([0.0 if same else 1.0, err], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            all_same, worst = t[0].item() == 0.0, float(t[1].item())
+            m = r.mods[direction]
+            # same kernels and k order -> bit-identical, except the row scheme's incoming direction, whose partial sums
+            # are rounded to fp16 once per GPU: two bf16 spacings of the output at most (|y| < 8 for this input)
+            exact_expected = direction == "outgoing" or m.contraction == "channels" or m.incoming_scheme == "gather"
+            line[direction] = "bit-identical" if all_same else worst
+            if (exact_expected and not all_same) or worst > 0.0625:
+                raise SystemExit(f"{r.name}: multi-GPU {direction} output differs from the single-GPU forward "
+                                 f"(max abs {worst}, bit-identical expected: {exact_expected})")
+        return line
+
+    # ---- headline workload
+    r = Runner(args.workload, world, rank, dev, contraction=args.contraction)
+    B, N = r.B, r.N
     for _ in range(max(args.warmup, 3)):
-        step()
+        r.step()
     barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank)  # samples clocks and throttle reasons over the timed regions that follow
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    barrier()
-    ms = time_events(step, args.steps, stream)
-    barrier()
-    ms = max_over_ranks(ms)
-    ms_eager = ms
-    launch = "eager launches from the module's forward"
-    if world == 1:
-        # the same K steps replayed from a CUDA graph of one step (same kernels, same arguments): the gaps between the
-        # eight launches of a step shrink from host-paced to device-paced
-        try:
-            side = torch.cuda.Stream(dev)
-            side.wait_stream(stream)
-            with torch.cuda.stream(side):
-                step()
-            stream.wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                step()
-            for _ in range(3):
-                graph.replay()
-            ms_graph = time_events(graph.replay, args.steps, stream)
-            if ms_graph < ms:
-                ms, launch = ms_graph, "CUDA graph replay of one step (two module forwards)"
-        except RuntimeError as exc:  # capture not possible in this set-up: keep the eager figure
-            launch += f" (graph capture failed: {type(exc).__name__})"
+    res = measure(r, args.steps, args.warmup, with_graph=(world == 1))
     # ---- end-to-end timing: host pinned input -> device -> two forwards -> host pinned output, every step
+    y_host = torch.empty_like(r.z_host).pin_memory()
+    pipe = HostPipeline(r.z_host, y_host, r.forward_pair, dev)
     for _ in range(2):
-        step_e2e()
-    barrier()
-    ms_e2e = max_over_ranks(time_events(step_e2e, args.steps, stream, before_end=pipe.drain))
+        pipe.step()
+    e2e = _stats(timed(pipe.step, args.steps, before_end=pipe.drain), args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    for name, m in mods.items():  # a device-side wait that gave up (bounded waits) must not pass as a result
-        code = m.device_status()
-        if code != 0:
-            raise SystemExit(f"{name} forward reported device status {code}")
+    r.check_status()
+    h2d = r.z_host.numel() * 2
+    d2h = y_host.numel() * 2
+    parity = parity_line(r) if world > 1 else None
 
     # ---- per-stage timing for the roofline (single GPU only: a second K-step loop with events per stage)
     roofline = None
     stages_ms = None
     if world == 1:
-        layout = F_.workspace_layout(B, N)
-        ws = F_.aligned_empty(F_.workspace_bytes(B, N), dev)
-        plane = B * N * 128 * N
-        status = ws[:64].view(torch.int32)
-        packed = ws[layout[1] : layout[1] + F_.packed_bytes()]
-        left = ws[layout[2] : layout[2] + plane * 2].view(torch.float16).view(B, N, 128, N)
-        right = ws[layout[3] : layout[3] + plane * 2].view(torch.float16).view(B, N, 128, N)
-        tri = ws[layout[4] : layout[4] + plane * 2].view(torch.float16).view(B, N, 128, N)
-        y = torch.empty_like(z)
-        params = mods["outgoing"]._params()
-        names = ("pack", "prologue", "contract_outgoing", "contract_incoming", "epilogue")
-        acc = {n: 0.0 for n in names}
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
-        for it in range(3 + args.steps):
-            evs[0].record(stream)
-            F_.pack_weights(params, packed)
-            evs[1].record(stream)
-            F_.prologue(z, packed, left, right, status, token_mask=mask)
-            evs[2].record(stream)
-            F_.contract(left, right, tri, status, B, N, 0, N, True)
-            evs[3].record(stream)
-            F_.contract(left, right, tri, status, B, N, 0, N, False)
-            evs[4].record(stream)
-            F_.epilogue(tri, z, packed, y, status)
-            evs[5].record(stream)
-            torch.cuda.synchronize()
-            if it >= 3:
-                for i, n in enumerate(names):
-                    acc[n] += evs[i].elapsed_time(evs[i + 1])
-        F_.check_status(status, "bench stages")
-        stages_ms = {n: v / args.steps for n, v in acc.items()}
-        peaks = measured_peaks()
-        fl = synthetic.flops(B, N)
-        t_contract = 0.5 * (stages_ms["contract_outgoing"] + stages_ms["contract_incoming"])
-        achieved = fl["contraction"] / (t_contract * 1e-3) / 1e12
-        P = synthetic.pass_bytes(B, N)
-        roofline = {
-            "kernel": "contract_pair_kernel" if N >= 256 else "contract_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
-            "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
-            "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
-            "flops_per_launch": fl["contraction"],
-            # dram__bytes_read.sum + dram__bytes_write.sum of one contraction launch, from the ncu capture of this
-            # workload summarised under profiles/; not captured for the other workloads
-            "traffic": 422.9e6 if args.workload == "crop768" else None,
-            "timed": "separate loop of K steps, CUDA events around each stage on the launching stream",
-            "other_kernels": {
-                "prologue_kernel": {"bound": "hbm", "algorithmic_bytes": 3 * P,
-                                    "achieved_gbs": 3 * P / (stages_ms["prologue"] * 1e-3) / 1e9,
-                                    "frac": 3 * P / (stages_ms["prologue"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
-                "epilogue_kernel": {"bound": "hbm", "algorithmic_bytes": 3 * P,
-                                    "achieved_gbs": 3 * P / (stages_ms["epilogue"] * 1e-3) / 1e9,
-                                    "frac": 3 * P / (stages_ms["epilogue"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
-            },
-        }
+        stages_ms, roofline = stage_roofline(r, args.steps, stream, traffic=422.9e6 if args.workload == "crop768" else None)
+
+    # ---- the other benchmark workloads, shorter runs (the headline stays the workload the metric is quoted on)
+    extra = {}
+    if not args.no_extra:
+        names = [n for n in ("n384", "batch8x256", "complex2048") if n != args.workload]
+        for name in names:
+            B2, N2, _, _ = synthetic.WORKLOADS[name]
+            if world > 1 and B2 == 1 and N2 % world != 0:
+                continue
+            if world > 1 and name == "n384":
+                continue  # 48-row slabs at 8 GPUs: below what the sharded kernels take; a single-GPU workload
+            steps2 = max(3, min(args.steps, 10 if name != "complex2048" else 5))
+            r2 = Runner(name, world, rank, dev, contraction=args.contraction, on_device=(name == "complex2048"))
+            m2 = measure(r2, steps2, 3, with_graph=(world == 1))
+            entry = {"B": r2.B, "N": r2.N, "ms_per_step": m2["ms_per_step"], "launch": m2["launch"], "eager": m2["eager"],
+                     "value": r2.cells_per_step / (m2["ms_per_step"] * 1e-3), "unit": UNIT, "steps": steps2,
+                     "parallelism": r2.describe(),
+                     "data": "synthetic, drawn on the device" if name == "complex2048" else "synthetic"}
+            if "graph" in m2:
+                entry["graph"] = m2["graph"]
+            if world == 1:
+                st2, rf2 = stage_roofline(r2, steps2, stream, traffic=None)
+                entry["stages_ms"], entry["roofline"] = st2, rf2
+            else:
+                p2 = parity_line(r2)
+                if p2 is not None:
+                    entry["parity"] = p2
+            extra[name] = entry
+            del r2
+            torch.cuda.empty_cache()
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        t = cpu_forward_pair(w, threads)
-        cpu_baseline = {"value": cells_per_step / t, "unit": UNIT, "cores": threads, "kind": "port",
+        t = cpu_forward_pair(r.w, threads)
+        cpu_baseline = {"value": r.cells_per_step / t, "unit": UNIT, "cores": threads, "kind": "port",
                         "sample": f"1 x (outgoing + incoming forward) of the full {args.workload} workload, fp32 PyTorch oracle",
                         "seconds": t, "torch": torch.__version__}
 
     if rank == 0:
-        t_step = ms / args.steps
-        t_e2e = ms_e2e / args.steps
+        t_step = res["ms_per_step"]
+        t_e2e = e2e["median"]
         line = {
-            "metric": METRIC, "value": cells_per_step / (t_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "metric": METRIC, "value": r.cells_per_step / (t_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t_step,
-            "ms_per_step_eager": ms_eager / args.steps, "launch": launch, "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "ms_per_step_eager": res["eager"]["median"], "launch": res["launch"],
+            "timing": {"repeats": REPEATS, "eager": res["eager"], "graph": res.get("graph"),
+                       "how": "each figure is the median of `repeats` measurements of K steps (CUDA events, barrier and "
+                              "synchronize on both sides, maximum over the ranks per measurement)"},
+            "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "B": B, "N": N, "d_pair": 128, "d_hidden": 128,
                        "step": "outgoing forward + incoming forward (2 module forwards)",
-                       "cells_per_step": cells_per_step,
-                       "parallelism": "single GPU" if world == 1 else describe_sharding(world, mods["outgoing"]),
+                       "cells_per_step": r.cells_per_step,
+                       "parallelism": r.describe(),
                        "l2": "inputs and intermediates (604 MB at N=768) exceed the 126 MB L2; no flush"},
-            "e2e": {"value": cells_per_step / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
+            "e2e": {"value": r.cells_per_step / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
+                    "min": e2e["min"], "max": e2e["max"], "repeats": REPEATS,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "pinned host z -> device, two module forwards, y -> pinned host, every step; two device "
-                           "input buffers so copies overlap the neighbouring steps' kernels"},
-            # this repository's kernels per step: (pack, prologue, contraction, epilogue) x 2 directions, plus the
-            # peer-reading reduce kernel of the incoming direction on the p2p transport
-            "gpu_launches": (9 if world > 1 and mods["outgoing"].transport == "p2p"
-                             and mods["outgoing"].contraction == "rows" else 8) * args.steps,
+                           "input buffers so copies overlap the neighbouring steps' kernels; median of the repeats"},
+            "gpu_launches": r.launches_per_step() * args.steps,
             "clocks": clocks,
         }
+        if parity is not None:
+            line["parity"] = parity
         if stages_ms is not None:
             line["stages_ms"] = stages_ms
         if roofline is not None:
             line["roofline"] = roofline
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
+        if extra:
+            line["extra"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def stage_roofline(r: Runner, steps: int, stream, traffic):
+    """Single GPU: K steps with CUDA events around each stage (called through the staged C-ABI entry points with
+    pointers prepared once), and the roofline figures that follow from the stage times."""
+    from miniworld_b200 import functional as F_
+
+    B, N, dev, z, mask = r.B, r.N, r.dev, r.z, r.mask
+    layout = F_.workspace_layout(B, N)
+    ws = F_.aligned_empty(F_.workspace_bytes(B, N), dev)
+    plane = B * N * 128 * N
+    status = ws[:64].view(torch.int32)
+    packed = ws[layout[1] : layout[1] + F_.packed_bytes()]
+    left = ws[layout[2] : layout[2] + plane * 2].view(torch.float16).view(B, N, 128, N)
+    right = ws[layout[3] : layout[3] + plane * 2].view(torch.float16).view(B, N, 128, N)
+    tri = ws[layout[4] : layout[4] + plane * 2].view(torch.float16).view(B, N, 128, N)
+    y = torch.empty_like(z)
+    params = r.mods["outgoing"]._params()
+    names = ("pack", "prologue", "contract_outgoing", "contract_incoming", "epilogue")
+    acc = {n: 0.0 for n in names}
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+    status.zero_()
+    for it in range(3 + steps):
+        evs[0].record(stream)
+        F_.pack_weights(params, packed)
+        evs[1].record(stream)
+        F_.prologue(z, packed, left, right, status, token_mask=mask)
+        evs[2].record(stream)
+        F_.contract(left, right, tri, status, B, N, 0, N, True)
+        evs[3].record(stream)
+        F_.contract(left, right, tri, status, B, N, 0, N, False)
+        evs[4].record(stream)
+        F_.epilogue(tri, z, packed, y, status)
+        evs[5].record(stream)
+        torch.cuda.synchronize()
+        if it >= 3:
+            for i, n in enumerate(names):
+                acc[n] += evs[i].elapsed_time(evs[i + 1])
+    F_.check_status(status, "bench stages")
+    stages_ms = {n: v / steps for n, v in acc.items()}
+    stages_ms["note"] = ("each stage is launched by its own Python call between two events, so a stage shorter than the "
+                         "call's host cost (about 30 us: pack) shows the host cost, not the kernel")
+    peaks = measured_peaks()
+    fl = synthetic.flops(B, N)
+    t_contract = 0.5 * (stages_ms["contract_outgoing"] + stages_ms["contract_incoming"])
+    achieved = fl["contraction"] / (t_contract * 1e-3) / 1e12
+    P = synthetic.pass_bytes(B, N)
+    roofline = {
+        "kernel": "contract_pair_kernel" if N >= 256 else "contract_kernel", "bound": "tensor", "achieved": achieved,
+        "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+        "peak_source": peaks["source"] + " (burst)",
+        "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
+        "flops_per_launch": fl["contraction"],
+        # dram__bytes_read.sum + dram__bytes_write.sum of one contraction launch, from the ncu capture of the crop768
+        # workload summarised under profiles/; not captured for the other workloads
+        "traffic": traffic,
+        "timed": "separate loop of K steps, CUDA events around each stage on the launching stream",
+        "other_kernels": {
+            "prologue_kernel": {"bound": "hbm", "algorithmic_bytes": 3 * P,
+                                "achieved_gbs": 3 * P / (stages_ms["prologue"] * 1e-3) / 1e9,
+                                "frac": 3 * P / (stages_ms["prologue"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+            "epilogue_kernel": {"bound": "hbm", "algorithmic_bytes": 3 * P,
+                                "achieved_gbs": 3 * P / (stages_ms["epilogue"] * 1e-3) / 1e9,
+                                "frac": 3 * P / (stages_ms["epilogue"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+        },
+    }
+    return stages_ms, roofline
 
 
 def describe_sharding(world: int, module) -> str:
@@ -463,6 +615,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--workload", default="crop768", choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the shorter runs of the other benchmark workloads")
     ap.add_argument("--contraction", choices=["auto", "rows", "channels"], default="auto",
                     help="several GPUs: how the contraction is split (auto: channels from 4 GPUs on)")
     args = ap.parse_args()

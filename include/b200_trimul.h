@@ -14,8 +14,17 @@
  *  - d_pair = d_hidden = 128 is the only supported width (B200_TRIMUL_E_UNSUPPORTED otherwise).
  *    N must be a multiple of 8 (16-byte rows for the bulk copies); callers pad with masked tokens.
  *  - The caller owns every buffer, including the workspace; the library never allocates or frees
- *    device memory and keeps no mutable global state besides a per-process cache of two function
- *    pointers. Calls are asynchronous on `cuda_stream` and may be issued from any host thread.
+ *    device memory. Its only process-wide state is a set of caches that are filled on first use and
+ *    never change afterwards (a driver entry point, the SM count of each device, which kernels have had
+ *    their shared-memory size enabled on which device) plus, for b200_trimul_forward_static alone, one
+ *    fixed scratch array per GPU and its cached device address. Calls are asynchronous on `cuda_stream`
+ *    and may be issued from any host thread.
+ *  - Magnitudes: left / right and the normalised input are rounded to fp16 with saturation (a value past
+ *    +-65504 becomes +-65504, never infinity), tri likewise after its 2^-4 scaling, so the output stays
+ *    finite for any finite input; results match the fp32 module to the stated bounds while
+ *    |sigmoid(g) * p| < 65504 and |t| < 2^20, which holds with a wide margin for LayerNorm-ed activations.
+ *    Linear weights are held as fp16(0.5 W): entries below about 1.2e-7 in magnitude flush to zero and
+ *    entries below 1.2e-4 lose precision gradually (fp16 subnormals).
  *  - Return value: 0 on success, a negative B200_TRIMUL_E_* code otherwise. Device-side waits are
  *    bounded; if one runs out the kernels finish, and `b200_trimul_read_status` reports a positive
  *    device code (101 producer, 102 MMA issuer, 103 epilogue, 104 statistics, 105 drain, 106 barrier between GPUs).
@@ -197,14 +206,16 @@ int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_ga
  * latency-critical loop by synchronising the device), or a plug-in whose host forbids allocation after start-up.
  * It has no counterpart in the reference, whose engine allocates its intermediates through PyTorch.
  *
- * The scratch is a 12.2 MiB array inside the library image, present on every GPU that loads the library until
- * the process exits. Limit: B * N * N <= 16384 pair cells (one 128-token sample, four 64-token samples, ...);
+ * The scratch is a fixed 12.2 MiB device array that belongs to the library's module: it takes no space in the
+ * file, and every GPU on which the library's kernels are loaded reserves it until the process exits. Limit: B * N * N <= 16384 pair cells (one 128-token sample, four 64-token samples, ...);
  * anything larger returns B200_TRIMUL_E_TOO_LARGE before any device work is issued. The function itself calls
  * no allocator of any kind. Its first call on a device looks up the array's device address, so make that
  * call before starting a stream capture. Every call on a device uses the same array, which keeps the previous
  * call's contents: the status words are cleared on entry and all other regions are overwritten before they are
  * read, but two calls that overlap on the GPU race on it - issue them on one stream, or serialise them.
  * `device_status_out` (may be null) receives the device address of the status word for b200_trimul_read_status.
+ * The looked-up address is cached per device for the life of the process: after cudaDeviceReset (or any other
+ * teardown of the device's primary context) it is stale and this entry point must not be used again.
  */
 int b200_trimul_forward_static(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
                                const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,

@@ -53,10 +53,8 @@ constexpr float kTriScale = 0.0625f;  // t is stored as t * 2^-4
 
 // two fp32 accumulators -> scaled, saturated fp16 pair
 __device__ __forceinline__ uint32_t pack_tri(uint32_t lo_bits, uint32_t hi_bits) {
-  float2 v = __fmul2_rn(make_float2(__uint_as_float(lo_bits), __uint_as_float(hi_bits)), make_float2(kTriScale, kTriScale));
-  v.x = fminf(fmaxf(v.x, -65504.f), 65504.f);
-  v.y = fminf(fmaxf(v.y, -65504.f), 65504.f);
-  return pack_f16x2(v);
+  return pack_f16x2_sat(
+      __fmul2_rn(make_float2(__uint_as_float(lo_bits), __uint_as_float(hi_bits)), make_float2(kTriScale, kTriScale)));
 }
 
 template <int BN>

@@ -358,6 +358,13 @@ __device__ __forceinline__ uint32_t pack_f16x2(float2 v) {
   __half2 h = __float22half2_rn(v);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// Saturating form: a value beyond the fp16 range becomes +-65504 instead of infinity (one instruction, like the
+// plain conversion), so that a later 0 * x in the contraction cannot produce NaN.
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float2 v) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(v.y), "f"(v.x));
+  return r;
+}
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
 

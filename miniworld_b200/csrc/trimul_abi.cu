@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* pa
       o[t] = __bfloat16_as_ushort(r);
       s += __bfloat162float(r);
     } else {
-      const __half r = __float2half_rn(v);
+      const __half r = __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f));
       o[t] = __half_as_ushort(r);
       s += __half2float(r);
     }
@@ -127,9 +127,7 @@ struct ReduceSrc {
   int n;
 };
 
-__device__ __forceinline__ uint32_t pack_sat(float a, float b) {
-  return pack_f16x2(make_float2(fminf(fmaxf(a, -65504.f), 65504.f), fminf(fmaxf(b, -65504.f), 65504.f)));
-}
+__device__ __forceinline__ uint32_t pack_sat(float a, float b) { return pack_f16x2_sat(make_float2(a, b)); }
 
 __global__ void __launch_bounds__(512) reduce_partials_kernel(const ReduceSrc src, uint4* __restrict__ tri, size_t count) {
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -239,20 +237,58 @@ static int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* 
 struct DeviceInfo {
   int sms;
   int cc_major;
+  int device;
 };
 
+constexpr int kMaxDevices = 64;
+
+// SM count and compute capability of the current device; queried once per device and process.
 static int device_info(DeviceInfo* info) {
+  static std::atomic<int> cached_sms[kMaxDevices];  // 0 = not queried yet
+  static std::atomic<int> cached_cc[kMaxDevices];
   int dev = 0;
   TRIMUL_CUDA(cudaGetDevice(&dev));
-  TRIMUL_CUDA(cudaDeviceGetAttribute(&info->sms, cudaDevAttrMultiProcessorCount, dev));
-  TRIMUL_CUDA(cudaDeviceGetAttribute(&info->cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (dev < 0 || dev >= kMaxDevices) return B200_TRIMUL_E_DEVICE;
+  info->device = dev;
+  int sms = cached_sms[dev].load(std::memory_order_acquire);
+  if (sms == 0) {
+    int cc = 0;
+    TRIMUL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    TRIMUL_CUDA(cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev));
+    cached_cc[dev].store(cc, std::memory_order_relaxed);
+    cached_sms[dev].store(sms, std::memory_order_release);
+  }
+  info->sms = sms;
+  info->cc_major = cached_cc[dev].load(std::memory_order_relaxed);
   if (info->cc_major != 10) return B200_TRIMUL_E_DEVICE;
   return B200_TRIMUL_OK;
 }
 
+// Opt a kernel in to its dynamic shared-memory size, once per kernel and device (the attribute belongs to the
+// function in a device's context; setting it again is harmless, so a benign race between two threads is fine).
 template <typename K>
-static int set_smem(K kernel, int bytes) {
-  TRIMUL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+static int set_smem(K kernel, int bytes, int device) {
+  struct Slot {
+    std::atomic<const void*> fn{nullptr};
+    std::atomic<unsigned long long> devices{0};
+  };
+  static Slot slots[64];
+  const void* key = reinterpret_cast<const void*>(kernel);
+  const unsigned long long bit = 1ull << device;
+  for (Slot& s : slots) {
+    const void* cur = s.fn.load(std::memory_order_acquire);
+    if (cur == nullptr) {
+      const void* expected = nullptr;
+      if (!s.fn.compare_exchange_strong(expected, key, std::memory_order_acq_rel) && expected != key) continue;
+      cur = key;
+    }
+    if (cur != key) continue;
+    if (s.devices.load(std::memory_order_acquire) & bit) return B200_TRIMUL_OK;
+    TRIMUL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    s.devices.fetch_or(bit, std::memory_order_release);
+    return B200_TRIMUL_OK;
+  }
+  TRIMUL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));  // table full
   return B200_TRIMUL_OK;
 }
 
@@ -288,10 +324,11 @@ static int choose_bn(int N) {
 
 template <int BN, bool INCOMING>
 static int launch_contract(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mt, const ContractParams& p,
-                           int sms, cudaStream_t stream) {
+                           const DeviceInfo& info, cudaStream_t stream) {
+  const int sms = info.sms;
   auto kernel = contract_kernel<BN, INCOMING>;
   constexpr int smem = ContractSmem<BN>::kTotal;
-  int rc = set_smem(kernel, smem);
+  int rc = set_smem(kernel, smem, info.device);
   if (rc != B200_TRIMUL_OK) return rc;
   const long long tiles = static_cast<long long>(p.planes) * p.m_tiles * p.n_tiles;
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
@@ -302,10 +339,12 @@ static int launch_contract(const CUtensorMap& ma, const CUtensorMap& mb, const C
 
 template <int BN, bool INCOMING>
 static int launch_contract_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mt,
-                                const TriOwners& own, const ContractParams& p, int sms, cudaStream_t stream) {
+                                const TriOwners& own, const ContractParams& p, const DeviceInfo& info,
+                                cudaStream_t stream) {
+  const int sms = info.sms;
   auto kernel = contract_pair_kernel<BN, INCOMING>;
   constexpr int smem = PairSmem<BN>::kTotal;
-  int rc = set_smem(kernel, smem);
+  int rc = set_smem(kernel, smem, info.device);
   if (rc != B200_TRIMUL_OK) return rc;
   const long long tiles = static_cast<long long>(p.planes) * p.m_tiles * p.n_tiles;
   const long long pairs = tiles < sms / 2 ? tiles : sms / 2;
@@ -505,11 +544,11 @@ static int prologue_impl(const void* z, const void* packed, const uint8_t* token
   const int grid = 2 * pairs;  // clusters of two CTAs: CTA 0 produces `left`, CTA 1 `right`
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (has_bias) {
-    rc = set_smem(prologue_kernel<true>, kProSmemBytes);
+    rc = set_smem(prologue_kernel<true>, kProSmemBytes, info.device);
     if (rc != B200_TRIMUL_OK) return rc;
     prologue_kernel<true><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, out, p);
   } else {
-    rc = set_smem(prologue_kernel<false>, kProSmemBytes);
+    rc = set_smem(prologue_kernel<false>, kProSmemBytes, info.device);
     if (rc != B200_TRIMUL_OK) return rc;
     prologue_kernel<false><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, out, p);
   }
@@ -636,20 +675,20 @@ static int contract_impl(const void* left, const void* right, void* tri, void* c
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (use_pair) {
     if (!incoming) {
-      if (bn == 256) return launch_contract_pair<256, false>(map_a, map_b, map_t, own, p, info.sms, stream);
-      return launch_contract_pair<128, false>(map_a, map_b, map_t, own, p, info.sms, stream);
+      if (bn == 256) return launch_contract_pair<256, false>(map_a, map_b, map_t, own, p, info, stream);
+      return launch_contract_pair<128, false>(map_a, map_b, map_t, own, p, info, stream);
     }
-    if (bn == 256) return launch_contract_pair<256, true>(map_a, map_b, map_t, own, p, info.sms, stream);
-    return launch_contract_pair<128, true>(map_a, map_b, map_t, own, p, info.sms, stream);
+    if (bn == 256) return launch_contract_pair<256, true>(map_a, map_b, map_t, own, p, info, stream);
+    return launch_contract_pair<128, true>(map_a, map_b, map_t, own, p, info, stream);
   }
   if (!incoming) {
-    if (bn == 256) return launch_contract<256, false>(map_a, map_b, map_t, p, info.sms, stream);
-    if (bn == 192) return launch_contract<192, false>(map_a, map_b, map_t, p, info.sms, stream);
-    return launch_contract<128, false>(map_a, map_b, map_t, p, info.sms, stream);
+    if (bn == 256) return launch_contract<256, false>(map_a, map_b, map_t, p, info, stream);
+    if (bn == 192) return launch_contract<192, false>(map_a, map_b, map_t, p, info, stream);
+    return launch_contract<128, false>(map_a, map_b, map_t, p, info, stream);
   }
-  if (bn == 256) return launch_contract<256, true>(map_a, map_b, map_t, p, info.sms, stream);
-  if (bn == 192) return launch_contract<192, true>(map_a, map_b, map_t, p, info.sms, stream);
-  return launch_contract<128, true>(map_a, map_b, map_t, p, info.sms, stream);
+  if (bn == 256) return launch_contract<256, true>(map_a, map_b, map_t, p, info, stream);
+  if (bn == 192) return launch_contract<192, true>(map_a, map_b, map_t, p, info, stream);
+  return launch_contract<128, true>(map_a, map_b, map_t, p, info, stream);
 }
 
 int b200_trimul_contract(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
@@ -769,7 +808,7 @@ static int epilogue_impl(const void* tri, const void* z, const void* packed, voi
   p.eps_out = eps_out * (kTriScale * kTriScale);  // tri arrives scaled by kTriScale
   p.residual = residual;
   p.status = status;
-  rc = set_smem(epilogue_kernel, kEpiSmemBytes);
+  rc = set_smem(epilogue_kernel, kEpiSmemBytes, info.device);
   if (rc != B200_TRIMUL_OK) return rc;
   const int grid = p.num_tiles < info.sms ? p.num_tiles : info.sms;
   epilogue_kernel<<<grid, kEpilogueThreads, kEpiSmemBytes, static_cast<cudaStream_t>(cuda_stream)>>>(map_t, map_z, map_y,
@@ -852,7 +891,6 @@ constexpr size_t kStaticScratchBytes = kStaticWorkspaceBytes + 1024;  // slack t
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];  // 12.2 MiB per GPU
 
-constexpr int kMaxDevices = 64;
 static std::mutex g_static_mutex;
 static void* g_static_ptr[kMaxDevices] = {};
 
@@ -888,6 +926,9 @@ extern "C" int b200_trimul_forward_static(const void* z, const void* w_left, con
   int rc = b200_trimul_workspace_bytes(B, N, d_pair, d_hidden, direction, &need);
   if (rc != B200_TRIMUL_OK) return rc;
   if (static_cast<long long>(B) * N * N > kStaticMaxCells || need > kStaticWorkspaceBytes) return B200_TRIMUL_E_TOO_LARGE;
+  DeviceInfo info;
+  rc = device_info(&info);  // a device of another architecture is reported as such, before the symbol look-up fails on it
+  if (rc != B200_TRIMUL_OK) return rc;
   void* scratch = nullptr;
   rc = static_scratch(&scratch);
   if (rc != B200_TRIMUL_OK) return rc;

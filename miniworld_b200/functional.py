@@ -84,14 +84,19 @@ class _Weights:
                 raise RuntimeError("all six linear weights must share one dtype")
             if tuple(w.shape) != (D, D):
                 raise RuntimeError(f"{k}: expected shape ({D},{D}), got {tuple(w.shape)} (only d_pair = d_hidden = 128 is supported)")
-            keep.append(w.detach().contiguous())
+            if not w.is_contiguous():
+                # a silent .contiguous() copy would be cached by the caller and go stale after an in-place update
+                raise RuntimeError(f"{k} must be contiguous (the kernels read the parameter's own storage on every call)")
+            keep.append(w.detach())
         lns = []
         for k in LN_KEYS:
             v = params[k]
             _require_cuda(v, k)
             if tuple(v.shape) != (D,):
                 raise RuntimeError(f"{k}: expected shape ({D},)")
-            lns.append(v.detach().to(torch.float32).contiguous())
+            if v.dtype != torch.float32 or not v.is_contiguous():
+                raise RuntimeError(f"{k} must be a contiguous fp32 tensor (LayerNorm affine parameters stay fp32), got {v.dtype}")
+            lns.append(v.detach())
         self.weights = keep
         self.lns = lns
         self.dtype_code = _lib.DTYPE_BF16 if dt == torch.bfloat16 else _lib.DTYPE_F32

@@ -38,6 +38,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import warnings
+
 import torch
 import torch.distributed as dist
 
@@ -45,6 +47,13 @@ from . import functional as F_
 from .modules import TriangleMultiplication
 
 D = 128
+
+
+def _symm_mem():
+    """torch's symmetric-memory module (imported late: it needs a CUDA build of torch)."""
+    import torch.distributed._symmetric_memory as symm_mem
+
+    return symm_mem
 
 
 def row_range(n_rows: int, world: int, rank: int) -> tuple[int, int]:
@@ -124,49 +133,72 @@ class RowShardedTriangleMultiplication(TriangleMultiplication):
             return None
         if self._sym is not None and self._sym[0] == (N, device):
             return self._sym[1]
-        import torch.distributed._symmetric_memory as symm_mem
-
         group = self.group if self.group is not None else dist.group.WORLD
         rows, cg = N // world, D // world
         if self.contraction == "channels":
             shapes = {"left": (1, N, cg, N), "right": (1, N, cg, N), "tri": (world, rows, cg, N)}
         else:
             shapes = {"full": (1, N, D, N)}  # gathered `right` (outgoing) or the partial sums (incoming)
-        ok = torch.ones(1, device=device)
-        sets, owners, flags = [], [], None
+
+        # Two phases, each closed by the same all-reduce on every rank whatever happened locally, so that a failure
+        # on one rank (out of memory, no peer mapping) can never leave the others waiting inside a collective:
+        # phase 1 allocates everything locally (no communication), phase 2 exchanges the handles (a collective per
+        # buffer, entered only when every rank holds all of its buffers).
+        allocs, err = [], None
         try:
+            symm_mem = _symm_mem()
             t = symm_mem.empty(8, dtype=torch.int32, device=device)
             t.zero_()
-            hdl = symm_mem.rendezvous(t, group)
-            owners.append((t, hdl))
-            flags = [hdl.get_buffer(r, (8,), torch.int32) for r in range(world)]
+            allocs.append(("flags", None, t))
             for _ in range(2):
-                views = {}
                 for name, shape in shapes.items():
                     numel = 1
-                    for s in shape:
-                        numel *= s
-                    t = symm_mem.empty(numel, dtype=torch.float16, device=device)
-                    hdl = symm_mem.rendezvous(t, group)
-                    owners.append((t, hdl))  # the views below do not keep the allocation alive
-                    views[name] = [hdl.get_buffer(r, shape, torch.float16) for r in range(world)]
-                sets.append(views)
-        except Exception as exc:  # no peer access between the GPUs, or no symmetric memory in this build
-            if self._explicit:
-                raise RuntimeError(f"transport 'p2p' needs torch symmetric memory between the ranks: {exc!r}") from exc
-            ok.zero_()
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)  # all ranks take the same path
-        if float(ok.item()) == 0.0:
-            self.transport = "nccl"
-            self.contraction = "rows"
-            self._sym = None
-            return None
+                    for d in shape:
+                        numel *= d
+                    allocs.append((name, shape, symm_mem.empty(numel, dtype=torch.float16, device=device)))
+        except Exception as exc:  # no symmetric memory in this build, or the allocation failed on this rank
+            err = exc
+        if not self._agree(err is None, device):
+            return self._no_p2p(err, "allocating symmetric memory failed on at least one rank")
+        sets, owners, flags = [], [], None
+        try:
+            for name, shape, t in allocs:
+                hdl = symm_mem.rendezvous(t, group)
+                owners.append((t, hdl))  # the views below do not keep the allocation alive
+                if name == "flags":
+                    flags = [hdl.get_buffer(r, (8,), torch.int32) for r in range(world)]
+                    continue
+                if not sets or name in sets[-1]:
+                    sets.append({})
+                sets[-1][name] = [hdl.get_buffer(r, shape, torch.float16) for r in range(world)]
+        except Exception as exc:  # no peer access between the GPUs
+            err = exc
+        if not self._agree(err is None, device):
+            return self._no_p2p(err, "mapping the peers' symmetric memory failed on at least one rank")
         # (the all-reduce above also orders every rank's zeroing of its flags before any peer's first barrier)
         self.transport = "p2p"
         self._flags = flags
         self._epoch = 0
         self._sym = ((N, device), sets, owners)
         return sets
+
+    def _agree(self, ok: bool, device: torch.device) -> bool:
+        """True iff ``ok`` holds on every rank (one all-reduce, issued by every rank on every path)."""
+        t = torch.full((1,), 1.0 if ok else 0.0, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        return float(t.item()) != 0.0
+
+    def _no_p2p(self, err, what: str):
+        """Every rank arrives here together. Asked for by name: raise everywhere; otherwise warn once and use NCCL."""
+        if self._explicit:
+            raise RuntimeError(f"transport 'p2p' needs torch symmetric memory between the ranks: {what}"
+                               + (f" (this rank: {err!r})" if err is not None else ""))
+        warnings.warn(f"RowShardedTriangleMultiplication: {what}; using NCCL collectives and the row scheme instead"
+                      + (f" (this rank: {err!r})" if err is not None else ""), RuntimeWarning, stacklevel=3)
+        self.transport = "nccl"
+        self.contraction = "rows"
+        self._sym = None
+        return None
 
     def _barrier(self, rank: int, status: torch.Tensor) -> None:
         """Everything enqueued so far has finished on every GPU before anything enqueued next starts."""

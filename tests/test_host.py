@@ -186,3 +186,60 @@ def test_row_sharded_schedule_on_two_gloo_ranks(scheme):
         ret = mgr.dict()
         mp.spawn(_row_sharded_worker, args=(world, port, scheme, ret), nprocs=world, join=True)
         assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)
+
+
+class _FakeSymmMem:
+    """Stand-in for torch's symmetric-memory module on CPU: ``empty`` fails on the ranks listed in ``fail_on``."""
+
+    def __init__(self, rank, fail_on):
+        self.rank, self.fail_on = rank, fail_on
+
+    def empty(self, numel, dtype, device):
+        if self.rank in self.fail_on:
+            raise RuntimeError("out of memory (injected)")
+        return torch.empty(numel, dtype=dtype, device=device)
+
+    def rendezvous(self, t, group):
+        raise AssertionError("handles must not be exchanged unless every rank holds all of its buffers")
+
+
+def _symmetric_failure_worker(rank, world, port, explicit, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import warnings
+
+        sharded._symm_mem = lambda: _FakeSymmMem(rank, fail_on={1})
+        m = sharded.RowShardedTriangleMultiplication(128, transport="p2p" if explicit else "auto")
+        dev = torch.device("cpu")
+        try:
+            with warnings.catch_warnings(record=True) as caught:
+                warnings.simplefilter("always")
+                out = m._symmetric(256, world, dev)
+            ret[rank] = ("fallback", out is None, m.transport, m.contraction, len(caught))
+        except RuntimeError as exc:
+            ret[rank] = ("raised", "p2p" in str(exc))
+        # both ranks are still in step: one more collective completes
+        t = torch.ones(1)
+        dist.all_reduce(t)
+        assert float(t) == world
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("explicit", [True, False])
+def test_symmetric_setup_failure_on_one_rank_does_not_split_the_ranks(explicit):
+    """One rank cannot allocate its symmetric buffers: every rank still runs the same collectives, then all of them
+    raise (transport asked for by name) or all of them fall back to NCCL with a warning (world_size 2, gloo, CPU)."""
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_symmetric_failure_worker, args=(world, port, explicit, ret), nprocs=world, join=True)
+        assert len(ret) == world
+        for rank in range(world):
+            if explicit:
+                assert ret[rank] == ("raised", True), dict(ret)
+            else:
+                assert ret[rank] == ("fallback", True, "nccl", "rows", 1), dict(ret)

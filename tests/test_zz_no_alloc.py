@@ -22,16 +22,17 @@ DEV = "cuda"
 E_TOO_LARGE = -8
 
 
-def _call_static(z, p, mask, outgoing, residual=True):
+def _call_static(z, p, mask, outgoing, residual=True, pair_mask=None, biases=None):
     lib = _lib.load()
-    w = F_._Weights(p, None, z.device)
+    w = F_._Weights(p, biases, z.device)
     y = torch.full_like(z, float("nan"))
     tm = F_.as_mask_u8(mask, z.device)
+    pm = F_.as_mask_u8(pair_mask, z.device)
     status_ptr = ctypes.c_void_p(0)
     B, N = int(z.shape[0]), int(z.shape[1])
     rc = lib.b200_trimul_forward_static(
-        z.data_ptr(), *[t.data_ptr() for t in w.weights], w.dtype_code, *[t.data_ptr() for t in w.lns], None,
-        None if tm is None else tm.data_ptr(), None, y.data_ptr(), B, N, 128, 128,
+        z.data_ptr(), *[t.data_ptr() for t in w.weights], w.dtype_code, *[t.data_ptr() for t in w.lns], w.bias_array,
+        None if tm is None else tm.data_ptr(), None if pm is None else pm.data_ptr(), y.data_ptr(), B, N, 128, 128,
         _lib.OUTGOING if outgoing else _lib.INCOMING, 1e-5, 1e-5, int(residual), ctypes.byref(status_ptr),
         torch.cuda.current_stream().cuda_stream,
     )
@@ -60,6 +61,23 @@ def test_static_scratch_forward_matches_workspace_forward_twice_in_a_row():
         assert status_ptr.value, "the status address must be reported"
         assert _device_status(status_ptr) == 0
         assert torch.isfinite(got.float()).all()
+        assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
+
+
+def test_static_scratch_forward_with_pair_mask_biases_and_no_residual():
+    """The remaining arguments of the entry point: an arbitrary pair mask, gate biases, and the update alone
+    (residual off) - again two calls in a row against the workspace entry point, same bytes required."""
+    p = params_to(rand_params(54), DEV)
+    g = torch.Generator().manual_seed(55)
+    biases = {"to_left_gate": torch.ones(128, device=DEV), "to_right_gate": torch.ones(128, device=DEV),
+              "to_gate": torch.linspace(-1, 1, 128).to(DEV)}
+    for outgoing in (True, False):
+        z = torch.randn(2, 88, 88, 128, generator=g).to(torch.bfloat16).to(DEV)
+        pm = (torch.rand(2, 88, 88, generator=g) > 0.3).to(DEV)
+        want = F_.trimul_forward(z, p, None, outgoing=outgoing, pair_mask=pm, residual=False, biases=biases, check=True)
+        rc, got, status_ptr = _call_static(z, p, None, outgoing, residual=False, pair_mask=pm, biases=biases)
+        assert rc == 0, _lib.strerror(rc)
+        assert _device_status(status_ptr) == 0
         assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
 
 

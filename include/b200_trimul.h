@@ -43,6 +43,7 @@
 extern "C" {
 #endif
 
+#define B200_TRIMUL_BIDIRECTIONAL 0 /* both of the above in one module: see b200_trimul_forward_ex */
 #define B200_TRIMUL_OUTGOING 1 /* t_ij = sum_k a_ik b_jk  (einsum bikd,bjkd->bijd) */
 #define B200_TRIMUL_INCOMING 2 /* t_ij = sum_k a_ki b_kj  (einsum bkid,bkjd->bijd) */
 
@@ -199,6 +200,48 @@ int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_ga
                         const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask, void* y,
                         void* workspace, size_t workspace_bytes, int B, int N, int d_pair, int d_hidden,
                         int direction, float eps_in, float eps_out, int residual, void* cuda_stream);
+
+/*
+ * General forward. Everything of b200_trimul_forward, plus:
+ *  - direction B200_TRIMUL_BIDIRECTIONAL (0, the engine's numbering: benchmarks/engine_ops/trimul_batch.py:10,66):
+ *    the BidirectionalTriangleMultiplication MiniWorld's trunk builds (src/miniworld/modules/mini_pairformer.py:76-80,
+ *    algorithm docs/paper/supplement.tex:125-136). Same eleven leaves with wider shapes: w_left, w_left_gate, w_right,
+ *    w_right_gate are [256, 128] (rows 0-127 -> outgoing contraction, rows 128-255 -> incoming), ln_out_w / ln_out_b
+ *    have 256 entries, w_out is [128, 256], w_gate stays [128, 128]; the first four entries of bias_opt, if given,
+ *    are fp32[256]. d_hidden is the width of one direction (128). Workspace: b200_trimul_workspace_bytes with
+ *    direction 0.
+ *  - drop_scale: null, or [B, N, 128] bf16 - the row-shared dropout scale [B, 1, N, C] of the training path
+ *    (keep-mask / (1 - p), scripts/check_trimul_module_reference.py:43 in the reference project): y = z + scale * update.
+ *    A zero scale returns z exactly. This is `flat_scale` of the engine's entry point.
+ */
+int b200_trimul_forward_ex(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
+                           const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                           const float* ln_in_w, const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,
+                           const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask,
+                           const void* drop_scale, void* y, void* workspace, size_t workspace_bytes, int B, int N,
+                           int d_pair, int d_hidden, int direction, float eps_in, float eps_out, int residual,
+                           void* cuda_stream);
+
+/*
+ * Weight packing of the bidirectional module (shapes as in b200_trimul_forward_ex): two blocks of
+ * b200_trimul_packed_bytes() each. `packed_out` feeds stage 1 of the outgoing half and stage 3, `packed_in` stage 1
+ * of the incoming half; stage 3 also reads the second half of w_out from `packed_in`.
+ */
+int b200_trimul_pack_weights_bidir(const void* w_left, const void* w_left_gate, const void* w_right,
+                                   const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                                   const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                                   const float* ln_out_b, const void* const* bias_opt, void* packed_out,
+                                   void* packed_in, void* cuda_stream);
+
+/*
+ * Stage 3, general form: output LayerNorm over 128 (tri_in null) or 256 (tri_in given: [tri, tri_in]) contracted
+ * channels, output projection, sigmoid gate, optional row-shared dropout scale, residual. tri / tri_in:
+ * [B, rows, 128, N] fp16 as written by stage 2; packed / packed_in: the blocks of b200_trimul_pack_weights(_bidir);
+ * drop_scale: null or [B, N, 128] bf16; z, y: [B, rows, N, 128] bf16.
+ */
+int b200_trimul_epilogue_wide(const void* tri, const void* tri_in, const void* z, const void* packed,
+                              const void* packed_in, const void* drop_scale, void* y, int B, int N, int rows,
+                              float eps_in, float eps_out, int residual, int* status, void* cuda_stream);
 
 /*
  * The same forward for callers that cannot give the library a workspace because they cannot allocate device

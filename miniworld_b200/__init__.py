@@ -6,6 +6,7 @@ batch-parallel multi-GPU wrappers.
 """
 
 from .modules import (  # noqa: F401
+    BidirectionalTriangleMultiplication,
     TriangleMultiplication,
     TriangleMultiplicationIncoming,
     TriangleMultiplicationOutgoing,
@@ -15,6 +16,7 @@ from .modules import (  # noqa: F401
 
 __all__ = [
     "TriangleMultiplication",
+    "BidirectionalTriangleMultiplication",
     "TriangleMultiplicationOutgoing",
     "TriangleMultiplicationIncoming",
     "to_openfold_state_dict",

@@ -11,6 +11,7 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libb200_trimul.so"
 
+BIDIRECTIONAL = 0
 OUTGOING = 1
 INCOMING = 2
 DTYPE_BF16 = 0
@@ -76,6 +77,23 @@ SIGNATURES = {
         + [POINTER(c_void_p), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]
         + [c_int] * 5
         + [c_float, c_float, c_int, c_void_p],
+    ),
+    "b200_trimul_forward_ex": (
+        c_int,
+        [c_void_p] * 7
+        + [c_int]
+        + [c_void_p] * 4
+        + [POINTER(c_void_p), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]
+        + [c_int] * 5
+        + [c_float, c_float, c_int, c_void_p],
+    ),
+    "b200_trimul_pack_weights_bidir": (
+        c_int,
+        [c_void_p] * 6 + [c_int] + [c_void_p] * 4 + [POINTER(c_void_p), c_void_p, c_void_p, c_void_p],
+    ),
+    "b200_trimul_epilogue_wide": (
+        c_int,
+        [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],
     ),
     "b200_trimul_forward_static": (
         c_int,

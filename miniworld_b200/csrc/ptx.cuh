@@ -81,6 +81,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+#ifdef VAR_LIGHT_POLL
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = code;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+#else
   while (true) {
     if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
     if (*abort_flag != 0) return false;
@@ -90,6 +103,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+#endif
 }
 
 // Warp-level bounded wait: lane 0 polls, the other lanes sleep at the shuffle instead of burning issue slots.

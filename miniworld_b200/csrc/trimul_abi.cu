@@ -9,6 +9,7 @@
 #include "contract.cuh"
 #include "contract_pair.cuh"
 #include "epilogue.cuh"
+#include "epilogue_wide.cuh"
 #include "prologue.cuh"
 
 namespace trimul {
@@ -40,6 +41,7 @@ static thread_local int tl_last_cuda_error = 0;
 //   matrix 5 (gate): W' = bf16(0.5 W gamma_in),  s = rowsum(W'), d = 0.5 (W beta_in + bias)
 struct PackArgs {
   const void* w[6];
+  int ld[6];  // elements between consecutive rows of w[m] (128 for a matrix of its own, more for a column slice)
   const float* bias[6];
   const float* ln_in_w;
   const float* ln_in_b;
@@ -57,10 +59,10 @@ __global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* pa
   const float* beta = (m == 4) ? a.ln_out_b : a.ln_in_b;
   float w[4];
   if (a.f32_weights) {
-    const float4 v = reinterpret_cast<const float4*>(a.w[m])[row * 32 + lane];
+    const float4 v = reinterpret_cast<const float4*>(static_cast<const float*>(a.w[m]) + static_cast<size_t>(row) * a.ld[m])[lane];
     w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
   } else {
-    const uint2 v = reinterpret_cast<const uint2*>(a.w[m])[row * 32 + lane];
+    const uint2 v = reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(a.w[m]) + static_cast<size_t>(row) * a.ld[m])[lane];
     w[0] = bf16_lo(v.x), w[1] = bf16_hi(v.x), w[2] = bf16_lo(v.y), w[3] = bf16_hi(v.y);
   }
   const float4 g = reinterpret_cast<const float4*>(gamma)[lane];
@@ -403,11 +405,14 @@ int b200_trimul_workspace_layout(int B, int N, size_t out_offsets[5]) {
 int b200_trimul_workspace_bytes(int B, int N, int d_pair, int d_hidden, int direction, size_t* out_bytes) {
   if (out_bytes == nullptr) return B200_TRIMUL_E_NULL;
   if (d_pair != kC || d_hidden != kC) return B200_TRIMUL_E_UNSUPPORTED;
-  if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING) return B200_TRIMUL_E_SHAPE;
+  if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING && direction != B200_TRIMUL_BIDIRECTIONAL)
+    return B200_TRIMUL_E_SHAPE;
   size_t off[5];
   int rc = b200_trimul_workspace_layout(B, N, off);
   if (rc != B200_TRIMUL_OK) return rc;
   *out_bytes = off[4] + plane_tensor_bytes(B, N, N);
+  // bidirectional: a second packed block and a second tri tensor (left / right are reused by the two halves)
+  if (direction == B200_TRIMUL_BIDIRECTIONAL) *out_bytes += kPackedBytes + plane_tensor_bytes(B, N, N);
   return B200_TRIMUL_OK;
 }
 
@@ -425,30 +430,19 @@ int b200_trimul_read_status(const int* status, void* cuda_stream, int* host_stat
   return B200_TRIMUL_OK;
 }
 
-int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const void* w_right,
-                             const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
-                             const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
-                             const float* ln_out_b, const void* const* bias_opt, void* packed, void* cuda_stream) {
-  if (!w_left || !w_left_gate || !w_right || !w_right_gate || !w_gate || !w_out || !ln_in_w || !ln_in_b ||
-      !ln_out_w || !ln_out_b || !packed)
-    return B200_TRIMUL_E_NULL;
+// Launch the pack kernel. w / bias in MATRIX order: left, left gate, right, right gate, out, gate.
+static int pack_impl(const void* const w[6], const int ld[6], int weight_dtype, const float* ln_in_w, const float* ln_in_b,
+                     const float* ln_out_w, const float* ln_out_b, const float* const bias[6], void* packed,
+                     void* cuda_stream) {
+  if (!ln_in_w || !ln_in_b || !ln_out_w || !ln_out_b || !packed) return B200_TRIMUL_E_NULL;
   if (weight_dtype != B200_TRIMUL_DTYPE_BF16 && weight_dtype != B200_TRIMUL_DTYPE_F32) return B200_TRIMUL_E_SHAPE;
   PackArgs a;
-  a.w[0] = w_left;
-  a.w[1] = w_left_gate;
-  a.w[2] = w_right;
-  a.w[3] = w_right_gate;
-  a.w[4] = w_out;
-  a.w[5] = w_gate;
   for (int i = 0; i < 6; ++i) {
-    if (!aligned(a.w[i], 16)) return B200_TRIMUL_E_ALIGN;
-    a.bias[i] = nullptr;
-  }
-  if (bias_opt != nullptr) {
-    // ABI order: left, left_gate, right, right_gate, gate, out  ->  matrix order: ..., out (4), gate (5)
-    for (int i = 0; i < 4; ++i) a.bias[i] = static_cast<const float*>(bias_opt[i]);
-    a.bias[5] = static_cast<const float*>(bias_opt[4]);
-    a.bias[4] = static_cast<const float*>(bias_opt[5]);
+    if (!w[i]) return B200_TRIMUL_E_NULL;
+    if (!aligned(w[i], 16)) return B200_TRIMUL_E_ALIGN;
+    a.w[i] = w[i];
+    a.ld[i] = ld[i];
+    a.bias[i] = bias[i];
   }
   if (!aligned(ln_in_w, 16) || !aligned(ln_in_b, 16) || !aligned(ln_out_w, 16) || !aligned(ln_out_b, 16))
     return B200_TRIMUL_E_ALIGN;
@@ -461,6 +455,54 @@ int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const 
   pack_kernel<<<192, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(a, static_cast<uint8_t*>(packed));
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
+}
+
+int b200_trimul_pack_weights(const void* w_left, const void* w_left_gate, const void* w_right,
+                             const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                             const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                             const float* ln_out_b, const void* const* bias_opt, void* packed, void* cuda_stream) {
+  const void* w[6] = {w_left, w_left_gate, w_right, w_right_gate, w_out, w_gate};
+  const int ld[6] = {kC, kC, kC, kC, kC, kC};
+  const float* bias[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  if (bias_opt != nullptr) {
+    // ABI order: left, left_gate, right, right_gate, gate, out  ->  matrix order: ..., out (4), gate (5)
+    for (int i = 0; i < 4; ++i) bias[i] = static_cast<const float*>(bias_opt[i]);
+    bias[5] = static_cast<const float*>(bias_opt[4]);
+    bias[4] = static_cast<const float*>(bias_opt[5]);
+  }
+  return pack_impl(w, ld, weight_dtype, ln_in_w, ln_in_b, ln_out_w, ln_out_b, bias, packed, cuda_stream);
+}
+
+// Bidirectional module: the four left / right matrices are [256, 128] (rows 0-127 feed the outgoing contraction, rows
+// 128-255 the incoming one), ln_out has 256 entries, w_out is [128, 256]. Two packed blocks of the ordinary layout:
+// `packed_out` serves stage 1 of the outgoing half and stage 3 (its matrix 4 is W_out[:, 0:128] folded with
+// gamma_out[0:128]; its constants carry the output bias), `packed_in` serves stage 1 of the incoming half and
+// holds W_out[:, 128:256] as its matrix 4. Stage 3 adds the two blocks' s_out / d_out constants.
+int b200_trimul_pack_weights_bidir(const void* w_left, const void* w_left_gate, const void* w_right,
+                                   const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                                   const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                                   const float* ln_out_b, const void* const* bias_opt, void* packed_out,
+                                   void* packed_in, void* cuda_stream) {
+  if (!w_left || !w_left_gate || !w_right || !w_right_gate || !w_gate || !w_out || !ln_out_w || !ln_out_b)
+    return B200_TRIMUL_E_NULL;
+  if (weight_dtype != B200_TRIMUL_DTYPE_BF16 && weight_dtype != B200_TRIMUL_DTYPE_F32) return B200_TRIMUL_E_SHAPE;
+  const size_t es = weight_dtype == B200_TRIMUL_DTYPE_F32 ? 4 : 2;
+  auto rows128 = [&](const void* base) { return static_cast<const uint8_t*>(base) + static_cast<size_t>(kC) * kC * es; };
+  const float* b[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  if (bias_opt != nullptr)
+    for (int i = 0; i < 6; ++i) b[i] = static_cast<const float*>(bias_opt[i]);
+  const int ld[6] = {kC, kC, kC, kC, 2 * kC, kC};
+  {
+    const void* w[6] = {w_left, w_left_gate, w_right, w_right_gate, w_out, w_gate};
+    const float* bias[6] = {b[0], b[1], b[2], b[3], b[5], b[4]};
+    int rc = pack_impl(w, ld, weight_dtype, ln_in_w, ln_in_b, ln_out_w, ln_out_b, bias, packed_out, cuda_stream);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  const void* w[6] = {rows128(w_left), rows128(w_left_gate), rows128(w_right), rows128(w_right_gate),
+                      static_cast<const uint8_t*>(w_out) + kC * es, w_gate};
+  const float* bias[6] = {b[0] ? b[0] + kC : nullptr, b[1] ? b[1] + kC : nullptr, b[2] ? b[2] + kC : nullptr,
+                          b[3] ? b[3] + kC : nullptr, nullptr, nullptr};
+  return pack_impl(w, ld, weight_dtype, ln_in_w, ln_in_b, ln_out_w + kC, ln_out_b + kC, bias, packed_in, cuda_stream);
 }
 
 // Where stage 1 writes (see OutputMaps): kLocal - left / right are [B, rows, 128, N]; kGatherRight (B = 1) - left is
@@ -827,12 +869,96 @@ int b200_trimul_epilogue_groups(const void* tri_groups, const void* z, const voi
   return epilogue_impl(tri_groups, z, packed, y, 1, N, rows, groups, eps_in, eps_out, residual, status, cuda_stream);
 }
 
-int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
-                        const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
-                        const float* ln_in_w, const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,
-                        const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask, void* y,
-                        void* workspace, size_t workspace_bytes, int B, int N, int d_pair, int d_hidden,
-                        int direction, float eps_in, float eps_out, int residual, void* cuda_stream) {
+}  // extern "C"
+
+template <int KCH, bool SCALED>
+static int launch_epilogue_wide(const CUtensorMap& mt0, const CUtensorMap& mt1, const CUtensorMap& mz, const CUtensorMap& my,
+                                const CUtensorMap& mw0, const CUtensorMap& mw1, const EpilogueWideParams& p,
+                                const DeviceInfo& info, cudaStream_t stream) {
+  auto kernel = epilogue_wide_kernel<KCH, SCALED>;
+  int rc = set_smem(kernel, kWideSmemBytes, info.device);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const int grid = p.num_tiles < info.sms ? p.num_tiles : info.sms;
+  kernel<<<grid, kEpilogueThreads, kWideSmemBytes, stream>>>(mt0, mt1, mz, my, mw0, mw1, p);
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
+}
+
+extern "C" {
+
+int b200_trimul_epilogue_wide(const void* tri, const void* tri_in, const void* z, const void* packed,
+                              const void* packed_in, const void* drop_scale, void* y, int B, int N, int rows,
+                              float eps_in, float eps_out, int residual, int* status, void* cuda_stream) {
+  if (!tri || !z || !packed || !y || !status) return B200_TRIMUL_E_NULL;
+  const bool bidir = tri_in != nullptr;
+  if (bidir && !packed_in) return B200_TRIMUL_E_NULL;
+  int rc = check_bn(B, N);
+  if (rc != B200_TRIMUL_OK) return rc;
+  if (rows < 1 || rows > N) return B200_TRIMUL_E_SHAPE;
+  if (!aligned(tri, 16) || !aligned(z, 16) || !aligned(y, 16) || !aligned(packed, 1024)) return B200_TRIMUL_E_ALIGN;
+  if (bidir && (!aligned(tri_in, 16) || !aligned(packed_in, 1024))) return B200_TRIMUL_E_ALIGN;
+  if (drop_scale && !aligned(drop_scale, 16)) return B200_TRIMUL_E_ALIGN;
+  DeviceInfo info;
+  rc = device_info(&info);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const uint64_t n64 = static_cast<uint64_t>(N);
+  const uint64_t nrows = static_cast<uint64_t>(B) * rows;
+  CUtensorMap map_t0, map_t1, map_z, map_y, map_w0, map_w1;
+  {
+    const uint64_t dims[3] = {n64, static_cast<uint64_t>(kC), nrows};
+    const uint64_t strides[2] = {n64 * 2, static_cast<uint64_t>(kC) * n64 * 2};
+    const uint32_t box[3] = {64, 64, 1};  // one chunk half: 64 positions of 64 channels
+    rc = make_map(&map_t0, tri, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = make_map(&map_t1, bidir ? tri_in : tri, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(kC), n64, nrows};
+    const uint64_t strides[2] = {kC * 2ull, n64 * kC * 2ull};
+    const uint32_t box[3] = {64, 128, 1};
+    rc = make_map(&map_z, z, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = make_map(&map_y, y, 3, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(kC), 6ull * 128};
+    const uint64_t strides[1] = {kC * 2ull};
+    const uint32_t box[2] = {64, 128};
+    rc = make_map(&map_w0, packed, 2, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = make_map(&map_w1, bidir ? packed_in : packed, 2, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  EpilogueWideParams p;
+  p.tiles_per_row = (N + 127) / 128;
+  p.num_tiles = static_cast<int>(nrows) * p.tiles_per_row;
+  p.rows_per_sample = rows;
+  p.n = N;
+  p.c3_a = reinterpret_cast<const float4*>(static_cast<const uint8_t*>(packed) + kPackedC3Off);
+  p.c3_b = reinterpret_cast<const float4*>(static_cast<const uint8_t*>(bidir ? packed_in : packed) + kPackedC3Off);
+  p.drop_scale = static_cast<const __nv_bfloat16*>(drop_scale);
+  p.eps_in = eps_in;
+  p.eps_out = eps_out * (kTriScale * kTriScale);  // tri arrives scaled by kTriScale
+  p.residual = residual;
+  p.status = status;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (bidir) {
+    if (drop_scale) return launch_epilogue_wide<4, true>(map_t0, map_t1, map_z, map_y, map_w0, map_w1, p, info, stream);
+    return launch_epilogue_wide<4, false>(map_t0, map_t1, map_z, map_y, map_w0, map_w1, p, info, stream);
+  }
+  if (drop_scale) return launch_epilogue_wide<2, true>(map_t0, map_t1, map_z, map_y, map_w0, map_w1, p, info, stream);
+  return launch_epilogue_wide<2, false>(map_t0, map_t1, map_z, map_y, map_w0, map_w1, p, info, stream);
+}
+
+int b200_trimul_forward_ex(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
+                           const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                           const float* ln_in_w, const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,
+                           const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask,
+                           const void* drop_scale, void* y, void* workspace, size_t workspace_bytes, int B, int N,
+                           int d_pair, int d_hidden, int direction, float eps_in, float eps_out, int residual,
+                           void* cuda_stream) {
   if (!z || !y || !workspace) return B200_TRIMUL_E_NULL;
   size_t need = 0;
   int rc = b200_trimul_workspace_bytes(B, N, d_pair, d_hidden, direction, &need);
@@ -850,18 +976,54 @@ int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_ga
   void* tri = ws + off[4];
   rc = b200_trimul_clear_status(status, cuda_stream);
   if (rc != B200_TRIMUL_OK) return rc;
-  rc = b200_trimul_pack_weights(w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out, weight_dtype, ln_in_w,
-                                ln_in_b, ln_out_w, ln_out_b, bias_opt, packed, cuda_stream);
-  if (rc != B200_TRIMUL_OK) return rc;
   int has_bias = 0;
   if (bias_opt != nullptr)
     for (int i = 0; i < 4; ++i) has_bias |= bias_opt[i] != nullptr;
+  if (direction == B200_TRIMUL_BIDIRECTIONAL) {
+    // workspace tail: second tri tensor, then the second packed block
+    const size_t plane = plane_tensor_bytes(B, N, N);
+    void* tri_in = ws + off[4] + plane;
+    void* packed_in = ws + off[4] + 2 * plane;
+    rc = b200_trimul_pack_weights_bidir(w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out, weight_dtype, ln_in_w,
+                                        ln_in_b, ln_out_w, ln_out_b, bias_opt, packed, packed_in, cuda_stream);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = b200_trimul_prologue(z, packed, token_mask, pair_mask, left, right, B, N, 0, N, eps_in, has_bias, status,
+                              cuda_stream);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = b200_trimul_contract(left, right, tri, B, N, 0, N, B200_TRIMUL_OUTGOING, status, cuda_stream);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = b200_trimul_prologue(z, packed_in, token_mask, pair_mask, left, right, B, N, 0, N, eps_in, has_bias, status,
+                              cuda_stream);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = b200_trimul_contract(left, right, tri_in, B, N, 0, N, B200_TRIMUL_INCOMING, status, cuda_stream);
+    if (rc != B200_TRIMUL_OK) return rc;
+    return b200_trimul_epilogue_wide(tri, tri_in, z, packed, packed_in, drop_scale, y, B, N, N, eps_in, eps_out, residual,
+                                     status, cuda_stream);
+  }
+  rc = b200_trimul_pack_weights(w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out, weight_dtype, ln_in_w,
+                                ln_in_b, ln_out_w, ln_out_b, bias_opt, packed, cuda_stream);
+  if (rc != B200_TRIMUL_OK) return rc;
   rc = b200_trimul_prologue(z, packed, token_mask, pair_mask, left, right, B, N, 0, N, eps_in, has_bias, status,
                             cuda_stream);
   if (rc != B200_TRIMUL_OK) return rc;
   rc = b200_trimul_contract(left, right, tri, B, N, 0, N, direction, status, cuda_stream);
   if (rc != B200_TRIMUL_OK) return rc;
+  if (drop_scale != nullptr)
+    return b200_trimul_epilogue_wide(tri, nullptr, z, packed, nullptr, drop_scale, y, B, N, N, eps_in, eps_out, residual,
+                                     status, cuda_stream);
   return b200_trimul_epilogue(tri, z, packed, y, B, N, N, eps_in, eps_out, residual, status, cuda_stream);
+}
+
+int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
+                        const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                        const float* ln_in_w, const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,
+                        const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask, void* y,
+                        void* workspace, size_t workspace_bytes, int B, int N, int d_pair, int d_hidden,
+                        int direction, float eps_in, float eps_out, int residual, void* cuda_stream) {
+  return b200_trimul_forward_ex(z, w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out, weight_dtype, ln_in_w,
+                                ln_in_b, ln_out_w, ln_out_b, bias_opt, token_mask, pair_mask, nullptr, y, workspace,
+                                workspace_bytes, B, N, d_pair, d_hidden, direction, eps_in, eps_out, residual,
+                                cuda_stream);
 }
 
 }  // extern "C"

@@ -41,9 +41,16 @@ def aligned_empty(nbytes: int, device: torch.device, align: int = 1024) -> torch
     return raw[off : off + nbytes]
 
 
-def workspace_bytes(B: int, N: int, outgoing: bool = True) -> int:
+def _direction(outgoing: Optional[bool]) -> int:
+    """True -> outgoing, False -> incoming, None -> the bidirectional module."""
+    if outgoing is None:
+        return _lib.BIDIRECTIONAL
+    return _lib.OUTGOING if outgoing else _lib.INCOMING
+
+
+def workspace_bytes(B: int, N: int, outgoing: Optional[bool] = True) -> int:
     out = c_size_t(0)
-    rc = _lib.load().b200_trimul_workspace_bytes(B, N, D, D, _lib.OUTGOING if outgoing else _lib.INCOMING, ctypes.byref(out))
+    rc = _lib.load().b200_trimul_workspace_bytes(B, N, D, D, _direction(outgoing), ctypes.byref(out))
     _lib.check(rc, "b200_trimul_workspace_bytes")
     return int(out.value)
 
@@ -72,7 +79,13 @@ def as_mask_u8(mask: Optional[torch.Tensor], device: torch.device) -> Optional[t
 class _Weights:
     """Validated pointers of one parameter set (all weights in one dtype, LN affine fp32)."""
 
-    def __init__(self, params: dict, biases: Optional[dict], device: torch.device):
+    def __init__(self, params: dict, biases: Optional[dict], device: torch.device, bidirectional: bool = False):
+        self.bidirectional = bool(bidirectional)
+        wide = 2 * D if bidirectional else D  # the four left / right matrices, ln_out and the columns of to_out
+        shapes = {"to_left.weight": (wide, D), "to_left_gate.weight": (wide, D), "to_right.weight": (wide, D),
+                  "to_right_gate.weight": (wide, D), "to_gate.weight": (D, D), "to_out.weight": (D, wide),
+                  "ln_pair.weight": (D,), "ln_pair.bias": (D,), "ln_out.weight": (wide,), "ln_out.bias": (wide,)}
+        bias_len = {"to_left": wide, "to_left_gate": wide, "to_right": wide, "to_right_gate": wide, "to_gate": D, "to_out": D}
         ws = [params[k] for k in WEIGHT_KEYS]
         dt = ws[0].dtype
         if dt not in (torch.bfloat16, torch.float32):
@@ -82,8 +95,8 @@ class _Weights:
             _require_cuda(w, k)
             if w.dtype != dt:
                 raise RuntimeError("all six linear weights must share one dtype")
-            if tuple(w.shape) != (D, D):
-                raise RuntimeError(f"{k}: expected shape ({D},{D}), got {tuple(w.shape)} (only d_pair = d_hidden = 128 is supported)")
+            if tuple(w.shape) != shapes[k]:
+                raise RuntimeError(f"{k}: expected shape {shapes[k]}, got {tuple(w.shape)} (only d_pair = d_hidden = 128 is supported)")
             if not w.is_contiguous():
                 # a silent .contiguous() copy would be cached by the caller and go stale after an in-place update
                 raise RuntimeError(f"{k} must be contiguous (the kernels read the parameter's own storage on every call)")
@@ -92,8 +105,8 @@ class _Weights:
         for k in LN_KEYS:
             v = params[k]
             _require_cuda(v, k)
-            if tuple(v.shape) != (D,):
-                raise RuntimeError(f"{k}: expected shape ({D},)")
+            if tuple(v.shape) != shapes[k]:
+                raise RuntimeError(f"{k}: expected shape {shapes[k]}, got {tuple(v.shape)}")
             if v.dtype != torch.float32 or not v.is_contiguous():
                 raise RuntimeError(f"{k} must be a contiguous fp32 tensor (LayerNorm affine parameters stay fp32), got {v.dtype}")
             lns.append(v.detach())
@@ -112,8 +125,8 @@ class _Weights:
                     arr[i] = None
                 else:
                     bb = b.detach().to(device=device, dtype=torch.float32).contiguous()
-                    if tuple(bb.shape) != (D,):
-                        raise RuntimeError(f"bias {k}: expected shape ({D},)")
+                    if tuple(bb.shape) != (bias_len[k],):
+                        raise RuntimeError(f"bias {k}: expected shape ({bias_len[k]},)")
                     bt.append(bb)
                     arr[i] = bb.data_ptr()
             self.bias_tensors = bt
@@ -145,6 +158,40 @@ def pack_weights(params: dict, packed: torch.Tensor, biases: Optional[dict] = No
             _stream(packed.device),
         )
     _lib.check(rc, "b200_trimul_pack_weights")
+
+
+def pack_weights_bidir(params: dict, packed_out: torch.Tensor, packed_in: torch.Tensor, biases: Optional[dict] = None) -> None:
+    """Pack the bidirectional module's parameters into the two blocks stage 1 (per direction) and stage 3 read."""
+    w = _Weights(params, biases, packed_out.device, bidirectional=True)
+    with torch.cuda.device(packed_out.device):
+        rc = _lib.load().b200_trimul_pack_weights_bidir(
+            *[_ptr(t) for t in w.weights[:4]], _ptr(w.weights[4]), _ptr(w.weights[5]), w.dtype_code,
+            *[_ptr(t) for t in w.lns], w.bias_array, _ptr(packed_out), _ptr(packed_in), _stream(packed_out.device),
+        )
+    _lib.check(rc, "b200_trimul_pack_weights_bidir")
+
+
+def epilogue_wide(
+    tri: torch.Tensor,
+    tri_in: Optional[torch.Tensor],
+    z: torch.Tensor,
+    packed: torch.Tensor,
+    packed_in: Optional[torch.Tensor],
+    y: torch.Tensor,
+    status: torch.Tensor,
+    drop_scale: Optional[torch.Tensor] = None,
+    eps_in: float = 1e-5,
+    eps_out: float = 1e-5,
+    residual: bool = True,
+) -> None:
+    """Stage 3, general form: LayerNorm over [tri] (128 channels) or [tri, tri_in] (256), optional dropout scale."""
+    B, N = _check_z(z)
+    with torch.cuda.device(z.device):
+        rc = _lib.load().b200_trimul_epilogue_wide(
+            _ptr(tri), _ptr(tri_in), _ptr(z), _ptr(packed), _ptr(packed_in), _ptr(drop_scale), _ptr(y), B, N,
+            int(z.shape[1]), float(eps_in), float(eps_out), int(bool(residual)), _ptr(status), _stream(z.device),
+        )
+    _lib.check(rc, "b200_trimul_epilogue_wide")
 
 
 def prologue(
@@ -373,8 +420,13 @@ def trimul_forward(
     out: Optional[torch.Tensor] = None,
     check: bool = False,
     weights: Optional["_Weights"] = None,
+    drop_scale: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """One module forward on one GPU. ``z`` [B,N,N,128] bf16; ``mask`` Bool[B,N] or None; returns ``out``.
+
+    ``outgoing=None`` selects the bidirectional module (parameters of the wider shapes, see
+    ``b200_trimul_forward_ex`` in the header). ``drop_scale`` [B,1,N,128] (or [B,N,128]) bf16 is the row-shared
+    dropout scale of the training path: ``out = z + drop_scale * update``.
 
     ``workspace`` (uint8, 1024-aligned, at least :func:`workspace_bytes`) is allocated when not given.
     ``check=True`` synchronises and raises if a device-side wait gave up. ``weights`` is an already validated
@@ -384,7 +436,15 @@ def trimul_forward(
     if z.shape[1] != N:
         raise RuntimeError(f"pair tensor must be square in its token dims, got {tuple(z.shape)}")
     dev = z.device
-    w = weights if weights is not None else _Weights(params, biases, dev)
+    w = weights if weights is not None else _Weights(params, biases, dev, bidirectional=outgoing is None)
+    if w.bidirectional != (outgoing is None):
+        raise RuntimeError("the validated weights belong to the other module kind (bidirectional vs one direction)")
+    ds = None
+    if drop_scale is not None:
+        _require_cuda(drop_scale, "drop_scale")
+        if drop_scale.numel() != B * N * D or drop_scale.shape[-1] != D or drop_scale.shape[0] != B:
+            raise RuntimeError(f"drop_scale must be [B, 1, N, {D}] = ({B}, 1, {N}, {D}), got {tuple(drop_scale.shape)}")
+        ds = drop_scale.detach().to(torch.bfloat16).contiguous()
     need = workspace_bytes(B, N, outgoing)
     if workspace is None:
         workspace = aligned_empty(need, dev)
@@ -399,7 +459,7 @@ def trimul_forward(
     if pm is not None and tuple(pm.shape) != (B, N, N):
         raise RuntimeError(f"pair mask must be [B, N, N], got {tuple(pm.shape)}")
     with torch.cuda.device(dev):
-        rc = _lib.load().b200_trimul_forward(
+        rc = _lib.load().b200_trimul_forward_ex(
             _ptr(z),
             *[_ptr(t) for t in w.weights],
             w.dtype_code,
@@ -407,6 +467,7 @@ def trimul_forward(
             w.bias_array,
             _ptr(tm),
             _ptr(pm),
+            _ptr(ds),
             _ptr(out),
             _ptr(workspace),
             workspace.numel() * workspace.element_size(),
@@ -414,13 +475,13 @@ def trimul_forward(
             N,
             D,
             D,
-            _lib.OUTGOING if outgoing else _lib.INCOMING,
+            _direction(outgoing),
             float(eps_in),
             float(eps_out),
             int(bool(residual)),
             _stream(dev),
         )
-    _lib.check(rc, "b200_trimul_forward")
+    _lib.check(rc, "b200_trimul_forward_ex")
     if check:
         check_status(workspace[:4].view(torch.int32), "b200_trimul_forward")
     return out

@@ -9,8 +9,16 @@ bias-free, ``benchmarks/protenix_finetune/patch_engine.py:25-29,51``); the modul
 ``pair + update`` (it owns the residual).  ``TriangleMultiplicationOutgoing`` / ``...Incoming`` are the
 OpenFold-style names with ``forward(z, pair_mask)``.
 
-Only the inference path exists (no autograd, no dropout): calling it with gradients enabled on inputs
-that require them, or in training mode with ``p_drop > 0``, raises ``NotImplementedError``.
+``BidirectionalTriangleMultiplication`` is the single operator MiniWorld's own trunk builds
+(``src/miniworld/modules/mini_pairformer.py:76-80``, ``src/miniworld/modules/mini_msa_module.py:104``): one input
+LayerNorm, left / right of width 2h whose halves are contracted outgoing and incoming, one LayerNorm over the 2h
+contracted channels, one gate, one residual (``docs/paper/supplement.tex:125-136``); same parameter names, wider
+shapes.
+
+Forward only. In training mode with ``p_drop > 0`` the forward applies the row-shared dropout of the reference
+(``x + drop_row(f(x))``: one keep-mask per (batch, column, channel), shared by all rows,
+``src/miniworld/blocks/template.py:38-40``); there is no backward: calling the module with gradients enabled on an
+input that requires them raises ``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -61,6 +69,22 @@ def from_openfold_state_dict(sd: dict) -> dict:
     return out
 
 
+class Fp32LayerNorm(nn.LayerNorm):
+    """LayerNorm parameter holder whose affine parameters are pinned to fp32: ``module.to(torch.bfloat16)`` moves them
+    between devices but never changes (or rounds) their values, like the reference's fp32-pinned LayerNorm
+    (``src/miniworld/layers/primitives.py:86-88``). Only ``weight``, ``bias`` and ``eps`` are used; the
+    normalisation itself runs inside the fused kernels."""
+
+    def _apply(self, fn, recurse=True):
+        def pinned(t):
+            out = fn(t)
+            if t.is_floating_point() and out.dtype != t.dtype:
+                return t.to(device=out.device)  # follow the device, keep the fp32 values bit for bit
+            return out
+
+        return super()._apply(pinned, recurse)
+
+
 class TriangleMultiplication(nn.Module):
     """Triangle multiplicative update, forward only, on B200 kernels.
 
@@ -69,6 +93,8 @@ class TriangleMultiplication(nn.Module):
     ``.to(dtype)`` is applied to the module (``src/miniworld/layers/primitives.py:86-88``).
     ``ln_pair.eps`` / ``ln_out.eps`` are read at call time.
     """
+
+    _bidirectional = False
 
     def __init__(
         self,
@@ -81,6 +107,7 @@ class TriangleMultiplication(nn.Module):
         check_status: bool = False,
     ):
         super().__init__()
+        wide = 2 if self._bidirectional else 1
         d_hidden = d_pair if d_hidden is None else d_hidden
         if d_pair != D_SUPPORTED or d_hidden != D_SUPPORTED:
             raise NotImplementedError(
@@ -96,14 +123,14 @@ class TriangleMultiplication(nn.Module):
         self.p_drop = float(p_drop)
         self.residual = bool(residual)
         self.check_status = bool(check_status)
-        self.ln_pair = nn.LayerNorm(d_pair, eps=1e-5)
-        self.to_left = nn.Linear(d_pair, d_hidden, bias=False)
-        self.to_left_gate = nn.Linear(d_pair, d_hidden, bias=False)
-        self.to_right = nn.Linear(d_pair, d_hidden, bias=False)
-        self.to_right_gate = nn.Linear(d_pair, d_hidden, bias=False)
-        self.ln_out = nn.LayerNorm(d_hidden, eps=1e-5)
+        self.ln_pair = Fp32LayerNorm(d_pair, eps=1e-5)
+        self.to_left = nn.Linear(d_pair, wide * d_hidden, bias=False)
+        self.to_left_gate = nn.Linear(d_pair, wide * d_hidden, bias=False)
+        self.to_right = nn.Linear(d_pair, wide * d_hidden, bias=False)
+        self.to_right_gate = nn.Linear(d_pair, wide * d_hidden, bias=False)
+        self.ln_out = Fp32LayerNorm(wide * d_hidden, eps=1e-5)
         self.to_gate = nn.Linear(d_pair, d_pair, bias=False)
-        self.to_out = nn.Linear(d_hidden, d_pair, bias=False)
+        self.to_out = nn.Linear(wide * d_hidden, d_pair, bias=False)
         # the reference initialises the two output linears to zero ("init='zero'")
         nn.init.zeros_(self.to_gate.weight)
         nn.init.zeros_(self.to_out.weight)
@@ -113,11 +140,7 @@ class TriangleMultiplication(nn.Module):
 
     # ------------------------------------------------------------------ dtype handling
     def _apply(self, fn, recurse=True):
-        super()._apply(fn, recurse)
-        for ln in (self.ln_pair, self.ln_out):  # LayerNorm affine stays fp32
-            for p in ln.parameters(recurse=False):
-                if p.dtype != torch.float32:
-                    p.data = p.data.to(torch.float32)
+        super()._apply(fn, recurse)  # the LayerNorm affine parameters stay fp32 (Fp32LayerNorm)
         self._workspace = None
         self._wcache = None
         return self
@@ -135,7 +158,7 @@ class TriangleMultiplication(nn.Module):
         params = self._params()
         key = tuple((v.data_ptr(), v.dtype, v.device, v.is_contiguous()) for v in params.values()) + (device,)
         if self._wcache is None or self._wcache[0] != key:
-            self._wcache = (key, F_._Weights(params, self._biases, device))
+            self._wcache = (key, F_._Weights(params, self._biases, device, bidirectional=self._bidirectional))
         return self._wcache[1]
 
     def _params(self) -> dict:
@@ -162,8 +185,19 @@ class TriangleMultiplication(nn.Module):
             return 0
         return F_.read_status(self._workspace[:64].view(torch.int32))
 
+    def _direction(self):
+        return None if self._bidirectional else self.outgoing
+
+    def _make_drop_row_scale(self, pair: torch.Tensor, p: float) -> torch.Tensor:
+        """Row-shared dropout scale [B, 1, N, C]: keep-mask / (1 - p), one draw per (batch, column, channel), shared by
+        all rows (the reference's hook of the same name, ``scripts/check_trimul_module_reference.py:43,100-103``;
+        tests replace it to fix the mask)."""
+        B, N, C = pair.shape[0], pair.shape[2], pair.shape[3]
+        keep = torch.rand(B, 1, N, C, device=pair.device) >= p
+        return keep.to(torch.bfloat16) / (1.0 - p)
+
     def _get_workspace(self, B: int, N: int, device: torch.device) -> torch.Tensor:
-        need = F_.workspace_bytes(B, N, self.outgoing)
+        need = F_.workspace_bytes(B, N, self._direction())
         ws = self._workspace
         if ws is None or ws.device != device or ws.numel() < need:
             ws = F_.aligned_empty(need, device)
@@ -171,8 +205,6 @@ class TriangleMultiplication(nn.Module):
         return ws
 
     def _run(self, pair: torch.Tensor, token_mask, pair_mask) -> torch.Tensor:
-        if self.training and self.p_drop > 0.0:
-            raise NotImplementedError("row-shared dropout (training mode with p_drop > 0) is not implemented on this path")
         if torch.is_grad_enabled() and pair.requires_grad:
             raise NotImplementedError("backward is not implemented: call under torch.no_grad() or with an input that does not require grad")
         if pair.dim() != 4 or pair.shape[1] != pair.shape[2] or pair.shape[3] != self.d_pair:
@@ -186,6 +218,13 @@ class TriangleMultiplication(nn.Module):
         z = z.contiguous()
         B, N = int(z.shape[0]), int(z.shape[1])
         pad = (-N) % 8
+        scale = None
+        if self.training and self.p_drop > 0.0:
+            scale = self._make_drop_row_scale(z, self.p_drop).to(device=z.device, dtype=torch.bfloat16)
+            if pad:
+                sp = scale.new_zeros(B, 1, N + pad, self.d_pair)
+                sp[:, :, :N] = scale
+                scale = sp
         if pad:
             # pad with masked tokens: masked rows/columns of left/right are zero, so the crop is exact
             zp = z.new_zeros(B, N + pad, N + pad, self.d_pair)
@@ -204,7 +243,7 @@ class TriangleMultiplication(nn.Module):
                 z,
                 self._params(),
                 token_mask,
-                outgoing=self.outgoing,
+                outgoing=self._direction(),
                 eps_in=float(self.ln_pair.eps),
                 eps_out=float(self.ln_out.eps),
                 pair_mask=pair_mask,
@@ -213,6 +252,7 @@ class TriangleMultiplication(nn.Module):
                 workspace=self._get_workspace(B, Np, z.device),
                 check=self.check_status,
                 weights=self._weights(z.device),
+                drop_scale=scale,
             )
         if pad:
             y = y[:, :N, :N].contiguous()
@@ -247,3 +287,20 @@ class TriangleMultiplicationOutgoing(_OpenFoldStyle):
 
 class TriangleMultiplicationIncoming(_OpenFoldStyle):
     _outgoing = False
+
+
+class BidirectionalTriangleMultiplication(TriangleMultiplication):
+    """Both directions in one operator: ``forward(pair [B,N,N,128] bf16, mask Bool[B,N] | None) -> pair + update``.
+
+    Constructor as in the reference (``BidirectionalTriangleMultiplication(d_pair, implementation=..., p_drop=...)``,
+    ``src/miniworld/modules/mini_pairformer.py:76-80``). Parameters: ``ln_pair`` [128]; ``to_left``, ``to_left_gate``,
+    ``to_right``, ``to_right_gate`` [256, 128] (rows 0-127: outgoing half, rows 128-255: incoming half); ``ln_out``
+    [256]; ``to_gate`` [128, 128]; ``to_out`` [128, 256].
+    """
+
+    _bidirectional = True
+
+    def __init__(self, d_pair: int = D_SUPPORTED, d_hidden: Optional[int] = None, implementation=None, p_drop: float = 0.0,
+                 residual: bool = True, check_status: bool = False):
+        super().__init__(d_pair, d_hidden, outgoing=True, implementation=implementation, p_drop=p_drop,
+                         residual=residual, check_status=check_status)

@@ -96,6 +96,7 @@ def trimul_forward_stages(
     biases: Optional[dict] = None,
     round_intermediates: bool = False,
     k_chunk: int = 0,
+    drop_scale: Optional[torch.Tensor] = None,
 ) -> Stages:
     """fp32 forward of TriangleMultiplication, returning every stage.
 
@@ -103,6 +104,9 @@ def trimul_forward_stages(
     [B,N,N] (non-zero = valid) or None.  ``params`` uses the reference's state_dict keys.
     ``round_intermediates`` rounds left/right/tri to bf16 where the GPU pipeline stores them
     (used only to attribute error, never as the parity target).
+    ``drop_scale`` [B,1,N,C] (row-shared dropout, keep-mask / (1 - p)) multiplies the update before the
+    residual is added, as the training path does (``scripts/check_trimul_module_reference.py:43,114-116``
+    in the reference project: a zero scale returns the input exactly).
     """
     p = {k: v.detach().to(torch.float32) for k, v in params.items()}
     bz = {k: None for k in BIAS_KEYS}
@@ -145,6 +149,8 @@ def trimul_forward_stages(
     proj = _lin(tn, p["to_out.weight"], bz["to_out"])
     gate = torch.sigmoid(_lin(x, p["to_gate.weight"], bz["to_gate"]))
     update = gate * proj
+    if drop_scale is not None:
+        update = update * drop_scale.detach().to(torch.float32)
     out = zf + update if residual else update
     return Stages(x_hat=x, left=left, right=right, tri=tri, update=update, out=out)
 
@@ -212,3 +218,77 @@ def trimul_forward_rows(
         upd = torch.sigmoid(x @ p["to_gate.weight"].T) * (tn @ p["to_out.weight"].T)
         out.append(zf + upd if residual else upd)
     return torch.stack(out)
+
+
+def bidir_forward_stages(
+    z: torch.Tensor,
+    params: dict,
+    mask: Optional[torch.Tensor] = None,
+    *,
+    eps_in: float = 1e-5,
+    eps_out: float = 1e-5,
+    pair_mask: Optional[torch.Tensor] = None,
+    residual: bool = True,
+    drop_scale: Optional[torch.Tensor] = None,
+) -> Stages:
+    """fp32 forward of BidirectionalTriangleMultiplication (``docs/paper/supplement.tex:125-136`` of the
+    reference project; the module MiniWorld's trunk builds, ``src/miniworld/modules/mini_pairformer.py:76-80``).
+
+    One input LayerNorm; ``to_left`` / ``to_left_gate`` / ``to_right`` / ``to_right_gate`` are [2h, C] and give
+    l, r in R^{2h}; the first h channels are contracted outgoing (sum_k l_ik r_jk), the last h incoming
+    (sum_k l_ki r_kj); one LayerNorm over the concatenated 2h channels, ``to_out`` [C, 2h], one gate
+    ``to_gate`` [C, C] on the normalised input, residual included. Mask semantics as in the unidirectional
+    module: the pair validity multiplies l and r only.
+    """
+    p = {k: v.detach().to(torch.float32) for k, v in params.items()}
+    zf = z.detach().to(torch.float32)
+    B, N, N2, C = zf.shape
+    assert N == N2
+    H2 = p["to_left.weight"].shape[0]
+    assert H2 % 2 == 0
+    h = H2 // 2
+    x = F.layer_norm(zf, (C,), p["ln_pair.weight"], p["ln_pair.bias"], eps_in)
+    left = torch.sigmoid(F.linear(x, p["to_left_gate.weight"])) * F.linear(x, p["to_left.weight"])
+    right = torch.sigmoid(F.linear(x, p["to_right_gate.weight"])) * F.linear(x, p["to_right.weight"])
+    valid = pair_valid(mask, pair_mask, B, N)
+    if valid is not None:
+        m = valid[..., None].to(torch.float32)
+        left = left * m
+        right = right * m
+    tri_out = torch.einsum("bikd,bjkd->bijd", left[..., :h], right[..., :h])
+    tri_in = torch.einsum("bkid,bkjd->bijd", left[..., h:], right[..., h:])
+    tri = torch.cat([tri_out, tri_in], dim=-1)
+    tn = F.layer_norm(tri, (H2,), p["ln_out.weight"], p["ln_out.bias"], eps_out)
+    update = torch.sigmoid(F.linear(x, p["to_gate.weight"])) * F.linear(tn, p["to_out.weight"])
+    if drop_scale is not None:
+        update = update * drop_scale.detach().to(torch.float32)
+    out = zf + update if residual else update
+    return Stages(x_hat=x, left=left, right=right, tri=tri, update=update, out=out)
+
+
+def bidir_forward(z, params, mask=None, **kw) -> torch.Tensor:
+    return bidir_forward_stages(z, params, mask, **kw).out
+
+
+TRANSITION_KEYS = ("ln_in.weight", "ln_in.bias", "expand_a.weight", "expand_b.weight", "squeeze.weight")
+
+
+def transition_forward(x: torch.Tensor, params: dict, *, eps: float = 1e-5, residual: bool = True) -> torch.Tensor:
+    """fp32 forward of the pair Transition that follows the triangle update in every block
+    (``src/miniworld/modules/mini_pairformer.py:81-84,108`` of the reference project):
+
+        y = x + squeeze( SiLU(expand_a(LN(x))) * expand_b(LN(x)) )
+
+    with ``expand_a`` / ``expand_b`` [n*C, C], ``squeeze`` [C, n*C], all bias-free, n = 4 (parameter names and the
+    OpenFold/Protenix mapping layernorm1 / linear_no_bias_a / linear_no_bias_b / linear_no_bias:
+    ``benchmarks/protenix_finetune/patch_engine.py:35-37``; the SwiGLU form h = SiLU(a) * b and the module-owned
+    residual: ``scripts/render_transition_fusion.py:218,262`` and ``docs/h100-kernel-upgrade.md:14``). PARITY
+    UNPINNED like the rest of this file: the module's source is in the same un-vendored wheel.
+    """
+    p = {k: v.detach().to(torch.float32) for k, v in params.items()}
+    xf = x.detach().to(torch.float32)
+    C = xf.shape[-1]
+    xn = F.layer_norm(xf, (C,), p["ln_in.weight"], p["ln_in.bias"], eps)
+    hdn = F.silu(F.linear(xn, p["expand_a.weight"])) * F.linear(xn, p["expand_b.weight"])
+    upd = F.linear(hdn, p["squeeze.weight"])
+    return xf + upd if residual else upd

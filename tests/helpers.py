@@ -43,7 +43,7 @@ def max_abs_split(y: torch.Tensor, ref: torch.Tensor) -> tuple[float, float]:
     return lo, hi
 
 
-def assert_module_parity(y_gpu: torch.Tensor, y_ref: torch.Tensor, z: torch.Tensor, what: str = "") -> None:
+def assert_module_parity(y_gpu: torch.Tensor, y_ref: torch.Tensor, z: torch.Tensor, what: str = "", check_update: bool = True) -> None:
     y = y_gpu.detach().float().cpu()
     ref = y_ref.detach().float().cpu()
     zf = z.detach().float().cpu()
@@ -60,4 +60,5 @@ def assert_module_parity(y_gpu: torch.Tensor, y_ref: torch.Tensor, z: torch.Tens
     limit = torch.maximum(torch.full_like(err, MAX_ABS_TOL), 0.75 * spacing)
     worst = float((err - limit).max())
     assert worst <= 0.0, (what, "max_abs", float(err.max()), "excess over limit", worst)
-    assert upd <= UPDATE_REL_TOL, (what, "update rel_frobenius", upd)
+    if check_update:  # meaningless where the update is smaller than the bf16 spacing of the output it is added to
+        assert upd <= UPDATE_REL_TOL, (what, "update rel_frobenius", upd)

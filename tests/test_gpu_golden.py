@@ -43,7 +43,9 @@ def test_module_output_matches_golden_vector(name):
     m.ln_pair.eps, m.ln_out.eps = case["eps_in"], case["eps_out"]
     with torch.no_grad():
         y = m(case["z"].to(DEV), None if arg is None else arg.to(DEV))
-    assert_module_parity(y, want, case["z"], name)
+    # all tokens masked: the update is sigmoid(g) * (W_o beta_out), about 1e-2, below the bf16 spacing of z + update,
+    # so its relative error says nothing; the output itself is still held to the bounds
+    assert_module_parity(y, want, case["z"], name, check_update=(name != "out_n16_allinvalid"))
     if name == "out_n16_allinvalid":
         # every token masked: left = right = 0, t = 0, LN_out(0) = beta_out; the update is sigmoid(g) * (W_o beta_out),
         # and the stored output pins it. With beta_out = 0 the module returns its input exactly.

@@ -137,4 +137,4 @@ def test_row_scheme_emulation_matches_single_gpu_forward(N, P, outgoing):
         # at the magnitudes of this input), nothing more
         err = (got.float() - want.float()).abs()
         assert float(err.max()) <= 0.0625, float(err.max())
-        assert oracle.rel_frobenius(got.float().cpu(), want.float().cpu()) < 2e-3
+        assert oracle.rel_frobenius(got.float().cpu(), want.float().cpu()) < 4e-3

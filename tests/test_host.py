@@ -33,9 +33,15 @@ def test_state_dict_layout_matches_the_reference_module():
 
 
 def test_layernorm_affine_stays_fp32_and_linears_follow_the_module_dtype():
-    m = mw.TriangleMultiplication(128).to(torch.bfloat16)
+    p = rand_params(3)
+    m = mw.TriangleMultiplication(128)
+    m.load_state_dict(p)
+    m = m.to(torch.bfloat16)
     assert m.ln_pair.weight.dtype == torch.float32 and m.ln_out.bias.dtype == torch.float32
     assert m.to_left.weight.dtype == torch.bfloat16
+    # pinned, not converted there and back: the fp32 values survive the module-wide cast bit for bit
+    for k in ("ln_pair.weight", "ln_pair.bias", "ln_out.weight", "ln_out.bias"):
+        assert torch.equal(m.state_dict()[k], p[k]), k
     m.ln_pair.eps = 0.03  # mutable attribute read at call time
     assert m.ln_pair.eps == 0.03
 
@@ -66,10 +72,8 @@ def test_unsupported_configurations_raise():
     m = mw.TriangleMultiplication(128)
     with pytest.raises(RuntimeError, match="CUDA"):
         m(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16))  # no CPU implementation, no fallback
-    m.p_drop = 0.1
-    m.train()
-    with pytest.raises(NotImplementedError):
-        m(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16))
+    with pytest.raises(NotImplementedError):  # no backward
+        m(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16, requires_grad=True))
     with pytest.raises(RuntimeError):
         mw.TriangleMultiplication(128).eval()(torch.zeros(1, 8, 8, 128), torch.ones(1, 8, 8, dtype=torch.bool))
 

@@ -128,3 +128,97 @@ def test_token_mask_equals_derived_pair_mask_and_einsum_directions():
     # channel-chunked contraction is the same contraction
     c = oracle.trimul_forward(z, p, tok, k_chunk=32)
     torch.testing.assert_close(c, oracle.trimul_forward(z, p, tok), rtol=1e-6, atol=1e-6)
+
+
+def _bidir_params(seed):
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    return {
+        "ln_pair.weight": 1.0 + 0.1 * rn(128), "ln_pair.bias": 0.2 * rn(128),
+        "to_left.weight": rn(64, 128) * 128**-0.5, "to_left_gate.weight": rn(64, 128) * 128**-0.5,
+        "to_right.weight": rn(64, 128) * 128**-0.5, "to_right_gate.weight": rn(64, 128) * 128**-0.5,
+        "ln_out.weight": 1.0 + 0.1 * rn(64), "ln_out.bias": 0.2 * rn(64),
+        "to_gate.weight": rn(128, 128) * 128**-0.5, "to_out.weight": rn(128, 64) * 64**-0.5,
+    }
+
+
+@pytest.mark.parametrize("with_scale", [False, True])
+def test_bidirectional_oracle_matches_c_restatement(with_scale):
+    """The torch restatement of the bidirectional module against the independent C one (h = 32 here: the split of the
+    2h channels into an outgoing and an incoming half, the LayerNorm over all 2h, the dropout scale)."""
+    lib = _c_ref()
+    dp = ctypes.POINTER(ctypes.c_double)
+    lib.trimul_ref_bidir_forward.restype = ctypes.c_int
+    lib.trimul_ref_bidir_forward.argtypes = [dp, ctypes.c_void_p] + [dp] * 10 + [ctypes.c_void_p] + [ctypes.c_int] * 3 + [ctypes.c_double] * 2 + [ctypes.c_int, dp]
+    N = 10
+    p = _bidir_params(51)
+    g = torch.Generator().manual_seed(52)
+    z = torch.randn(1, N, N, 128, generator=g)
+    mask = torch.rand(1, N, generator=g) > 0.3
+    scale = (torch.rand(1, 1, N, 128, generator=g) > 0.25).float() / 0.75 if with_scale else None
+    ref = oracle.bidir_forward(z, p, mask, eps_in=0.03, eps_out=0.07, drop_scale=scale)
+    valid = oracle.pair_valid(mask, None, 1, N)
+    keep, ptrs = [], []
+    for t in (z[0], p["ln_pair.weight"], p["ln_pair.bias"], p["to_left.weight"], p["to_left_gate.weight"], p["to_right.weight"],
+              p["to_right_gate.weight"], p["ln_out.weight"], p["ln_out.bias"], p["to_gate.weight"], p["to_out.weight"]):
+        a, ptr = _as_dp(t)
+        keep.append(a)
+        ptrs.append(ptr)
+    vm = np.ascontiguousarray(valid[0].numpy().astype(np.uint8))
+    sc = None
+    sptr = None
+    if scale is not None:
+        sc = np.ascontiguousarray(scale[0, 0].double().numpy())
+        sptr = sc.ctypes.data_as(ctypes.c_void_p)
+    out = np.zeros((N, N, 128), dtype=np.float64)
+    rc = lib.trimul_ref_bidir_forward(ptrs[0], vm.ctypes.data_as(ctypes.c_void_p), *ptrs[1:], sptr, N, 128, 32, 0.03, 0.07, 1,
+                                      out.ctypes.data_as(dp))
+    assert rc == 0
+    np.testing.assert_allclose(ref[0].numpy(), out, rtol=2e-4, atol=2e-4)
+    # the halves really are contracted in different directions: swapping them changes the result
+    st = oracle.bidir_forward_stages(z, p, mask)
+    h = 32
+    assert not torch.allclose(st.tri[..., :h], st.tri[..., h:])
+    # zero dropout scale returns the input exactly (reference: scripts/check_trimul_module_reference.py:114-116)
+    y0 = oracle.bidir_forward(z, p, mask, drop_scale=torch.zeros(1, 1, N, 128))
+    assert torch.equal(y0, z)
+
+
+def test_bidirectional_oracle_halves_equal_the_unidirectional_contractions():
+    p = _bidir_params(53)
+    g = torch.Generator().manual_seed(54)
+    z = torch.randn(1, 9, 9, 128, generator=g)
+    mask = torch.rand(1, 9, generator=g) > 0.3
+    st = oracle.bidir_forward_stages(z, p, mask)
+    for sl, outgoing in ((slice(0, 32), True), (slice(32, 64), False)):
+        q = {k: v for k, v in p.items()}
+        for k in ("to_left.weight", "to_left_gate.weight", "to_right.weight", "to_right_gate.weight"):
+            q[k] = p[k][sl]
+        q["ln_out.weight"], q["ln_out.bias"], q["to_out.weight"] = p["ln_out.weight"][sl], p["ln_out.bias"][sl], p["to_out.weight"][:, sl]
+        uni = oracle.trimul_forward_stages(z, q, mask, outgoing=outgoing)
+        torch.testing.assert_close(st.tri[..., sl], uni.tri, rtol=1e-5, atol=1e-5)
+
+
+def test_transition_oracle_matches_c_restatement():
+    lib = _c_ref()
+    dp = ctypes.POINTER(ctypes.c_double)
+    lib.transition_ref_forward.restype = ctypes.c_int
+    lib.transition_ref_forward.argtypes = [dp] * 6 + [ctypes.c_long, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_int, dp]
+    g = torch.Generator().manual_seed(61)
+    C, n = 128, 4
+    p = {"ln_in.weight": 1.0 + 0.1 * torch.randn(C, generator=g), "ln_in.bias": 0.2 * torch.randn(C, generator=g),
+         "expand_a.weight": torch.randn(n * C, C, generator=g) * C**-0.5, "expand_b.weight": torch.randn(n * C, C, generator=g) * C**-0.5,
+         "squeeze.weight": torch.randn(C, n * C, generator=g) * (n * C) ** -0.5}
+    x = torch.randn(2, 5, 5, C, generator=g)
+    ref = oracle.transition_forward(x, p, eps=0.02)
+    keep, ptrs = [], []
+    for t in (x.reshape(-1, C), p["ln_in.weight"], p["ln_in.bias"], p["expand_a.weight"], p["expand_b.weight"], p["squeeze.weight"]):
+        a, ptr = _as_dp(t)
+        keep.append(a)
+        ptrs.append(ptr)
+    out = np.zeros((50, C), dtype=np.float64)
+    rc = lib.transition_ref_forward(*ptrs, 50, C, n * C, 0.02, 1, out.ctypes.data_as(dp))
+    assert rc == 0
+    np.testing.assert_allclose(ref.reshape(50, C).numpy(), out, rtol=2e-4, atol=2e-4)
+    upd = oracle.transition_forward(x, p, eps=0.02, residual=False)
+    torch.testing.assert_close(upd + x, ref)

@@ -268,6 +268,22 @@ int b200_trimul_forward_static(const void* z, const void* w_left, const void* w_
                                int direction, float eps_in, float eps_out, int residual, int** device_status_out,
                                void* cuda_stream);
 
+/*
+ * Pair Transition, the operator on the other side of the triangle update in every block
+ * (src/miniworld/modules/mini_pairformer.py:81-84,108 in the reference project; the engine's fused kernel is
+ * `transition_fused_fwd_sm100a`, docs/phase2-b200-training-speed.md:165):
+ *   y = x + squeeze( SiLU(expand_a(LN(x))) * expand_b(LN(x)) ),  expand_a / expand_b: [4 d, d], squeeze: [d, 4 d], no biases
+ * (parameter names and the OpenFold mapping: benchmarks/protenix_finetune/patch_engine.py:35-37). d = 128, n = 4 only.
+ * x, y: [positions, 128] bf16 (any leading shape flattened; y may alias x); `packed`: b200_transition_packed_bytes()
+ * bytes, 1024-aligned, written by b200_transition_pack_weights (weights bf16 or fp32, LayerNorm affine fp32);
+ * `status`: a device int, zero before the call, receives a positive device code if a bounded wait runs out.
+ */
+size_t b200_transition_packed_bytes(void);
+int b200_transition_pack_weights(const void* w_expand_a, const void* w_expand_b, const void* w_squeeze, int weight_dtype,
+                                 const float* ln_w, const float* ln_b, void* packed, void* cuda_stream);
+int b200_transition_forward(const void* x, const void* packed, void* y, long long positions, int d, int n, float eps,
+                            int residual, int* status, void* cuda_stream);
+
 /* Zero the status words at the start of a workspace (asynchronous). */
 int b200_trimul_clear_status(int* status, void* cuda_stream);
 

@@ -7,6 +7,7 @@ batch-parallel multi-GPU wrappers.
 
 from .modules import (  # noqa: F401
     BidirectionalTriangleMultiplication,
+    Transition,
     TriangleMultiplication,
     TriangleMultiplicationIncoming,
     TriangleMultiplicationOutgoing,
@@ -17,6 +18,7 @@ from .modules import (  # noqa: F401
 __all__ = [
     "TriangleMultiplication",
     "BidirectionalTriangleMultiplication",
+    "Transition",
     "TriangleMultiplicationOutgoing",
     "TriangleMultiplicationIncoming",
     "to_openfold_state_dict",

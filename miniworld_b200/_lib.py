@@ -104,6 +104,12 @@ SIGNATURES = {
         + [c_int] * 5
         + [c_float, c_float, c_int, POINTER(c_void_p), c_void_p],
     ),
+    "b200_transition_packed_bytes": (c_size_t, []),
+    "b200_transition_pack_weights": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200_transition_forward": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    ),
     "b200_trimul_clear_status": (c_int, [c_void_p, c_void_p]),
     "b200_trimul_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
 }

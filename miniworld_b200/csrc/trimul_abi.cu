@@ -11,6 +11,7 @@
 #include "epilogue.cuh"
 #include "epilogue_wide.cuh"
 #include "prologue.cuh"
+#include "transition.cuh"
 
 namespace trimul {
 
@@ -1024,6 +1025,78 @@ int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_ga
                                 ln_in_b, ln_out_w, ln_out_b, bias_opt, token_mask, pair_mask, nullptr, y, workspace,
                                 workspace_bytes, B, N, d_pair, d_hidden, direction, eps_in, eps_out, residual,
                                 cuda_stream);
+}
+
+// --------------------------------------------------------------------------------------------- pair Transition
+size_t b200_transition_packed_bytes(void) { return kTrPackedBytes; }
+
+int b200_transition_pack_weights(const void* w_expand_a, const void* w_expand_b, const void* w_squeeze, int weight_dtype,
+                                 const float* ln_w, const float* ln_b, void* packed, void* cuda_stream) {
+  if (!w_expand_a || !w_expand_b || !w_squeeze || !ln_w || !ln_b || !packed) return B200_TRIMUL_E_NULL;
+  if (weight_dtype != B200_TRIMUL_DTYPE_BF16 && weight_dtype != B200_TRIMUL_DTYPE_F32) return B200_TRIMUL_E_SHAPE;
+  if (!aligned(packed, 1024)) return B200_TRIMUL_E_ALIGN;
+  TransitionPackArgs a;
+  a.w_a = w_expand_a;
+  a.w_b = w_expand_b;
+  a.w_s = w_squeeze;
+  a.ln_w = ln_w;
+  a.ln_b = ln_b;
+  a.f32_weights = weight_dtype == B200_TRIMUL_DTYPE_F32;
+  transition_pack_kernel<<<(1024 * 128 + 128 * 512) / 256, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      a, static_cast<uint8_t*>(packed));
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
+}
+
+int b200_transition_forward(const void* x, const void* packed, void* y, long long positions, int d, int n, float eps,
+                            int residual, int* status, void* cuda_stream) {
+  if (!x || !packed || !y || !status) return B200_TRIMUL_E_NULL;
+  if (d != kC || n != 4) return B200_TRIMUL_E_UNSUPPORTED;
+  if (positions < 1 || positions > 0x7FFFFFFFll - 512) return B200_TRIMUL_E_SHAPE;
+  if (!aligned(x, 16) || !aligned(y, 16) || !aligned(packed, 1024)) return B200_TRIMUL_E_ALIGN;
+  DeviceInfo info;
+  int rc = device_info(&info);
+  if (rc != B200_TRIMUL_OK) return rc;
+  CUtensorMap map_x, map_y, map_wab, map_ws;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(kC), static_cast<uint64_t>(positions)};
+    const uint64_t strides[1] = {kC * 2ull};
+    const uint32_t box[2] = {64, 128};
+    rc = make_map(&map_x, x, 2, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = make_map(&map_y, y, 2, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(kC), 1024ull};
+    const uint64_t strides[1] = {kC * 2ull};
+    const uint32_t box[2] = {64, 64};
+    rc = make_map(&map_wab, packed, 2, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {512ull, static_cast<uint64_t>(kC)};
+    const uint64_t strides[1] = {512 * 2ull};
+    const uint32_t box[2] = {64, 64};
+    rc = make_map(&map_ws, static_cast<const uint8_t*>(packed) + kTrPackedAbBytes, 2, dims, strides, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+  }
+  TransitionParams p;
+  p.positions = positions;
+  p.num_tiles = static_cast<int>((positions + 255) / 256);
+  p.ln_w = reinterpret_cast<const float*>(static_cast<const uint8_t*>(packed) + kTrPackedLnOff);
+  p.ln_b = p.ln_w + 128;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.eps = eps;
+  p.residual = residual;
+  p.status = status;
+  rc = set_smem(transition_kernel, kTrSmemBytes, info.device);
+  if (rc != B200_TRIMUL_OK) return rc;
+  const int pairs = p.num_tiles < info.sms / 2 ? p.num_tiles : info.sms / 2;
+  transition_kernel<<<2 * pairs, kTrThreads, kTrSmemBytes, static_cast<cudaStream_t>(cuda_stream)>>>(map_x, map_y, map_wab,
+                                                                                                   map_ws, p);
+  TRIMUL_CUDA(cudaGetLastError());
+  return B200_TRIMUL_OK;
 }
 
 }  // extern "C"

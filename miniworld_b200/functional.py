@@ -485,3 +485,51 @@ def trimul_forward(
     if check:
         check_status(workspace[:4].view(torch.int32), "b200_trimul_forward")
     return out
+
+
+# ------------------------------------------------------------------------------------------ pair Transition
+TRANSITION_KEYS = ("ln_in.weight", "ln_in.bias", "expand_a.weight", "expand_b.weight", "squeeze.weight")
+
+
+def transition_packed_bytes() -> int:
+    return int(_lib.load().b200_transition_packed_bytes())
+
+
+def transition_pack_weights(params: dict, packed: torch.Tensor) -> None:
+    """Pack ``expand_a`` / ``expand_b`` [512, 128], ``squeeze`` [128, 512] (bf16 or fp32) and the fp32 LayerNorm
+    affine into the block the transition kernel reads."""
+    wa, wb, wsq = params["expand_a.weight"], params["expand_b.weight"], params["squeeze.weight"]
+    g, b = params["ln_in.weight"], params["ln_in.bias"]
+    dt = wa.dtype
+    if dt not in (torch.bfloat16, torch.float32) or wb.dtype != dt or wsq.dtype != dt:
+        raise RuntimeError("the three transition weights must share one dtype, bf16 or fp32")
+    if tuple(wa.shape) != (4 * D, D) or tuple(wb.shape) != (4 * D, D) or tuple(wsq.shape) != (D, 4 * D):
+        raise RuntimeError(f"transition weights must be [{4 * D},{D}], [{4 * D},{D}], [{D},{4 * D}] (d = {D}, n = 4 only)")
+    for name, t in (("expand_a.weight", wa), ("expand_b.weight", wb), ("squeeze.weight", wsq), ("ln_in.weight", g), ("ln_in.bias", b)):
+        _require_cuda(t, name)
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    if g.dtype != torch.float32 or b.dtype != torch.float32 or tuple(g.shape) != (D,) or tuple(b.shape) != (D,):
+        raise RuntimeError(f"ln_in.weight / ln_in.bias must be fp32[{D}]")
+    with torch.cuda.device(packed.device):
+        rc = _lib.load().b200_transition_pack_weights(
+            _ptr(wa.detach()), _ptr(wb.detach()), _ptr(wsq.detach()), _lib.DTYPE_BF16 if dt == torch.bfloat16 else _lib.DTYPE_F32,
+            _ptr(g.detach()), _ptr(b.detach()), _ptr(packed), _stream(packed.device),
+        )
+    _lib.check(rc, "b200_transition_pack_weights")
+
+
+def transition_forward(x: torch.Tensor, packed: torch.Tensor, status: torch.Tensor, out: Optional[torch.Tensor] = None,
+                       eps: float = 1e-5, residual: bool = True) -> torch.Tensor:
+    """``y = x + squeeze(SiLU(expand_a(LN x)) * expand_b(LN x))`` for ``x`` [..., 128] bf16 (contiguous)."""
+    _require_cuda(x, "transition input")
+    if x.dtype != torch.bfloat16 or x.shape[-1] != D or not x.is_contiguous():
+        raise RuntimeError(f"transition input must be a contiguous bf16 tensor [..., {D}], got {x.dtype} {tuple(x.shape)}")
+    if out is None:
+        out = torch.empty_like(x)
+    positions = x.numel() // D
+    with torch.cuda.device(x.device):
+        rc = _lib.load().b200_transition_forward(_ptr(x), _ptr(packed), _ptr(out), positions, D, 4, float(eps),
+                                                 int(bool(residual)), _ptr(status), _stream(x.device))
+    _lib.check(rc, "b200_transition_forward")
+    return out

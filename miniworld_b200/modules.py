@@ -304,3 +304,64 @@ class BidirectionalTriangleMultiplication(TriangleMultiplication):
                  residual: bool = True, check_status: bool = False):
         super().__init__(d_pair, d_hidden, outgoing=True, implementation=implementation, p_drop=p_drop,
                          residual=residual, check_status=check_status)
+
+
+class Transition(nn.Module):
+    """Pair transition ``x + squeeze(SiLU(expand_a(LN x)) * expand_b(LN x))``, forward only, on the B200 kernel.
+
+    Mirrors ``miniworld_engine.modules.Transition(d, n=4, implementation=...)`` as MiniWorld's blocks build it
+    (``src/miniworld/modules/mini_pairformer.py:81-84``; it owns its residual, ``:108``): parameters ``ln_in`` [d],
+    ``expand_a`` / ``expand_b`` [n d, d], ``squeeze`` [d, n d], all linears bias-free
+    (``benchmarks/protenix_finetune/patch_engine.py:35-37``). d = 128 and n = 4 are what the kernel takes.
+    """
+
+    def __init__(self, d: int = D_SUPPORTED, n: int = 4, implementation=None, residual: bool = True, check_status: bool = False):
+        super().__init__()
+        if d != D_SUPPORTED or n != 4:
+            raise NotImplementedError(f"only d = {D_SUPPORTED}, n = 4 is implemented on this path (got d = {d}, n = {n})")
+        impl = getattr(implementation, "value", implementation)
+        impl = impl.lower() if isinstance(impl, str) else impl
+        if impl not in _ACCEPTED_IMPLEMENTATIONS:
+            raise ValueError(f"implementation={implementation!r}: this module has exactly one backend (B200 CUDA kernels)")
+        self.d, self.n = d, n
+        self.residual = bool(residual)
+        self.check_status = bool(check_status)
+        self.ln_in = Fp32LayerNorm(d, eps=1e-5)
+        self.expand_a = nn.Linear(d, n * d, bias=False)
+        self.expand_b = nn.Linear(d, n * d, bias=False)
+        self.squeeze = nn.Linear(n * d, d, bias=False)
+        nn.init.zeros_(self.squeeze.weight)  # the reference's final linears start at zero
+        self._scratch = None
+
+    def _apply(self, fn, recurse=True):
+        super()._apply(fn, recurse)
+        self._scratch = None
+        return self
+
+    def device_status(self) -> int:
+        return 0 if self._scratch is None else F_.read_status(self._scratch[1])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if torch.is_grad_enabled() and x.requires_grad:
+            raise NotImplementedError("backward is not implemented: call under torch.no_grad()")
+        if not x.is_cuda:
+            raise RuntimeError("input must be a CUDA tensor: this module has no CPU implementation")
+        if x.shape[-1] != self.d:
+            raise RuntimeError(f"input must be [..., {self.d}], got {tuple(x.shape)}")
+        in_dtype = x.dtype
+        xb = x.detach()
+        if xb.dtype != torch.bfloat16:
+            xb = xb.to(torch.bfloat16)
+        xb = xb.contiguous()
+        if self._scratch is None or self._scratch[0].device != xb.device:
+            self._scratch = (F_.aligned_empty(F_.transition_packed_bytes(), xb.device),
+                             torch.zeros(16, dtype=torch.int32, device=xb.device))
+        packed, status = self._scratch
+        params = {"ln_in.weight": self.ln_in.weight, "ln_in.bias": self.ln_in.bias, "expand_a.weight": self.expand_a.weight,
+                  "expand_b.weight": self.expand_b.weight, "squeeze.weight": self.squeeze.weight}
+        with torch.no_grad():
+            F_.transition_pack_weights(params, packed)  # packed in every call: a captured graph replays current weights
+            y = F_.transition_forward(xb, packed, status, eps=float(self.ln_in.eps), residual=self.residual)
+        if self.check_status:
+            F_.check_status(status, "b200_transition_forward")
+        return y if in_dtype == torch.bfloat16 else y.to(in_dtype)

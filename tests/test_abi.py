@@ -21,7 +21,7 @@ def lib():
 def _declared_symbols():
     text = open(os.path.join(ROOT, "include", "b200_trimul.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(b200_trimul_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(b200_(?:trimul|transition)_\w+)\s*\(", text)))
 
 
 def test_header_symbols_are_exported_and_bound(lib):

@@ -479,6 +479,11 @@ def run_b200(args):
             del r2
             torch.cuda.empty_cache()
 
+    # ---- the two neighbouring operators of a Pairformer block, single GPU, on the headline shape: the bidirectional
+    # triangle update MiniWorld's trunk builds and the pair Transition that follows it
+    if world == 1 and not args.no_extra:
+        extra.update(block_operators(r, max(3, min(args.steps, 10)), stream, dev))
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
@@ -526,6 +531,53 @@ def run_b200(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def block_operators(r: "Runner", steps: int, stream, dev) -> dict:
+    """CUDA-event times of BidirectionalTriangleMultiplication and Transition forwards on the headline input."""
+    import miniworld_b200 as mw
+
+    out = {}
+    peaks = measured_peaks()
+    gen = torch.Generator().manual_seed(77)
+
+    def rn(*shape):
+        return torch.randn(*shape, generator=gen)
+
+    bid = mw.BidirectionalTriangleMultiplication(128)
+    bid.load_state_dict({
+        "ln_pair.weight": 1.0 + 0.1 * rn(128), "ln_pair.bias": 0.02 * rn(128),
+        "to_left.weight": rn(256, 128) * 128**-0.5, "to_left_gate.weight": rn(256, 128) * 128**-0.5,
+        "to_right.weight": rn(256, 128) * 128**-0.5, "to_right_gate.weight": rn(256, 128) * 128**-0.5,
+        "ln_out.weight": 1.0 + 0.1 * rn(256), "ln_out.bias": 0.02 * rn(256),
+        "to_gate.weight": rn(128, 128) * 128**-0.5, "to_out.weight": rn(128, 256) * 256**-0.5})
+    bid = bid.to(dev).to(torch.bfloat16).eval()
+    tr = mw.Transition(128)
+    tr.load_state_dict({"ln_in.weight": 1.0 + 0.1 * rn(128), "ln_in.bias": 0.02 * rn(128),
+                        "expand_a.weight": rn(512, 128) * 128**-0.5, "expand_b.weight": rn(512, 128) * 128**-0.5,
+                        "squeeze.weight": rn(128, 512) * 512**-0.5})
+    tr = tr.to(dev).to(torch.bfloat16).eval()
+    cells = synthetic.cells(r.w)
+    with torch.no_grad():
+        for name, fn in (("bidirectional", lambda: bid(r.z, r.mask)), ("transition", lambda: tr(r.z))):
+            for _ in range(3):
+                fn()
+            ms = sorted(time_events(fn, steps, stream) / steps for _ in range(REPEATS))
+            entry = {"workload": r.name, "ms_per_forward": statistics.median(ms), "min": ms[0], "max": ms[-1],
+                     "value": cells / (statistics.median(ms) * 1e-3), "unit": UNIT}
+            if name == "transition":
+                fl = cells * 393216.0  # 2 * (2 * 128 * 512 + 512 * 128) FLOP per position
+                entry["roofline"] = {"kernel": "transition_kernel", "bound": "tensor", "flops_per_launch": fl,
+                                     "achieved": fl / (entry["ms_per_forward"] * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                     "peak": peaks["bf16_tflops"],
+                                     "frac": fl / (entry["ms_per_forward"] * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+            else:
+                entry["note"] = ("one operator = both directions: compare with ms_per_step of the headline, which is one "
+                                 "outgoing and one incoming module forward")
+            out[name] = entry
+    if bid.device_status() != 0 or tr.device_status() != 0:
+        raise SystemExit("bidirectional / transition forward reported a device status")
+    return out
 
 
 def stage_roofline(r: Runner, steps: int, stream, traffic):

@@ -240,6 +240,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 32 lanes x 16 consecutive 32-bit columns, registers -> TMEM (thread `lane` writes row lane base + lane).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------ UMMA descriptors
 // Shared-memory matrix descriptor, 128-byte swizzle, tile base 1024-byte aligned.
@@ -309,6 +319,14 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Arrive on the leader CTA's copy of a barrier: a plain local arrival in the leader itself (the cluster-addressed form
+// costs the arriving thread a few hundred cycles even when the target is its own CTA), the remote form in CTA 1.
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar, uint32_t my_rank) {
+  if (my_rank == 0)
+    mbar_arrive(bar);
+  else
+    mbar_arrive_cluster(map_to_cta(bar, 0));
+}
 // TMA load issued by either CTA of a pair; the completion bytes go to the mbarrier at `cluster_bar`
 // (normally the leader CTA's barrier). No cluster-wide broadcast of the data is involved: the tile lands in
 // the issuing CTA's own shared memory only.
@@ -345,6 +363,17 @@ __device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a_desc, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same with the A operand read from tensor memory (this CTA's 128 lanes, 16-bit elements packed two per 32-bit
+// column, K-major: 8 columns per 16-deep MMA) instead of shared memory.
+__device__ __forceinline__ void umma_pair_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrive (once the MMAs issued so far are complete) on the mbarrier at this offset in both CTAs of the pair.

@@ -10,16 +10,21 @@
 // 64 output rows of W_s), 24 KiB, because the MMAs of a pair read the B operand from both CTAs' shared memory.
 //
 //   G1(block): D1[pos, 0:64 | 64:128] = x_hat[pos, :] * [0.5 W_a(block) ; W_b(block)]^T     (M 256, N 128, K 128)
-//   SwiGLU   : h[pos, u] = a2 (1 + tanh a2) * b,  a2 = D1[pos, u] (= a / 2),  b = D1[pos, 64 + u]   -> fp16, shared memory
-//   G2(block): D2[pos, :] += h[pos, 0:64] * W_s[:, block]^T                                    (M 256, N 128, K 64)
+//   SwiGLU   : h[pos, u] = a2 (1 + tanh a2) * b,  a2 = D1[pos, u] (= a / 2),  b = D1[pos, 64 + u]   -> fp16, back into TMEM
+//   G2(block): D2[pos, :] += h[pos, 0:64] * W_s[:, block]^T                (M 256, N 128, K 64, A operand from TMEM)
 //
-// D1 is double-buffered in TMEM and so is h in shared memory, and the MMA thread runs G1 one block ahead of G2, so the
-// tensor pipe works on block k+1 while the SwiGLU warps turn block k into h. D2 is double-buffered across tiles.
+// h never touches shared memory: each SwiGLU thread overwrites the first columns of its own slice of the D1 buffer
+// with its 32 packed h values, and G2 takes its A operand from there. D1 is double-buffered, so the tensor pipe works
+// on G1 of block k+1 while the SwiGLU warps turn block k into h; a D1 buffer is reused by G1 of block k+2 once G2 of
+// block k is complete. D2 is double-buffered across tiles.
 // LayerNorm is done once per tile by dedicated warps, in place on the loaded tile (fp32 statistics, affine applied,
 // rounded to fp16 for the tensor cores); the residual re-reads x from global memory (L2) at the end of the tile.
 //
-// Warp roles (608 threads per CTA): warp 0 weight producer, warp 1 MMA issuer (leader CTA) / TMEM owner, warp 2
-// input-tile producer, warps 3-10 LayerNorm, warps 11-18 SwiGLU and the tile's final y = x + D2.
+// Warp roles (640 threads per CTA): warp 0 weight producer, warp 1 issuer of the G1 MMAs (leader CTA) / TMEM owner,
+// warp 2 input-tile producer, warp 3 issuer of the G2 MMAs (leader CTA), warps 4-11 LayerNorm, warps 12-19 SwiGLU and
+// the tile's final y = x + D2. G1 and G2 have an issuing thread each: issuing one 256 x 128 x 16 MMA costs about as
+// long as it runs, so a single thread that also waits for the SwiGLU warps between the two GEMMs leaves the tensor
+// pipe idle more than half of the time (measured: 330 us at 589 824 positions with one issuer).
 // Only mbarrier signals cross between the two CTAs. All waits are bounded.
 #pragma once
 
@@ -36,16 +41,24 @@ struct TransitionParams {
   float eps;
   int residual;
   int* status;
+#ifdef TR_STAMPS
+  long long* stamps;
+#endif
 };
 
-constexpr int kTrThreads = 608;
+#ifdef TR_STAMPS
+#define TR_STAMP(idx) do { if (pair == 0 && rank == 0) p.stamps[(idx)] = clock64(); } while (0)
+#else
+#define TR_STAMP(idx) do { } while (0)
+#endif
+
+constexpr int kTrThreads = 640;
 constexpr int kTrBlocks = 8;            // hidden blocks of 64 units
-constexpr int kTrWStages = 4;
+constexpr int kTrWStages = 6;
 constexpr int kTrWStageBytes = 24576;   // 16 KiB of W_a or W_b rows + 8 KiB of W_s rows
 constexpr int kTrXBytes = 32768;        // 128 positions x 128 channels, 16-bit
-constexpr int kTrHBytes = 16384;        // 128 positions x 64 hidden units, fp16
 constexpr int kTrBarBytes = 256;
-constexpr int kTrSmemBytes = 2 * kTrXBytes + kTrWStages * kTrWStageBytes + 2 * kTrHBytes + kTrBarBytes + 1024;
+constexpr int kTrSmemBytes = 2 * kTrXBytes + kTrWStages * kTrWStageBytes + kTrBarBytes + 1024;
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTrThreads, 1)
 transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
@@ -57,21 +70,18 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t x_base = smem_base;
   const uint32_t w_base = x_base + 2 * kTrXBytes;
-  const uint32_t h_base = w_base + WS * kTrWStageBytes;
-  const uint32_t bar_base = h_base + 2 * kTrHBytes;
+  const uint32_t bar_base = w_base + WS * kTrWStageBytes;
   // barriers ("leader": only the copy in CTA 0 is used; "both": the MMA commit signals the copy in each CTA)
   auto x_full = [&](int s) { return bar_base + 8u * (0 + s); };     // own: this CTA's tile has landed
   auto xn_ready = [&](int s) { return bar_base + 8u * (2 + s); };   // leader: 16 LayerNorm warps
   auto x_empty = [&](int s) { return bar_base + 8u * (4 + s); };    // own: the tile's y has been stored
   auto w_full = [&](int s) { return bar_base + 8u * (6 + s); };     // leader: bytes of both CTAs
-  auto w_empty = [&](int s) { return bar_base + 8u * (6 + WS + s); };  // both
+  auto blk_done = [&](int s) { return bar_base + 8u * (6 + WS + s); };  // both: G2 of the block in weight stage s is complete
   auto d1_full = [&](int b) { return bar_base + 8u * (6 + 2 * WS + b); };   // both
-  auto d1_empty = [&](int b) { return bar_base + 8u * (8 + 2 * WS + b); };  // leader: 16 SwiGLU warps
   auto h_full = [&](int b) { return bar_base + 8u * (10 + 2 * WS + b); };   // leader: 16 SwiGLU warps
-  auto h_empty = [&](int b) { return bar_base + 8u * (12 + 2 * WS + b); };  // both
   auto d2_full = [&](int b) { return bar_base + 8u * (14 + 2 * WS + b); };  // both
   auto d2_empty = [&](int b) { return bar_base + 8u * (16 + 2 * WS + b); }; // leader: 16 SwiGLU warps
-  constexpr int kBarOff = 2 * kTrXBytes + WS * kTrWStageBytes + 2 * kTrHBytes;
+  constexpr int kBarOff = 2 * kTrXBytes + WS * kTrWStageBytes;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kBarOff + 8 * (18 + 2 * WS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -87,15 +97,13 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       mbar_init(xn_ready(s), 16);
       mbar_init(x_empty(s), 1);
       mbar_init(d1_full(s), 1);
-      mbar_init(d1_empty(s), 16);
       mbar_init(h_full(s), 16);
-      mbar_init(h_empty(s), 1);
       mbar_init(d2_full(s), 1);
       mbar_init(d2_empty(s), 16);
     }
     for (int s = 0; s < WS; ++s) {
       mbar_init(w_full(s), 1);
-      mbar_init(w_empty(s), 1);
+      mbar_init(blk_done(s), 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -125,7 +133,7 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       for (long long gb = 0; gb < total; ++gb) {
         const int slot = static_cast<int>(gb % WS);
         const uint32_t ph = static_cast<uint32_t>((gb / WS) & 1);
-        if (!mbar_wait(w_empty(slot), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
+        if (!mbar_wait(blk_done(slot), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
         const int hb = static_cast<int>(gb % kTrBlocks);
         if (rank == 0) mbar_arrive_expect_tx(w_full(slot), 2 * kTrWStageBytes);  // bytes of both CTAs
         const uint32_t bar = map_to_cta(w_full(slot), lead);
@@ -168,20 +176,29 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       // every tile loaded here is consumed by this CTA's LayerNorm warps before the kernel ends: nothing to drain
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    // ------------------------------------------------------------ issuer of G1 (leader CTA only)
+    // D1[gb & 1] = x_hat * [W_a ; W_b](block)^T, as soon as the weights are there and the SwiGLU warps have taken the
+    // previous contents of that D1 buffer into registers.
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = umma_idesc(256, 128, false, false, kFmtF16, kFmtF16);
       const long long total = static_cast<long long>(my_tiles) * kTrBlocks;
-      bool ok = true;
-      auto g1 = [&](long long gb) -> bool {  // D1[gb & 1] = x_hat * [W_a ; W_b](block)^T
+      for (long long gb = 0; gb < total; ++gb) {
         const int t = static_cast<int>(gb / kTrBlocks);
         const int hb = static_cast<int>(gb % kTrBlocks);
         const int s = t & 1;
-        if (hb == 0 && !mbar_wait(xn_ready(s), (t >> 1) & 1, abort_flag, p.status, kDevTimeoutMma)) return false;
+        if (hb == 0 && !mbar_wait(xn_ready(s), (t >> 1) & 1, abort_flag, p.status, kDevTimeoutMma)) break;
         const int slot = static_cast<int>(gb % WS);
-        if (!mbar_wait(w_full(slot), static_cast<uint32_t>((gb / WS) & 1), abort_flag, p.status, kDevTimeoutMma)) return false;
+        if (gb < 32) TR_STAMP(gb * 8 + 0);
+        if (!mbar_wait(w_full(slot), static_cast<uint32_t>((gb / WS) & 1), abort_flag, p.status, kDevTimeoutMma)) break;
+        if (gb < 32) TR_STAMP(gb * 8 + 1);
         const int b = static_cast<int>(gb & 1);
-        if (!mbar_wait(d1_empty(b), static_cast<uint32_t>(((gb >> 1) & 1) ^ 1), abort_flag, p.status, kDevTimeoutMma)) return false;
+        if (gb >= 2) {  // the D1 buffer also holds h of block gb - 2 until G2 of that block is complete
+          const long long pb = gb - 2;
+          if (!mbar_wait(blk_done(static_cast<int>(pb % WS)), static_cast<uint32_t>((pb / WS) & 1), abort_flag, p.status,
+                         kDevTimeoutMma))
+            break;
+        }
+        if (gb < 32) TR_STAMP(gb * 8 + 2);
         tc_fence_after();
         const uint32_t xs = x_base + s * kTrXBytes;
         const uint32_t ws = w_base + slot * kTrWStageBytes;
@@ -192,39 +209,43 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           umma_pair(tmem_base + b * 128, da, db, idesc, ks != 0 ? 1u : 0u);
         }
         umma_commit_pair(d1_full(b));
-        return true;
-      };
-      auto g2 = [&](long long gb) -> bool {  // D2[t & 1] += h[gb & 1] * W_s(block)^T
+      }
+    }
+  } else if (warp == 3) {
+    // ------------------------------------------------------------ issuer of G2 (leader CTA only)
+    // D2[t & 1] += h[gb & 1] * W_s(block)^T once the SwiGLU warps of both CTAs have written h. G1 of the same block
+    // completed before h could be computed, so one commit after G2 says that the block's weight stage and its h
+    // buffer are both free.
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(256, 128, false, false, kFmtF16, kFmtF16);
+      const long long total = static_cast<long long>(my_tiles) * kTrBlocks;
+      for (long long gb = 0; gb < total; ++gb) {
         const int t = static_cast<int>(gb / kTrBlocks);
         const int hb = static_cast<int>(gb % kTrBlocks);
         const int b = static_cast<int>(gb & 1);
         const int slot = static_cast<int>(gb % WS);
-        if (hb == 0 && !mbar_wait(d2_empty(t & 1), ((t >> 1) & 1) ^ 1u, abort_flag, p.status, kDevTimeoutMma)) return false;
-        if (!mbar_wait(h_full(b), static_cast<uint32_t>((gb >> 1) & 1), abort_flag, p.status, kDevTimeoutMma)) return false;
+        if (hb == 0 && !mbar_wait(d2_empty(t & 1), ((t >> 1) & 1) ^ 1u, abort_flag, p.status, kDevTimeoutMma)) break;
+        if (gb < 32) TR_STAMP(gb * 8 + 3);
+        if (!mbar_wait(h_full(b), static_cast<uint32_t>((gb >> 1) & 1), abort_flag, p.status, kDevTimeoutMma)) break;
+        if (gb < 32) TR_STAMP(gb * 8 + 4);
         tc_fence_after();
-        const uint32_t hs = h_base + b * kTrHBytes;
         const uint32_t ws = w_base + slot * kTrWStageBytes + 16384;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t da = umma_desc_kmajor(hs) + static_cast<uint64_t>(ks * 2);
+          // h units 0-31 sit in columns 0-15 of the D1 buffer, units 32-63 in columns 32-47 (each SwiGLU thread writes
+          // into the columns it has read itself); 8 columns per 16-deep MMA
+          const uint32_t a_tmem = tmem_base + b * 128 + (ks >> 1) * 32 + (ks & 1) * 8;
           const uint64_t db = umma_desc_kmajor(ws) + static_cast<uint64_t>(ks * 2);
-          umma_pair(tmem_base + 256 + (t & 1) * 128, da, db, idesc, (hb | ks) != 0 ? 1u : 0u);
+          umma_pair_ta(tmem_base + 256 + (t & 1) * 128, a_tmem, db, idesc, (hb | ks) != 0 ? 1u : 0u);
         }
-        umma_commit_pair(w_empty(slot));  // both G1 and G2 of this block have read the weight stage
-        umma_commit_pair(h_empty(b));
+        umma_commit_pair(blk_done(slot));
         if (hb == kTrBlocks - 1) umma_commit_pair(d2_full(t & 1));
-        return true;
-      };
-      if (total > 0) ok = g1(0);
-      for (long long gb = 0; ok && gb < total; ++gb) {
-        if (gb + 1 < total) ok = g1(gb + 1);  // one block ahead: the tensor pipe works while block gb becomes h
-        if (ok) ok = g2(gb);
       }
     }
-  } else if (warp < 11) {
+  } else if (warp < 12) {
     // ------------------------------------------------------------ LayerNorm of this CTA's 128 positions, in place
     // Eight threads per position (16 channels each, their gamma / beta in registers), four passes of 32 positions.
-    const int ts = threadIdx.x - 96;  // 0 .. 255
+    const int ts = threadIdx.x - 128;  // 0 .. 255
     const int sub = ts & 7;           // 16-byte chunk: channels 8*sub .. 8*sub+7 of each 64-channel half
     const int slot = ts >> 3;         // position slot inside a pass
     float2 g[8], b[8];
@@ -284,13 +305,13 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       }
       fence_proxy_async_smem();  // x_hat was written through the generic proxy; the MMA reads it through the async one
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(xn_ready(s), 0));
+      if (lane == 0) mbar_arrive_leader(xn_ready(s), rank);
     }
   } else {
     // ------------------------------------------------------------ SwiGLU per block, then y = x + D2 per tile
     // Thread = one position (TMEM lane) and half of the columns: 32 of a block's 64 hidden units, 64 of the 128
     // output channels.
-    const int sw = warp - 11;          // 0 .. 7
+    const int sw = warp - 12;          // 0 .. 7
     const int q = warp & 3;            // TMEM lane quarter this warp may read
     const int uh = sw >> 2;            // which half of the columns (the two warps of a quarter take one half each)
     const int pos = q * 32 + lane;     // position inside this CTA's tile
@@ -310,38 +331,28 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           alive = false;
           break;
         }
+        if (gb < 32 && sw == 0 && lane == 0) TR_STAMP(gb * 8 + 5);
         tc_fence_after();
         uint32_t va[32], vb[32];
         tmem_ld32(tmem_base + lane_off + bsel * 128 + uh * 32, va);
         tmem_ld32(tmem_base + lane_off + bsel * 128 + 64 + uh * 32, vb);
         tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(d1_empty(bsel), 0));  // D1 may be overwritten by block gb + 2
+        if (gb < 32 && sw == 0 && lane == 0) TR_STAMP(gb * 8 + 7);
         uint32_t o[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 a2 = make_float2(__uint_as_float(va[2 * i]), __uint_as_float(va[2 * i + 1]));
           const float2 bb = make_float2(__uint_as_float(vb[2 * i]), __uint_as_float(vb[2 * i + 1]));
-          const float2 th = make_float2(tanh_approx(a2.x), tanh_approx(a2.y));
+          const float2 th = make_float2(tanh_approx(a2.x), tanh_approx(a2.y));  // (the packed fp16 form measured no faster)
           o[i] = pack_f16x2_sat(__fmul2_rn(__ffma2_rn(th, a2, a2), bb));
         }
-        // the h buffer is free once G2 of block gb - 2 has read it
-        if (!mbar_wait_warp(h_empty(bsel), bph ^ 1u, abort_flag, p.status, kDevTimeoutEpilogue)) {
-          alive = false;
-          break;
-        }
-        const uint32_t hrow = h_base + bsel * kTrHBytes + pos * 128;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t addr = hrow + (((uh * 4 + c) ^ (pos & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[4 * c]), "r"(o[4 * c + 1]),
-                       "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
-                       : "memory");
-        }
-        fence_proxy_async_smem();
+        if (gb < 32 && sw == 0 && lane == 0) TR_STAMP(gb * 8 + 6);
+        // h goes where this thread's own a-values were: nobody else reads or writes these columns of these lanes
+        tmem_st16(tmem_base + lane_off + bsel * 128 + uh * 32, o);
+        tmem_st_wait();
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(h_full(bsel), 0));
+        if (lane == 0) mbar_arrive_leader(h_full(bsel), rank);
       }
       if (!named_bar_and(1, 256, alive)) break;
       // ---- y = x + D2 for this thread's position and 64 channels
@@ -368,7 +379,7 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (hf == 1) {
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(map_to_cta(d2_empty(t & 1), 0));
+          if (lane == 0) mbar_arrive_leader(d2_empty(t & 1), rank);
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {

@@ -226,11 +226,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       const int row = tile / p.tiles_per_row;
       const int j0 = (tile - row * p.tiles_per_row) * 128;
       {
-#ifdef VAR_SINGLE_POLL_EPI
-        const bool got = wg == 0 ? mbar_wait_warp(t_full(grp), ph, abort_flag, p.status, kDevTimeoutStats) : true;
-#else
         const bool got = mbar_wait_warp(t_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
-#endif
         if (!named_bar_and(bar_id, 256, got)) break;
       }
       // ---- output partial statistics: two adjacent positions, 32 channels of the t tile
@@ -255,11 +251,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
                      : "memory");
       }
       {
-#ifdef VAR_SINGLE_POLL_EPI
-        const bool got = wg == 0 ? mbar_wait_warp(z_full(grp), ph, abort_flag, p.status, kDevTimeoutStats) : true;
-#else
         const bool got = mbar_wait_warp(z_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
-#endif
         if (!named_bar_and(bar_id, 256, got)) break;
       }
       // ---- input partial statistics over this thread's 64 channels of its z row (kept for the residual)
@@ -319,11 +311,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       const float2 rs_out2 = make_float2(rs_out, rs_out), nmr_out2 = make_float2(nmr_out, nmr_out);
 
       {
-#ifdef VAR_SINGLE_POLL_EPI
-        const bool got = wg == 0 ? mbar_wait_warp(acc_full(grp), ph, abort_flag, p.status, kDevTimeoutEpilogue) : true;
-#else
         const bool got = mbar_wait_warp(acc_full(grp), ph, abort_flag, p.status, kDevTimeoutEpilogue);
-#endif
         if (!named_bar_and(bar_id, 256, got)) break;
       }
       tc_fence_after();

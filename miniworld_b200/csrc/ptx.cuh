@@ -81,19 +81,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-#ifdef VAR_LIGHT_POLL
-  while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i)
-      if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
-    if (*abort_flag != 0) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
-      *abort_flag = code;
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-#else
   while (true) {
     if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
     if (*abort_flag != 0) return false;
@@ -103,7 +90,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
-#endif
 }
 
 // Warp-level bounded wait: lane 0 polls, the other lanes sleep at the shuffle instead of burning issue slots.
@@ -313,9 +299,15 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
 // Arrive on an mbarrier that may live in the other CTA of the cluster (address from map_to_cta). Default
-// semantics (release at CTA scope): the cluster-scope release form stalled the arriving thread for about
-// 1400 cycles per arrival. What the waiter consumes is ordered by other means: TMEM reads by
+// semantics (release at CTA scope). What the waiter consumes is ordered by other means: TMEM reads by
 // tcgen05.wait::ld + tcgen05.fence, shared-memory operands by fence.proxy.async before the arrival.
+// The cluster-scope forms were measured on the prologue at N = 768 and rejected for their cost: arriving with
+// mbarrier.arrive.release.cluster from the writing warps themselves 129 -> 162 us; a relay warp that forwards one
+// cluster-scope release per tile (writers arrive on a barrier of their own CTA, the MMA thread waits with
+// acquire.cluster) plus a CTA-local barrier for the validity bitmap 107.5 -> 116.3 us, the same with
+// fence.acq_rel.cluster before a plain arrival, 126 us when the relay covers two tiles per fence (the signal's
+// latency is on the critical path). The CTA-scope form is kept; it is checked by bit-exact repeat runs
+// (tests/test_gpu_determinism.py) and by every parity test.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }

@@ -41,16 +41,7 @@ struct TransitionParams {
   float eps;
   int residual;
   int* status;
-#ifdef TR_STAMPS
-  long long* stamps;
-#endif
 };
-
-#ifdef TR_STAMPS
-#define TR_STAMP(idx) do { if (pair == 0 && rank == 0) p.stamps[(idx)] = clock64(); } while (0)
-#else
-#define TR_STAMP(idx) do { } while (0)
-#endif
 
 constexpr int kTrThreads = 640;
 constexpr int kTrBlocks = 8;            // hidden blocks of 64 units
@@ -188,9 +179,7 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int s = t & 1;
         if (hb == 0 && !mbar_wait(xn_ready(s), (t >> 1) & 1, abort_flag, p.status, kDevTimeoutMma)) break;
         const int slot = static_cast<int>(gb % WS);
-        if (gb < 32) TR_STAMP(gb * 8 + 0);
         if (!mbar_wait(w_full(slot), static_cast<uint32_t>((gb / WS) & 1), abort_flag, p.status, kDevTimeoutMma)) break;
-        if (gb < 32) TR_STAMP(gb * 8 + 1);
         const int b = static_cast<int>(gb & 1);
         if (gb >= 2) {  // the D1 buffer also holds h of block gb - 2 until G2 of that block is complete
           const long long pb = gb - 2;
@@ -198,7 +187,6 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                          kDevTimeoutMma))
             break;
         }
-        if (gb < 32) TR_STAMP(gb * 8 + 2);
         tc_fence_after();
         const uint32_t xs = x_base + s * kTrXBytes;
         const uint32_t ws = w_base + slot * kTrWStageBytes;
@@ -225,9 +213,7 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int b = static_cast<int>(gb & 1);
         const int slot = static_cast<int>(gb % WS);
         if (hb == 0 && !mbar_wait(d2_empty(t & 1), ((t >> 1) & 1) ^ 1u, abort_flag, p.status, kDevTimeoutMma)) break;
-        if (gb < 32) TR_STAMP(gb * 8 + 3);
         if (!mbar_wait(h_full(b), static_cast<uint32_t>((gb >> 1) & 1), abort_flag, p.status, kDevTimeoutMma)) break;
-        if (gb < 32) TR_STAMP(gb * 8 + 4);
         tc_fence_after();
         const uint32_t ws = w_base + slot * kTrWStageBytes + 16384;
 #pragma unroll
@@ -331,13 +317,11 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           alive = false;
           break;
         }
-        if (gb < 32 && sw == 0 && lane == 0) TR_STAMP(gb * 8 + 5);
         tc_fence_after();
         uint32_t va[32], vb[32];
         tmem_ld32(tmem_base + lane_off + bsel * 128 + uh * 32, va);
         tmem_ld32(tmem_base + lane_off + bsel * 128 + 64 + uh * 32, vb);
         tmem_ld_wait();
-        if (gb < 32 && sw == 0 && lane == 0) TR_STAMP(gb * 8 + 7);
         uint32_t o[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -346,7 +330,6 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           const float2 th = make_float2(tanh_approx(a2.x), tanh_approx(a2.y));  // (the packed fp16 form measured no faster)
           o[i] = pack_f16x2_sat(__fmul2_rn(__ffma2_rn(th, a2, a2), bb));
         }
-        if (gb < 32 && sw == 0 && lane == 0) TR_STAMP(gb * 8 + 6);
         // h goes where this thread's own a-values were: nobody else reads or writes these columns of these lanes
         tmem_st16(tmem_base + lane_off + bsel * 128 + uh * 32, o);
         tmem_st_wait();

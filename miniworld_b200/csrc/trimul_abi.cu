@@ -1090,9 +1090,6 @@ int b200_transition_forward(const void* x, const void* packed, void* y, long lon
   p.eps = eps;
   p.residual = residual;
   p.status = status;
-#ifdef TR_STAMPS
-  p.stamps = reinterpret_cast<long long*>(status + 16);  // debug build: 256 time stamps after the status words
-#endif
   rc = set_smem(transition_kernel, kTrSmemBytes, info.device);
   if (rc != B200_TRIMUL_OK) return rc;
   const int pairs = p.num_tiles < info.sms / 2 ? p.num_tiles : info.sms / 2;

@@ -672,11 +672,18 @@ def main():
     ap.add_argument("--workload", default="crop768", choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the shorter runs of the other benchmark workloads")
+    ap.add_argument("--operators-only", action="store_true",
+                    help="run only the bidirectional and transition forwards on the workload (for profiler captures)")
     ap.add_argument("--contraction", choices=["auto", "rows", "channels"], default="auto",
                     help="several GPUs: how the contraction is split (auto: channels from 4 GPUs on)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.operators_only:
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        r = Runner(args.workload, 1, 0, dev)
+        print(json.dumps({"operators": block_operators(r, args.steps, torch.cuda.current_stream(dev), dev)}), flush=True)
     else:
         run_b200(args)
 

@@ -10,21 +10,26 @@
 // 64 output rows of W_s), 24 KiB, because the MMAs of a pair read the B operand from both CTAs' shared memory.
 //
 //   G1(block): D1[pos, 0:64 | 64:128] = x_hat[pos, :] * [0.5 W_a(block) ; W_b(block)]^T     (M 256, N 128, K 128)
-//   SwiGLU   : h[pos, u] = a2 (1 + tanh a2) * b,  a2 = D1[pos, u] (= a / 2),  b = D1[pos, 64 + u]   -> fp16, back into TMEM
+//   SwiGLU   : h[pos, u] = a2 (1 + tanh a2) * b,  a2 = D1[pos, u] (= a / 2),  b = D1[pos, 64 + u]   -> fp16, into TMEM
 //   G2(block): D2[pos, :] += h[pos, 0:64] * W_s[:, block]^T                (M 256, N 128, K 64, A operand from TMEM)
 //
-// h never touches shared memory: each SwiGLU thread overwrites the first columns of its own slice of the D1 buffer
-// with its 32 packed h values, and G2 takes its A operand from there. D1 is double-buffered, so the tensor pipe works
-// on G1 of block k+1 while the SwiGLU warps turn block k into h; a D1 buffer is reused by G1 of block k+2 once G2 of
-// block k is complete. D2 is double-buffered across tiles.
+// Tensor memory (512 columns per CTA): D1[0], D1[1] (128 each) and D2[0], D2[1] (128 each, alternating by tile).
+// h never touches shared memory: the SwiGLU threads store it with tcgen05.st into the first 64 columns of the D2
+// buffer that is NOT accumulating during the tile (H[g] = 32 columns per group: 64 fp16 per lane), and G2 reads its A
+// operand from there. Two groups of SwiGLU warps take alternate blocks (group g: blocks with k & 1 == g, D1[g],
+// H[g]), so the tensor pipe runs G1 of block k+1 and G2 of block k-1 while block k is turned into h; a D1 buffer is
+// free as soon as its values are in registers, an H buffer once G2 of its block is complete. A separate group of
+// warps writes the tile's y = x + D2, so the SwiGLU groups never leave the block loop; the first h of a tile waits
+// until that group has read the D2 buffer h is about to borrow.
 // LayerNorm is done once per tile by dedicated warps, in place on the loaded tile (fp32 statistics, affine applied,
 // rounded to fp16 for the tensor cores); the residual re-reads x from global memory (L2) at the end of the tile.
 //
-// Warp roles (640 threads per CTA): warp 0 weight producer, warp 1 issuer of the G1 MMAs (leader CTA) / TMEM owner,
-// warp 2 input-tile producer, warp 3 issuer of the G2 MMAs (leader CTA), warps 4-11 LayerNorm, warps 12-19 SwiGLU and
-// the tile's final y = x + D2. G1 and G2 have an issuing thread each: issuing one 256 x 128 x 16 MMA costs about as
-// long as it runs, so a single thread that also waits for the SwiGLU warps between the two GEMMs leaves the tensor
-// pipe idle more than half of the time (measured: 330 us at 589 824 positions with one issuer).
+// Warp roles (768 threads per CTA): warp 0 weight producer, warp 1 issuer of the G1 MMAs (leader CTA) / TMEM owner,
+// warp 2 input-tile producer, warp 3 issuer of the G2 MMAs (leader CTA), warps 4-11 LayerNorm (four of them took
+// 19 k cycles per tile next to the busy SwiGLU warps instead of 4 k alone), warps 12-15 and 16-19 the two SwiGLU
+// groups (one thread per position, 64 hidden units per block in four passes of 16), warps 20-23 the output group.
+// G1 and G2 have an issuing thread each: issuing one 256 x 128 x 16 MMA costs about as long as it runs, so a single
+// thread that also waits for the SwiGLU warps between the two GEMMs leaves the tensor pipe idle half of the time.
 // Only mbarrier signals cross between the two CTAs. All waits are bounded.
 #pragma once
 
@@ -43,37 +48,43 @@ struct TransitionParams {
   int* status;
 };
 
-constexpr int kTrThreads = 640;
+constexpr int kTrThreads = 768;
 constexpr int kTrBlocks = 8;            // hidden blocks of 64 units
-constexpr int kTrWStages = 6;
+constexpr int kTrWStages = 5;
+constexpr int kTrXStages = 3;           // input tiles in flight: LayerNorm of tile t + 2 runs while tile t is still being written out
 constexpr int kTrWStageBytes = 24576;   // 16 KiB of W_a or W_b rows + 8 KiB of W_s rows
 constexpr int kTrXBytes = 32768;        // 128 positions x 128 channels, 16-bit
 constexpr int kTrBarBytes = 256;
-constexpr int kTrSmemBytes = 2 * kTrXBytes + kTrWStages * kTrWStageBytes + kTrBarBytes + 1024;
+constexpr int kTrSmemBytes = kTrXStages * kTrXBytes + kTrWStages * kTrWStageBytes + kTrBarBytes + 1024;
+constexpr uint32_t kTrColD2 = 256;      // tensor-memory columns: D1[b] at b * 128, D2[b] at kTrColD2 + b * 128
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTrThreads, 1)
 transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                   const __grid_constant__ CUtensorMap map_wab, const __grid_constant__ CUtensorMap map_ws,
                   const TransitionParams p) {
   constexpr int WS = kTrWStages;
+  constexpr int XS = kTrXStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t x_base = smem_base;
-  const uint32_t w_base = x_base + 2 * kTrXBytes;
+  const uint32_t w_base = x_base + XS * kTrXBytes;
   const uint32_t bar_base = w_base + WS * kTrWStageBytes;
   // barriers ("leader": only the copy in CTA 0 is used; "both": the MMA commit signals the copy in each CTA)
-  auto x_full = [&](int s) { return bar_base + 8u * (0 + s); };     // own: this CTA's tile has landed
-  auto xn_ready = [&](int s) { return bar_base + 8u * (2 + s); };   // leader: 16 LayerNorm warps
-  auto x_empty = [&](int s) { return bar_base + 8u * (4 + s); };    // own: the tile's y has been stored
-  auto w_full = [&](int s) { return bar_base + 8u * (6 + s); };     // leader: bytes of both CTAs
-  auto blk_done = [&](int s) { return bar_base + 8u * (6 + WS + s); };  // both: G2 of the block in weight stage s is complete
-  auto d1_full = [&](int b) { return bar_base + 8u * (6 + 2 * WS + b); };   // both
-  auto h_full = [&](int b) { return bar_base + 8u * (10 + 2 * WS + b); };   // leader: 16 SwiGLU warps
-  auto d2_full = [&](int b) { return bar_base + 8u * (14 + 2 * WS + b); };  // both
-  auto d2_empty = [&](int b) { return bar_base + 8u * (16 + 2 * WS + b); }; // leader: 16 SwiGLU warps
-  constexpr int kBarOff = 2 * kTrXBytes + WS * kTrWStageBytes;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kBarOff + 8 * (18 + 2 * WS));
+  auto x_full = [&](int s) { return bar_base + 8u * (0 + s); };          // own: this CTA's tile has landed
+  auto xn_ready = [&](int s) { return bar_base + 8u * (XS + s); };       // leader: 16 LayerNorm warps (8 per CTA)
+  auto x_empty = [&](int s) { return bar_base + 8u * (2 * XS + s); };    // own: the tile's y has been stored
+  constexpr int B0 = 3 * XS;
+  auto w_full = [&](int s) { return bar_base + 8u * (B0 + s); };         // leader: bytes of both CTAs
+  auto blk_done = [&](int s) { return bar_base + 8u * (B0 + WS + s); };  // both: G2 of the block in weight stage s is complete
+  auto d1_full = [&](int b) { return bar_base + 8u * (B0 + 2 * WS + b); };       // both
+  auto d1_empty = [&](int b) { return bar_base + 8u * (B0 + 2 * WS + 2 + b); };  // leader: 8 warps (group b of both CTAs)
+  auto h_full = [&](int b) { return bar_base + 8u * (B0 + 2 * WS + 4 + b); };    // leader: 8 warps (group b of both CTAs)
+  auto d2_full = [&](int b) { return bar_base + 8u * (B0 + 2 * WS + 6 + b); };   // both
+  auto d2_empty = [&](int b) { return bar_base + 8u * (B0 + 2 * WS + 8 + b); };  // leader: 8 warps (output group of both CTAs)
+  auto d2_read = [&](int b) { return bar_base + 8u * (B0 + 2 * WS + 10 + b); };  // own: this CTA's output group has read D2[b]
+  constexpr int kBarOff = XS * kTrXBytes + WS * kTrWStageBytes;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kBarOff + 8 * (B0 + 2 * WS + 12));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -83,14 +94,18 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const int num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < XS; ++s) {
       mbar_init(x_full(s), 1);
       mbar_init(xn_ready(s), 16);
       mbar_init(x_empty(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(d1_full(s), 1);
-      mbar_init(h_full(s), 16);
+      mbar_init(d1_empty(s), 8);
+      mbar_init(h_full(s), 8);
       mbar_init(d2_full(s), 1);
-      mbar_init(d2_empty(s), 16);
+      mbar_init(d2_empty(s), 8);
+      mbar_init(d2_read(s), 4);
     }
     for (int s = 0; s < WS; ++s) {
       mbar_init(w_full(s), 1);
@@ -120,14 +135,13 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // ------------------------------------------------------------ weight producer (both CTAs): 8 blocks per tile
     if (lane == 0) {
       const long long total = static_cast<long long>(my_tiles) * kTrBlocks;
-      const uint32_t lead = 0;
       for (long long gb = 0; gb < total; ++gb) {
         const int slot = static_cast<int>(gb % WS);
         const uint32_t ph = static_cast<uint32_t>((gb / WS) & 1);
         if (!mbar_wait(blk_done(slot), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
         const int hb = static_cast<int>(gb % kTrBlocks);
         if (rank == 0) mbar_arrive_expect_tx(w_full(slot), 2 * kTrWStageBytes);  // bytes of both CTAs
-        const uint32_t bar = map_to_cta(w_full(slot), lead);
+        const uint32_t bar = map_to_cta(w_full(slot), 0);
         const uint32_t ws = w_base + slot * kTrWStageBytes;
         // [0.5 W_a ; W_b] packed per block: rows hb*128 .. +63 are W_a's units, +64 .. +127 W_b's; two 64-wide k halves
         const int row_ab = hb * 128 + static_cast<int>(rank) * 64;
@@ -155,8 +169,8 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // ------------------------------------------------------------ input-tile producer (both CTAs)
     if (lane == 0) {
       for (int t = 0; t < my_tiles; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+        const int s = t % XS;
+        const uint32_t ph = (t / XS) & 1;
         if (!mbar_wait(x_empty(s), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
         const int tile = pair + t * num_pairs;
         const int row0 = tile * 256 + static_cast<int>(rank) * 128;  // rows past the end read as zero
@@ -168,25 +182,20 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ issuer of G1 (leader CTA only)
-    // D1[gb & 1] = x_hat * [W_a ; W_b](block)^T, as soon as the weights are there and the SwiGLU warps have taken the
-    // previous contents of that D1 buffer into registers.
+    // D1[gb & 1] = x_hat * [W_a ; W_b](block)^T, as soon as the weights are there and the SwiGLU group of that buffer
+    // has taken its previous contents into registers.
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = umma_idesc(256, 128, false, false, kFmtF16, kFmtF16);
       const long long total = static_cast<long long>(my_tiles) * kTrBlocks;
       for (long long gb = 0; gb < total; ++gb) {
         const int t = static_cast<int>(gb / kTrBlocks);
         const int hb = static_cast<int>(gb % kTrBlocks);
-        const int s = t & 1;
-        if (hb == 0 && !mbar_wait(xn_ready(s), (t >> 1) & 1, abort_flag, p.status, kDevTimeoutMma)) break;
+        const int s = t % XS;
+        if (hb == 0 && !mbar_wait(xn_ready(s), (t / XS) & 1, abort_flag, p.status, kDevTimeoutMma)) break;
         const int slot = static_cast<int>(gb % WS);
         if (!mbar_wait(w_full(slot), static_cast<uint32_t>((gb / WS) & 1), abort_flag, p.status, kDevTimeoutMma)) break;
         const int b = static_cast<int>(gb & 1);
-        if (gb >= 2) {  // the D1 buffer also holds h of block gb - 2 until G2 of that block is complete
-          const long long pb = gb - 2;
-          if (!mbar_wait(blk_done(static_cast<int>(pb % WS)), static_cast<uint32_t>((pb / WS) & 1), abort_flag, p.status,
-                         kDevTimeoutMma))
-            break;
-        }
+        if (!mbar_wait(d1_empty(b), static_cast<uint32_t>(((gb >> 1) & 1) ^ 1), abort_flag, p.status, kDevTimeoutMma)) break;
         tc_fence_after();
         const uint32_t xs = x_base + s * kTrXBytes;
         const uint32_t ws = w_base + slot * kTrWStageBytes;
@@ -201,9 +210,8 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   } else if (warp == 3) {
     // ------------------------------------------------------------ issuer of G2 (leader CTA only)
-    // D2[t & 1] += h[gb & 1] * W_s(block)^T once the SwiGLU warps of both CTAs have written h. G1 of the same block
-    // completed before h could be computed, so one commit after G2 says that the block's weight stage and its h
-    // buffer are both free.
+    // D2 += H[gb & 1] * W_s(block)^T once the SwiGLU warps of both CTAs have written h. G1 of the same block completed
+    // before h could be computed, so one commit after G2 says that the block's weight stage and its H buffer are free.
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = umma_idesc(256, 128, false, false, kFmtF16, kFmtF16);
       const long long total = static_cast<long long>(my_tiles) * kTrBlocks;
@@ -212,17 +220,18 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int hb = static_cast<int>(gb % kTrBlocks);
         const int b = static_cast<int>(gb & 1);
         const int slot = static_cast<int>(gb % WS);
+        // D2[t & 1] last held tile t - 2 (and lent its first columns to h during tile t - 1, whose G2s this thread has
+        // issued before): wait until the output group has read tile t - 2 out of it
         if (hb == 0 && !mbar_wait(d2_empty(t & 1), ((t >> 1) & 1) ^ 1u, abort_flag, p.status, kDevTimeoutMma)) break;
         if (!mbar_wait(h_full(b), static_cast<uint32_t>((gb >> 1) & 1), abort_flag, p.status, kDevTimeoutMma)) break;
         tc_fence_after();
         const uint32_t ws = w_base + slot * kTrWStageBytes + 16384;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          // h units 0-31 sit in columns 0-15 of the D1 buffer, units 32-63 in columns 32-47 (each SwiGLU thread writes
-          // into the columns it has read itself); 8 columns per 16-deep MMA
-          const uint32_t a_tmem = tmem_base + b * 128 + (ks >> 1) * 32 + (ks & 1) * 8;
+          // H[b]: 32 columns of the D2 buffer that is idle during this tile; 8 columns = 16 fp16 per 16-deep MMA
+          const uint32_t a_tmem = tmem_base + kTrColD2 + ((t + 1) & 1) * 128 + b * 32 + ks * 8;
           const uint64_t db = umma_desc_kmajor(ws) + static_cast<uint64_t>(ks * 2);
-          umma_pair_ta(tmem_base + 256 + (t & 1) * 128, a_tmem, db, idesc, (hb | ks) != 0 ? 1u : 0u);
+          umma_pair_ta(tmem_base + kTrColD2 + (t & 1) * 128, a_tmem, db, idesc, (hb | ks) != 0 ? 1u : 0u);
         }
         umma_commit_pair(blk_done(slot));
         if (hb == kTrBlocks - 1) umma_commit_pair(d2_full(t & 1));
@@ -232,8 +241,8 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // ------------------------------------------------------------ LayerNorm of this CTA's 128 positions, in place
     // Eight threads per position (16 channels each, their gamma / beta in registers), four passes of 32 positions.
     const int ts = threadIdx.x - 128;  // 0 .. 255
-    const int sub = ts & 7;           // 16-byte chunk: channels 8*sub .. 8*sub+7 of each 64-channel half
-    const int slot = ts >> 3;         // position slot inside a pass
+    const int sub = ts & 7;            // 16-byte chunk: channels 8*sub .. 8*sub+7 of each 64-channel half
+    const int slot = ts >> 3;          // position slot inside a pass
     float2 g[8], b[8];
 #pragma unroll
     for (int half = 0; half < 2; ++half)
@@ -244,8 +253,8 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         b[half * 4 + t] = make_float2(p.ln_b[c], p.ln_b[c + 1]);
       }
     for (int t = 0; t < my_tiles; ++t) {
-      const int s = t & 1;
-      if (!mbar_wait_warp(x_full(s), (t >> 1) & 1, abort_flag, p.status, kDevTimeoutStats)) break;
+      const int s = t % XS;
+      if (!mbar_wait_warp(x_full(s), (t / XS) & 1, abort_flag, p.status, kDevTimeoutStats)) break;
       const uint32_t xs = x_base + s * kTrXBytes;
 #pragma unroll 2
       for (int pass = 0; pass < 4; ++pass) {
@@ -293,80 +302,127 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(xn_ready(s), rank);
     }
-  } else {
-    // ------------------------------------------------------------ SwiGLU per block, then y = x + D2 per tile
-    // Thread = one position (TMEM lane) and half of the columns: 32 of a block's 64 hidden units, 64 of the 128
-    // output channels.
-    const int sw = warp - 12;          // 0 .. 7
-    const int q = warp & 3;            // TMEM lane quarter this warp may read
-    const int uh = sw >> 2;            // which half of the columns (the two warps of a quarter take one half each)
-    const int pos = q * 32 + lane;     // position inside this CTA's tile
-    const bool store_thread = sw == 0 && lane == 0;
+  } else if (warp < 20) {
+    // ------------------------------------------------------------ SwiGLU groups (4 warps each)
+    // Thread = one position (TMEM lane) and all 64 hidden units of the block, in four passes of 16.
+    const int grp = (warp - 12) >> 2;  // 0: even blocks, 1: odd blocks
+    const int q = warp & 3;            // TMEM lane quarter this warp may access
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t t_d1 = tmem_base + lane_off + grp * 128;
     for (int t = 0; t < my_tiles; ++t) {
-      const int s = t & 1;
-      const int tile = pair + t * num_pairs;
-      const long long grow = static_cast<long long>(tile) * 256 + static_cast<long long>(rank) * 128 + pos;
+      // h of this tile borrows the first 64 columns of the D2 buffer that is not accumulating: H[grp] = 32 of them
+      const int hbuf = (t + 1) & 1;
+      const uint32_t t_h = tmem_base + lane_off + kTrColD2 + hbuf * 128 + grp * 32;
       bool alive = true;
 #pragma unroll 1
-      for (int hb = 0; hb < kTrBlocks; ++hb) {
+      for (int hb = grp; hb < kTrBlocks; hb += 2) {
         const long long gb = static_cast<long long>(t) * kTrBlocks + hb;
-        const int bsel = static_cast<int>(gb & 1);
         const uint32_t bph = static_cast<uint32_t>((gb >> 1) & 1);
-        if (!mbar_wait_warp(d1_full(bsel), bph, abort_flag, p.status, kDevTimeoutEpilogue)) {
+        if (!mbar_wait_warp(d1_full(grp), bph, abort_flag, p.status, kDevTimeoutEpilogue)) {
           alive = false;
           break;
         }
         tc_fence_after();
-        uint32_t va[32], vb[32];
-        tmem_ld32(tmem_base + lane_off + bsel * 128 + uh * 32, va);
-        tmem_ld32(tmem_base + lane_off + bsel * 128 + 64 + uh * 32, vb);
-        tmem_ld_wait();
-        uint32_t o[16];
+        uint32_t o[32];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 a2 = make_float2(__uint_as_float(va[2 * i]), __uint_as_float(va[2 * i + 1]));
-          const float2 bb = make_float2(__uint_as_float(vb[2 * i]), __uint_as_float(vb[2 * i + 1]));
-          const float2 th = make_float2(tanh_approx(a2.x), tanh_approx(a2.y));  // (the packed fp16 form measured no faster)
-          o[i] = pack_f16x2_sat(__fmul2_rn(__ffma2_rn(th, a2, a2), bb));
+        for (int pq = 0; pq < 4; ++pq) {
+          uint32_t va[16], vb[16];
+          tmem_ld16(t_d1 + pq * 16, va);
+          tmem_ld16(t_d1 + 64 + pq * 16, vb);
+          tmem_ld_wait();
+          if (pq == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(d1_empty(grp), rank);  // D1[grp] may be overwritten by block gb + 2
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float2 a2 = make_float2(__uint_as_float(va[2 * i]), __uint_as_float(va[2 * i + 1]));
+            const float2 bb = make_float2(__uint_as_float(vb[2 * i]), __uint_as_float(vb[2 * i + 1]));
+            const float2 th = make_float2(tanh_approx(a2.x), tanh_approx(a2.y));  // (the packed fp16 form measured no faster)
+            o[pq * 8 + i] = pack_f16x2_sat(__fmul2_rn(__ffma2_rn(th, a2, a2), bb));
+          }
         }
-        // h goes where this thread's own a-values were: nobody else reads or writes these columns of these lanes
-        tmem_st16(tmem_base + lane_off + bsel * 128 + uh * 32, o);
+        // H[grp] is free once G2 of block gb - 2 (weight stage (gb - 2) % WS) is complete; the first h of a tile also
+        // waits until this CTA's output group has read tile t - 1 out of the D2 buffer that h borrows
+        if (gb >= 2) {
+          const long long pb = gb - 2;
+          if (!mbar_wait_warp(blk_done(static_cast<int>(pb % WS)), static_cast<uint32_t>((pb / WS) & 1), abort_flag, p.status,
+                              kDevTimeoutEpilogue)) {
+            alive = false;
+            break;
+          }
+        }
+        if (hb == grp && t >= 1) {
+          // tile t - 1 accumulated in D2[(t - 1) & 1] = D2[hbuf]; it is that buffer's use number (t - 1) / 2
+          if (!mbar_wait_warp(d2_read(hbuf), static_cast<uint32_t>(((t - 1) >> 1) & 1), abort_flag, p.status,
+                              kDevTimeoutEpilogue)) {
+            alive = false;
+            break;
+          }
+        }
+        tc_fence_after();
+        {
+          uint32_t lo[16], hi[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) lo[i] = o[i], hi[i] = o[16 + i];
+          tmem_st16(t_h, lo);
+          tmem_st16(t_h + 16, hi);
+        }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_leader(h_full(bsel), rank);
+        if (lane == 0) mbar_arrive_leader(h_full(grp), rank);
       }
-      if (!named_bar_and(1, 256, alive)) break;
-      // ---- y = x + D2 for this thread's position and 64 channels
-      uint4 xr[8];
-      {
-        const bool in_range = grow < p.positions;
-        const uint4* xp = reinterpret_cast<const uint4*>(p.x + (in_range ? grow : 0) * 128 + uh * 64);
+      if (!alive) break;
+    }
+  } else {
+    // ------------------------------------------------------------ output group: y = x + D2 per tile
+    // Thread = one position and all 128 channels, in four passes of 32.
+    const int q = warp & 3;
+    const int pos = q * 32 + lane;
+    const bool store_thread = warp == 20 && lane == 0;
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    for (int t = 0; t < my_tiles; ++t) {
+      const int s = t % XS;
+      const int tile = pair + t * num_pairs;
+      const long long grow = static_cast<long long>(tile) * 256 + static_cast<long long>(rank) * 128 + pos;
+      const bool in_range = grow < p.positions;
+      const uint4* xp = reinterpret_cast<const uint4*>(p.x + (in_range ? grow : 0) * 128);
+      uint4 xr[2][4];  // the residual, one pass ahead
 #pragma unroll
-        for (int c = 0; c < 8; ++c) xr[c] = (p.residual && in_range) ? __ldg(xp + c) : make_uint4(0u, 0u, 0u, 0u);
-      }
+      for (int c = 0; c < 4; ++c) xr[0][c] = (p.residual && in_range) ? __ldg(xp + c) : make_uint4(0u, 0u, 0u, 0u);
       {
         const bool got = mbar_wait_warp(d2_full(t & 1), (t >> 1) & 1, abort_flag, p.status, kDevTimeoutEpilogue);
-        if (!named_bar_and(1, 256, got)) break;
+        if (!named_bar_and(1, 128, got)) break;
       }
       tc_fence_after();
       const uint32_t xs = x_base + s * kTrXBytes;  // x_hat is dead (every G1 of the tile has completed): reuse for y
-      const uint32_t yrow = xs + uh * 16384 + pos * 128;
-      const uint32_t t_d2 = tmem_base + lane_off + 256 + (t & 1) * 128 + uh * 64;
+      const uint32_t t_d2 = tmem_base + lane_off + kTrColD2 + (t & 1) * 128;
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
+      for (int ps = 0; ps < 4; ++ps) {
+        if (ps < 3) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            xr[(ps + 1) & 1][c] = (p.residual && in_range) ? __ldg(xp + (ps + 1) * 4 + c) : make_uint4(0u, 0u, 0u, 0u);
+        }
         uint32_t v[32];
-        tmem_ld32(t_d2 + hf * 32, v);
+        tmem_ld32(t_d2 + ps * 32, v);
         tmem_ld_wait();
-        if (hf == 1) {
+        if (ps == 3) {
+          // D2[t & 1] has been read: h of tile t + 1 may borrow it (this CTA's SwiGLU groups), and the G2s of tile
+          // t + 2 may accumulate into it (the leader's issuer)
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_leader(d2_empty(t & 1), rank);
+          if (lane == 0) {
+            mbar_arrive(d2_read(t & 1));
+            mbar_arrive_leader(d2_empty(t & 1), rank);
+          }
         }
+        const uint32_t yrow = xs + (ps >> 1) * 16384 + pos * 128;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const uint4 xv = xr[hf * 4 + c];
+          const uint4 xv = xr[ps & 1][c];
           const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
           uint32_t o[4];
 #pragma unroll
@@ -374,13 +430,13 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             const float2 d = make_float2(__uint_as_float(v[8 * c + 2 * i]), __uint_as_float(v[8 * c + 2 * i + 1]));
             o[i] = pack_bf16x2(__fadd2_rn(d, bf16x2_to_float2(xw[i])));
           }
-          const uint32_t addr = yrow + (((hf * 4 + c) ^ (pos & 7)) << 4);
+          const uint32_t addr = yrow + ((((ps & 1) * 4 + c) ^ (pos & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
                        : "memory");
         }
       }
       fence_proxy_async_smem();
-      named_bar_sync(1, 256);
+      named_bar_sync(1, 128);
       if (store_thread) {
         const int row0 = tile * 256 + static_cast<int>(rank) * 128;
         if (row0 < p.positions) {  // rows past the end are clipped by the copy; a tile wholly past it is skipped

@@ -24,10 +24,11 @@
 // LayerNorm is done once per tile by dedicated warps, in place on the loaded tile (fp32 statistics, affine applied,
 // rounded to fp16 for the tensor cores); the residual re-reads x from global memory (L2) at the end of the tile.
 //
-// Warp roles (768 threads per CTA): warp 0 weight producer, warp 1 issuer of the G1 MMAs (leader CTA) / TMEM owner,
-// warp 2 input-tile producer, warp 3 issuer of the G2 MMAs (leader CTA), warps 4-11 LayerNorm (four of them took
-// 19 k cycles per tile next to the busy SwiGLU warps instead of 4 k alone), warps 12-15 and 16-19 the two SwiGLU
-// groups (one thread per position, 64 hidden units per block in four passes of 16), warps 20-23 the output group.
+// Warp roles (1024 threads per CTA, 64 registers each): warp 0 weight producer, warp 1 issuer of the G1 MMAs (leader
+// CTA) / TMEM owner, warp 2 input-tile producer, warp 3 issuer of the G2 MMAs (leader CTA), warps 4-11 LayerNorm (four
+// of them took 19 k cycles per tile next to the busy SwiGLU warps instead of 4 k alone), warps 12-19 and 20-27 the two
+// SwiGLU groups (two threads per position, 32 hidden units each per block in two passes of 16), warps 28-31 the output
+// group. Three input stages let LayerNorm of tile t + 2 run while tile t is still being written out.
 // G1 and G2 have an issuing thread each: issuing one 256 x 128 x 16 MMA costs about as long as it runs, so a single
 // thread that also waits for the SwiGLU warps between the two GEMMs leaves the tensor pipe idle half of the time.
 // Only mbarrier signals cross between the two CTAs. All waits are bounded.
@@ -48,7 +49,7 @@ struct TransitionParams {
   int* status;
 };
 
-constexpr int kTrThreads = 768;
+constexpr int kTrThreads = 1024;
 constexpr int kTrBlocks = 8;            // hidden blocks of 64 units
 constexpr int kTrWStages = 5;
 constexpr int kTrXStages = 3;           // input tiles in flight: LayerNorm of tile t + 2 runs while tile t is still being written out
@@ -101,8 +102,8 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(d1_full(s), 1);
-      mbar_init(d1_empty(s), 8);
-      mbar_init(h_full(s), 8);
+      mbar_init(d1_empty(s), 16);
+      mbar_init(h_full(s), 16);
       mbar_init(d2_full(s), 1);
       mbar_init(d2_empty(s), 8);
       mbar_init(d2_read(s), 4);
@@ -302,17 +303,18 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(xn_ready(s), rank);
     }
-  } else if (warp < 20) {
-    // ------------------------------------------------------------ SwiGLU groups (4 warps each)
-    // Thread = one position (TMEM lane) and all 64 hidden units of the block, in four passes of 16.
-    const int grp = (warp - 12) >> 2;  // 0: even blocks, 1: odd blocks
+  } else if (warp < 28) {
+    // ------------------------------------------------------------ SwiGLU groups (8 warps each)
+    // Thread = one position (TMEM lane) and half of the block's 64 hidden units, in two passes of 16.
+    const int grp = (warp - 12) >> 3;  // 0: even blocks, 1: odd blocks
+    const int uh = ((warp - 12) >> 2) & 1;  // which 32 units
     const int q = warp & 3;            // TMEM lane quarter this warp may access
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
-    const uint32_t t_d1 = tmem_base + lane_off + grp * 128;
+    const uint32_t t_d1 = tmem_base + lane_off + grp * 128 + uh * 32;
     for (int t = 0; t < my_tiles; ++t) {
       // h of this tile borrows the first 64 columns of the D2 buffer that is not accumulating: H[grp] = 32 of them
       const int hbuf = (t + 1) & 1;
-      const uint32_t t_h = tmem_base + lane_off + kTrColD2 + hbuf * 128 + grp * 32;
+      const uint32_t t_h = tmem_base + lane_off + kTrColD2 + hbuf * 128 + grp * 32 + uh * 16;
       bool alive = true;
 #pragma unroll 1
       for (int hb = grp; hb < kTrBlocks; hb += 2) {
@@ -323,14 +325,14 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           break;
         }
         tc_fence_after();
-        uint32_t o[32];
+        uint32_t o[16];
 #pragma unroll
-        for (int pq = 0; pq < 4; ++pq) {
+        for (int pq = 0; pq < 2; ++pq) {
           uint32_t va[16], vb[16];
           tmem_ld16(t_d1 + pq * 16, va);
           tmem_ld16(t_d1 + 64 + pq * 16, vb);
           tmem_ld_wait();
-          if (pq == 3) {
+          if (pq == 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(d1_empty(grp), rank);  // D1[grp] may be overwritten by block gb + 2
@@ -362,13 +364,7 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           }
         }
         tc_fence_after();
-        {
-          uint32_t lo[16], hi[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) lo[i] = o[i], hi[i] = o[16 + i];
-          tmem_st16(t_h, lo);
-          tmem_st16(t_h + 16, hi);
-        }
+        tmem_st16(t_h, o);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -378,10 +374,10 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ output group: y = x + D2 per tile
-    // Thread = one position and all 128 channels, in four passes of 32.
+    // Thread = one position and all 128 channels, in eight passes of 16 (the residual is fetched one pass ahead).
     const int q = warp & 3;
     const int pos = q * 32 + lane;
-    const bool store_thread = warp == 20 && lane == 0;
+    const bool store_thread = warp == 28 && lane == 0;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     for (int t = 0; t < my_tiles; ++t) {
       const int s = t % XS;
@@ -389,9 +385,9 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const long long grow = static_cast<long long>(tile) * 256 + static_cast<long long>(rank) * 128 + pos;
       const bool in_range = grow < p.positions;
       const uint4* xp = reinterpret_cast<const uint4*>(p.x + (in_range ? grow : 0) * 128);
-      uint4 xr[2][4];  // the residual, one pass ahead
+      uint4 xr[2][2];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) xr[0][c] = (p.residual && in_range) ? __ldg(xp + c) : make_uint4(0u, 0u, 0u, 0u);
+      for (int c = 0; c < 2; ++c) xr[0][c] = (p.residual && in_range) ? __ldg(xp + c) : make_uint4(0u, 0u, 0u, 0u);
       {
         const bool got = mbar_wait_warp(d2_full(t & 1), (t >> 1) & 1, abort_flag, p.status, kDevTimeoutEpilogue);
         if (!named_bar_and(1, 128, got)) break;
@@ -400,16 +396,16 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const uint32_t xs = x_base + s * kTrXBytes;  // x_hat is dead (every G1 of the tile has completed): reuse for y
       const uint32_t t_d2 = tmem_base + lane_off + kTrColD2 + (t & 1) * 128;
 #pragma unroll
-      for (int ps = 0; ps < 4; ++ps) {
-        if (ps < 3) {
+      for (int ps = 0; ps < 8; ++ps) {
+        if (ps < 7) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            xr[(ps + 1) & 1][c] = (p.residual && in_range) ? __ldg(xp + (ps + 1) * 4 + c) : make_uint4(0u, 0u, 0u, 0u);
+          for (int c = 0; c < 2; ++c)
+            xr[(ps + 1) & 1][c] = (p.residual && in_range) ? __ldg(xp + (ps + 1) * 2 + c) : make_uint4(0u, 0u, 0u, 0u);
         }
-        uint32_t v[32];
-        tmem_ld32(t_d2 + ps * 32, v);
+        uint32_t v[16];
+        tmem_ld16(t_d2 + ps * 16, v);
         tmem_ld_wait();
-        if (ps == 3) {
+        if (ps == 7) {
           // D2[t & 1] has been read: h of tile t + 1 may borrow it (this CTA's SwiGLU groups), and the G2s of tile
           // t + 2 may accumulate into it (the leader's issuer)
           tc_fence_before();
@@ -419,9 +415,9 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             mbar_arrive_leader(d2_empty(t & 1), rank);
           }
         }
-        const uint32_t yrow = xs + (ps >> 1) * 16384 + pos * 128;
+        const uint32_t yrow = xs + (ps >> 2) * 16384 + pos * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           const uint4 xv = xr[ps & 1][c];
           const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
           uint32_t o[4];
@@ -430,7 +426,7 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             const float2 d = make_float2(__uint_as_float(v[8 * c + 2 * i]), __uint_as_float(v[8 * c + 2 * i + 1]));
             o[i] = pack_bf16x2(__fadd2_rn(d, bf16x2_to_float2(xw[i])));
           }
-          const uint32_t addr = yrow + ((((ps & 1) * 4 + c) ^ (pos & 7)) << 4);
+          const uint32_t addr = yrow + ((((ps & 3) * 2 + c) ^ (pos & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
                        : "memory");
         }

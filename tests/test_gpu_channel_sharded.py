@@ -16,7 +16,7 @@ DEV = torch.device("cuda", 0) if torch.cuda.is_available() else None
 
 
 @pytest.mark.parametrize("outgoing", [True, False])
-@pytest.mark.parametrize("N,P", [(256, 2), (256, 4), (768, 8), (512, 4), (1024, 2)])
+@pytest.mark.parametrize("N,P", [(256, 2), (256, 4), (768, 8), (512, 4), (1024, 2), (2048, 8)])
 def test_channel_sharded_emulation_equals_single_gpu(N, P, outgoing):
     p = rand_params(71)
     g = torch.Generator().manual_seed(72 + N)

@@ -11,7 +11,11 @@
  * Conventions
  *  - All pointers are device pointers unless the name says `host`. Activations are bf16, LayerNorm
  *    affine vectors fp32, linear weights bf16 or fp32 (`weight_dtype`), masks uint8 (non-zero = valid).
- *  - d_pair = d_hidden = 128 is the only supported width (B200_TRIMUL_E_UNSUPPORTED otherwise).
+ *  - Widths: d_pair = d_hidden = 128 (every direction), and through b200_trimul_forward / _forward_ex / _forward_static
+ *    also d_pair = 64 with 128 contracted channels in total: d_hidden = 128 for one direction (the template blocks,
+ *    benchmarks/protenix_finetune/patch_engine.py:283-295) or d_hidden = 64 per direction for the bidirectional
+ *    module. Anything else is B200_TRIMUL_E_UNSUPPORTED. The staged entry points (pack, prologue, epilogue) are
+ *    128-wide.
  *    N must be a multiple of 8 (16-byte rows for the bulk copies); callers pad with masked tokens.
  *  - The caller owns every buffer, including the workspace; the library never allocates or frees
  *    device memory. Its only process-wide state is a set of caches that are filled on first use and
@@ -53,7 +57,7 @@ extern "C" {
 #define B200_TRIMUL_OK 0
 #define B200_TRIMUL_E_NULL (-1)        /* a required pointer is null */
 #define B200_TRIMUL_E_SHAPE (-2)       /* bad B / N / rows / direction */
-#define B200_TRIMUL_E_UNSUPPORTED (-3) /* d_pair or d_hidden other than 128, N not a multiple of 8 */
+#define B200_TRIMUL_E_UNSUPPORTED (-3) /* a width outside the list above, N not a multiple of 8 */
 #define B200_TRIMUL_E_ALIGN (-4)       /* a pointer is not 16-byte aligned (workspace: 1024) */
 #define B200_TRIMUL_E_WORKSPACE (-5)   /* workspace too small */
 #define B200_TRIMUL_E_CUDA (-6)        /* a CUDA runtime / driver call failed; see b200_trimul_last_cuda_error */
@@ -212,7 +216,12 @@ int b200_trimul_forward(const void* z, const void* w_left, const void* w_left_ga
  *    direction 0.
  *  - drop_scale: null, or [B, N, 128] bf16 - the row-shared dropout scale [B, 1, N, C] of the training path
  *    (keep-mask / (1 - p), scripts/check_trimul_module_reference.py:43 in the reference project): y = z + scale * update.
- *    A zero scale returns z exactly. This is `flat_scale` of the engine's entry point.
+ *    A zero scale returns z exactly. This is `flat_scale` of the engine's entry point. 128-wide pairs only.
+ *  - d_pair = 64: z, y are [B, N, N, 64]; w_left, w_left_gate, w_right, w_right_gate are [128, 64], ln_in 64 entries,
+ *    ln_out 128 entries, w_out [64, 128], w_gate [64, 64]; bias_opt entries 0-3 fp32[128], 4-5 fp32[64]. With one
+ *    direction (d_hidden = 128) all 128 channels are contracted that way; with direction 0 (d_hidden = 64) channels
+ *    0-63 are contracted outgoing and 64-127 incoming, as in the reference's 64-wide validation case
+ *    (docs/archive/engine2-validation-20260923/validate_bidir_reference.py:11). drop_scale must be null.
  */
 int b200_trimul_forward_ex(const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
                            const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,

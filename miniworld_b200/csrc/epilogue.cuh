@@ -44,10 +44,19 @@ constexpr int kEpiConstBytes = 2048;          // per channel pair: {sg0,sg1,dg0,
 constexpr int kEpiXchgBytes = 6144;           // per group: 2 x 128 input partials + 4 x 128 output partials (float2)
 constexpr int kEpiSmemBytes = kEpiWBytes + 2 * kEpiStageBytes + kEpiConstBytes + 2 * kEpiXchgBytes + 128 + 1024;
 
+// C = d_pair: the channels of z / y and the rows of both weight matrices (128, or 64 for the narrow pair stacks). The
+// contracted width (channels of t, columns of Wo') is 128 in both cases. The shared-memory layout is that of C = 128;
+// with C = 64 the z tile, the weights and the per-channel constants fill the first half of their regions.
+template <int C = 128>
 __global__ void __launch_bounds__(kEpilogueThreads, 1)
 epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_z,
-                const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_w,
-                const EpilogueParams p) {
+                const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_wo,
+                const __grid_constant__ CUtensorMap map_wg, const EpilogueParams p) {
+  static_assert(C == 128 || C == 64, "d_pair is 128 or 64");
+  constexpr int kZHalves = C / 64;        // 64-channel (128-byte) halves of a z row
+  constexpr int kWoHalf = C * 128;        // bytes of one 64-wide k half of a [C, *] weight matrix
+  constexpr int CH = C / 2;               // output channels per epilogue thread
+  constexpr int NCH = CH / 8;             // 16-byte chunks (8 channels) per epilogue thread
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -90,9 +99,10 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
     prefetch_tmap(&map_t);
     prefetch_tmap(&map_z);
     prefetch_tmap(&map_y);
-    prefetch_tmap(&map_w);
+    prefetch_tmap(&map_wo);
+    prefetch_tmap(&map_wg);
   }
-  if (threadIdx.x >= 64 && threadIdx.x < 128) {
+  if (threadIdx.x >= 64 && threadIdx.x < 64 + C / 2) {
     // constants regrouped per channel pair so that one 16-byte load feeds a packed fp32x2 FMA
     const int cp = threadIdx.x - 64;
     const float4 a = p.c3[2 * cp];
@@ -112,12 +122,12 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(w_full, kEpiWBytes);
+      // Wo' [C, 128] as two k halves, Wg' [C, C] as C / 64 k halves
+      mbar_arrive_expect_tx(w_full, 2 * kWoHalf + kZHalves * kWoHalf);
 #pragma unroll
-      for (int m = 0; m < 2; ++m)
+      for (int kh = 0; kh < 2; ++kh) tma_load_2d(wo_base + kh * kWoHalf, &map_wo, w_full, kh * 64, 0);
 #pragma unroll
-        for (int kh = 0; kh < 2; ++kh)
-          tma_load_2d(wo_base + m * 32768 + kh * 16384, &map_w, w_full, kh * 64, (4 + m) * 128);
+      for (int kh = 0; kh < kZHalves; ++kh) tma_load_2d(wg_base + kh * kWoHalf, &map_wg, w_full, kh * 64, 0);
       int it = 0, t_issued = 0, z_issued = 0;
       for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
         const int s = it & 1;
@@ -134,9 +144,9 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
         tma_load_4d(ts + 16384, &map_t, t_full(s), j0 + 64, 0, 0, row);
         ++t_issued;
         if (!mbar_wait(z_empty(s), ph ^ 1u, abort_flag, p.status, kDevTimeoutProducer)) break;
-        mbar_arrive_expect_tx(z_full(s), 32768);
-        tma_load_3d(zs, &map_z, z_full(s), 0, j0, row);
-        tma_load_3d(zs + 16384, &map_z, z_full(s), 64, j0, row);
+        mbar_arrive_expect_tx(z_full(s), kZHalves * 16384);
+#pragma unroll
+        for (int kh = 0; kh < kZHalves; ++kh) tma_load_3d(zs + kh * 16384, &map_z, z_full(s), kh * 64, j0, row);
         ++z_issued;
       }
       // Drain every copy this thread started before the CTA may exit.
@@ -167,8 +177,8 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_p = umma_idesc(128, 128, true, false, kFmtF16, kFmtF16);
-      constexpr uint32_t idesc_g = umma_idesc(128, 128, false, false);
+      constexpr uint32_t idesc_p = umma_idesc(128, C, true, false, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_g = umma_idesc(128, C, false, false);
       bool ok = mbar_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma);
       int it = 0;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
@@ -184,15 +194,15 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t da = umma_desc_mnmajor(ts + ks * 2048, 16384);
-          const uint64_t db = umma_desc_kmajor(wo_base + (ks >> 2) * 16384) + static_cast<uint64_t>((ks & 3) * 2);
+          const uint64_t db = umma_desc_kmajor(wo_base + (ks >> 2) * kWoHalf) + static_cast<uint64_t>((ks & 3) * 2);
           umma_bf16(d_p, da, db, idesc_p, ks != 0 ? 1u : 0u);
         }
         if (!mbar_wait(z_full(s), ph, abort_flag, p.status, kDevTimeoutMma)) break;
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+        for (int ks = 0; ks < C / 16; ++ks) {
           const uint64_t da = umma_desc_kmajor(zs + (ks >> 2) * 16384) + static_cast<uint64_t>((ks & 3) * 2);
-          const uint64_t db = umma_desc_kmajor(wg_base + (ks >> 2) * 16384) + static_cast<uint64_t>((ks & 3) * 2);
+          const uint64_t db = umma_desc_kmajor(wg_base + (ks >> 2) * kWoHalf) + static_cast<uint64_t>((ks & 3) * 2);
           umma_bf16(d_g, da, db, idesc_g, ks != 0 ? 1u : 0u);
         }
         umma_commit(acc_full(s));
@@ -203,7 +213,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
     const int grp = (warp - 2) >> 3;         // 0: even tiles, 1: odd tiles
     const int wg = (warp - 2) & 7;           // warp inside the group
     const int tg = wg * 32 + lane;           // thread inside the group
-    const int half = wg >> 2;                // which 64 output channels this thread finishes
+    const int half = wg >> 2;                // which C / 2 output channels this thread finishes
     const int q = warp & 3;                  // TMEM lane quarter this warp may read
     const int pos = q * 32 + lane;           // position inside the tile == TMEM lane
     const int bar_id = 2 + grp;
@@ -212,7 +222,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
     const uint32_t zs = ts + 32768;
     const uint32_t xin = xchg_base + grp * kEpiXchgBytes;   // float2 [2][128]: {mean, M2} over 64 channels of z
     const uint32_t xout = xin + 2048;                        // float2 [4][128]: {mean, M2} over 32 channels of t
-    const uint32_t t_p = tmem_base + grp * 256 + half * 64 + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t t_p = tmem_base + grp * 256 + half * CH + (static_cast<uint32_t>(q * 32) << 16);
     const uint32_t t_g = t_p + 128;
     // output statistics: this thread covers positions 2*pp, 2*pp+1 over channels 32*hq .. 32*hq+31
     const int pp = tg & 63;
@@ -254,21 +264,24 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
         const bool got = mbar_wait_warp(z_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
         if (!named_bar_and(bar_id, 256, got)) break;
       }
-      // ---- input partial statistics over this thread's 64 channels of its z row (kept for the residual)
-      const uint32_t zrow = zs + half * 16384 + pos * 128;
-      uint4 zr[8];
+      // ---- input partial statistics over this thread's C / 2 channels of its z row (kept for the residual)
+      // C = 128: the thread's channels are one 64-channel half of the tile; C = 64: four of the eight 16-byte chunks of
+      // the tile's only half
+      const uint32_t zrow = zs + (C == 128 ? half * 16384 : 0) + pos * 128;
+      constexpr int kChunk0 = C == 128 ? 0 : 1;  // chunk index of this thread's first chunk = half * 4 * kChunk0
+      uint4 zr[NCH];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < NCH; ++c) {
         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(zr[c].x), "=r"(zr[c].y), "=r"(zr[c].z), "=r"(zr[c].w)
-                     : "r"(zrow + ((c ^ (pos & 7)) << 4)));
+                     : "r"(zrow + (((half * 4 * kChunk0 + c) ^ (pos & 7)) << 4)));
       }
       {
         const float pv = bf16_lo(zr[0].x);
         const float2 npv = make_float2(-pv, -pv);
         float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < NCH; ++c) {
           const uint32_t w4[4] = {zr[c].x, zr[c].y, zr[c].z, zr[c].w};
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
@@ -278,8 +291,8 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
           }
         }
         const float a1 = s1.x + s1.y, a2 = s2.x + s2.y;
-        const float mean = pv + a1 * (1.0f / 64.0f);
-        const float m2 = fmaxf(a2 - a1 * a1 * (1.0f / 64.0f), 0.f);
+        const float mean = pv + a1 * (1.0f / CH);
+        const float m2 = fmaxf(a2 - a1 * a1 * (1.0f / CH), 0.f);
         asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xin + (half * 128 + pos) * 8), "f"(mean), "f"(m2) : "memory");
       }
       named_bar_sync(bar_id, 256);
@@ -291,8 +304,8 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
         asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(mb), "=f"(qb) : "r"(xin + (128 + pos) * 8));
         const float mean = 0.5f * (ma + mb);
         const float dlt = ma - mb;
-        const float m2 = qa + qb + dlt * dlt * 32.0f;  // n_a n_b / (n_a + n_b) = 32
-        rs_in = rsqrtf(m2 * (1.0f / 128.0f) + p.eps_in);
+        const float m2 = qa + qb + dlt * dlt * (0.25f * C);  // n_a n_b / (n_a + n_b) = C / 4
+        rs_in = rsqrtf(m2 * (1.0f / C) + p.eps_in);
         nmr_in = -mean * rs_in;
       }
       {
@@ -317,14 +330,14 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       tc_fence_after();
       // every thread is past its output statistics (barrier above) and the P MMAs are complete: t is dead
       if (store_thread) mbar_arrive(t_empty(grp));
-      // 8 chunks of 8 channels; the TMEM loads of chunk cc+1 are in flight while chunk cc is finished
+      // C / 16 chunks of 8 channels; the TMEM loads of chunk cc+1 are in flight while chunk cc is finished
       uint32_t vp[2][8], vg[2][8];
       tmem_ld8(t_p, vp[0]);
       tmem_ld8(t_g, vg[0]);
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {  // fully unrolled so that zr[] and the two register sets stay in registers
+      for (int cc = 0; cc < NCH; ++cc) {  // fully unrolled so that zr[] and the two register sets stay in registers
         tmem_ld_wait();
-        if (cc < 7) {
+        if (cc < NCH - 1) {
           tmem_ld8(t_p + (cc + 1) * 8, vp[(cc + 1) & 1]);
           tmem_ld8(t_g + (cc + 1) * 8, vg[(cc + 1) & 1]);
         } else {
@@ -336,7 +349,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
         const uint32_t zz[4] = {zr[cc].x, zr[cc].y, zr[cc].z, zr[cc].w};
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          const int pair = half * 32 + cc * 4 + t;  // channel pair index 0..63
+          const int pair = half * (CH / 2) + cc * 4 + t;  // channel pair index 0 .. C / 2 - 1
           float4 cg, co;
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                        : "=f"(cg.x), "=f"(cg.y), "=f"(cg.z), "=f"(cg.w)
@@ -353,15 +366,15 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
           if (p.residual) u = __fadd2_rn(u, bf16x2_to_float2(zz[t]));
           o[t] = pack_bf16x2(u);
         }
-        const uint32_t addr = zrow + ((cc ^ (pos & 7)) << 4);
+        const uint32_t addr = zrow + (((half * 4 * kChunk0 + cc) ^ (pos & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
                      : "memory");
       }
       fence_proxy_async_smem();
       named_bar_sync(bar_id, 256);
       if (store_thread) {
-        tma_store_3d(&map_y, zs, 0, j0, row);
-        tma_store_3d(&map_y, zs + 16384, 64, j0, row);
+#pragma unroll
+        for (int kh = 0; kh < kZHalves; ++kh) tma_store_3d(&map_y, zs + kh * 16384, kh * 64, j0, row);
         bulk_commit();
         bulk_wait_read<0>();
         mbar_arrive(z_empty(grp));

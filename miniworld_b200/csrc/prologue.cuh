@@ -81,18 +81,22 @@ constexpr int kProThreads = 864;
 constexpr int kProStages = 5;
 constexpr int kProRing = 8;              // mask ring entries (>= stages + 3)
 constexpr int kProRingBytes = 272;       // 64 pair-mask words + 4 ballots
-constexpr int kProWBytes = 2 * 32768;    // this CTA's proj and gate matrices
-constexpr int kProZBytes = 16384;        // 64 positions x 128 channels, 16-bit
 constexpr int kProStageOutBytes = 2 * 32768;  // two staging buffers of [128 channels][128 positions]
 constexpr int kProBarBytes = 256;
+// C = d_pair, the channels of the input tensor (128, or 64 for the narrow pair stacks); the outputs always have 128
+// channels. The shared-memory budget is that of C = 128 for both.
 constexpr int kProSmemBytes =
-    kProWBytes + kProStages * kProZBytes + kProStageOutBytes + kProRing * kProRingBytes + kProBarBytes + 1024;
+    2 * 32768 + kProStages * 16384 + kProStageOutBytes + kProRing * kProRingBytes + kProBarBytes + 1024;
 
-template <bool HAS_BIAS>
+template <bool HAS_BIAS, int C = 128>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kProThreads, 1)
 prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_w,
                 const __grid_constant__ OutputMaps out, const PrologueParams p) {
+  static_assert(C == 128 || C == 64, "d_pair is 128 or 64");
   constexpr int S = kProStages;
+  constexpr int kHalves = C / 64;              // 64-channel (128-byte) halves of an input row
+  constexpr int kProWBytes = 2 * 128 * C * 2;  // this CTA's proj and gate matrices, [128, C] fp16 each
+  constexpr int kProZBytes = 64 * C * 2;       // 64 positions x C channels, 16-bit
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -157,8 +161,9 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
 #pragma unroll
       for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int kh = 0; kh < 2; ++kh)
-          tma_load_2d_pair(w_base + m * 32768 + kh * 16384, &map_w, lead_w, kh * 64, (static_cast<int>(rank) * 2 + m) * 128);
+        for (int kh = 0; kh < kHalves; ++kh)
+          tma_load_2d_pair(w_base + m * (kProWBytes / 2) + kh * 16384, &map_w, lead_w, kh * 64,
+                           (static_cast<int>(rank) * 2 + m) * 128);
       int s = 0;
       uint32_t ph = 0;
       int issued = 0;
@@ -167,8 +172,8 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
         const int row = tile / p.tiles_per_row;
         const int j0 = (tile - row * p.tiles_per_row) * 128 + static_cast<int>(rank) * 64;  // this CTA's 64 positions
         mbar_arrive_expect_tx(z_full(s), kProZBytes);
-        tma_load_3d(z_base + s * kProZBytes, &map_z, z_full(s), 0, j0, row);
-        tma_load_3d(z_base + s * kProZBytes + 8192, &map_z, z_full(s), 64, j0, row);
+#pragma unroll
+        for (int kh = 0; kh < kHalves; ++kh) tma_load_3d(z_base + s * kProZBytes + kh * 8192, &map_z, z_full(s), kh * 64, j0, row);
         ++issued;
         if (++s == S) {
           s = 0;
@@ -219,9 +224,9 @@ prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
           const uint32_t d_tmem = tmem_base + buf * 256 + m * 128;
-          const uint32_t wm = w_base + m * 32768;
+          const uint32_t wm = w_base + m * (kProWBytes / 2);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
+          for (int ks = 0; ks < C / 16; ++ks) {
             const uint64_t da = umma_desc_kmajor(wm + (ks >> 2) * 16384) + static_cast<uint64_t>((ks & 3) * 2);
             const uint64_t db = umma_desc_kmajor(zs + (ks >> 2) * 8192) + static_cast<uint64_t>((ks & 3) * 2);
             umma_pair(d_tmem, da, db, idesc, ks != 0 ? 1u : 0u);

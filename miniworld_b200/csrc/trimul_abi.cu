@@ -35,11 +35,12 @@ static thread_local int tl_last_cuda_error = 0;
   } while (0)
 
 // ---------------------------------------------------------------------------------------------
-// Weight packing: one warp per matrix row.
-//   matrices 0..3 (left, left gate, right, right gate): W' = fp16(0.5 W), d = 0.5 bias
+// Weight packing: one warp per matrix row. C = d_pair (128 or 64); the contracted width is 128 in both cases.
+//   matrices 0..3 (left, left gate, right, right gate) [128, C]: W' = fp16(0.5 W), d = 0.5 bias
 //     (the prologue applies the input LayerNorm affine itself; gamma_in / beta_in are copied alongside)
-//   matrix 4 (out):  W' = fp16(0.5 W gamma_out), s = rowsum(W'), d = 0.5 (W beta_out + bias)
-//   matrix 5 (gate): W' = bf16(0.5 W gamma_in),  s = rowsum(W'), d = 0.5 (W beta_in + bias)
+//   matrix 4 (out)  [C, 128]: W' = fp16(0.5 W gamma_out), s = rowsum(W'), d = 0.5 (W beta_out + bias)
+//   matrix 5 (gate) [C, C]:   W' = bf16(0.5 W gamma_in),  s = rowsum(W'), d = 0.5 (W beta_in + bias)
+// Packed matrices are dense and follow one another: 0..3 at m * 128 * C * 2 bytes, 4 after them, 5 after 4.
 struct PackArgs {
   const void* w[6];
   int ld[6];  // elements between consecutive rows of w[m] (128 for a matrix of its own, more for a column slice)
@@ -49,25 +50,35 @@ struct PackArgs {
   const float* ln_out_w;
   const float* ln_out_b;
   int f32_weights;
+  int c;  // d_pair
 };
+
+__host__ __device__ inline size_t packed_matrix_offset(int m, int c) {
+  return m <= 4 ? static_cast<size_t>(m) * 128 * c * 2 : static_cast<size_t>(4) * 128 * c * 2 + static_cast<size_t>(c) * 128 * 2;
+}
 
 __global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* packed) {
   const int gw = blockIdx.x * 4 + (threadIdx.x >> 5);  // 0 .. 767
   const int lane = threadIdx.x & 31;
   const int m = gw >> 7;
   const int row = gw & 127;
+  const int n_rows = m < 4 ? 128 : a.c;
+  const int k = m == 4 ? 128 : a.c;  // row length
+  if (row >= n_rows) return;
+  const bool active = lane * 4 < k;
   const float* gamma = (m == 4) ? a.ln_out_w : a.ln_in_w;
   const float* beta = (m == 4) ? a.ln_out_b : a.ln_in_b;
-  float w[4];
-  if (a.f32_weights) {
+  float w[4] = {0.f, 0.f, 0.f, 0.f};
+  if (!active) {
+  } else if (a.f32_weights) {
     const float4 v = reinterpret_cast<const float4*>(static_cast<const float*>(a.w[m]) + static_cast<size_t>(row) * a.ld[m])[lane];
     w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
   } else {
     const uint2 v = reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(a.w[m]) + static_cast<size_t>(row) * a.ld[m])[lane];
     w[0] = bf16_lo(v.x), w[1] = bf16_hi(v.x), w[2] = bf16_lo(v.y), w[3] = bf16_hi(v.y);
   }
-  const float4 g = reinterpret_cast<const float4*>(gamma)[lane];
-  const float4 b = reinterpret_cast<const float4*>(beta)[lane];
+  const float4 g = active ? reinterpret_cast<const float4*>(gamma)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 b = active ? reinterpret_cast<const float4*>(beta)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
   const float gg[4] = {g.x, g.y, g.z, g.w};
   const float bb[4] = {b.x, b.y, b.z, b.w};
   float s = 0.f, d = 0.f;
@@ -90,14 +101,16 @@ __global__ void __launch_bounds__(128) pack_kernel(const PackArgs a, uint8_t* pa
     }
     if (fold) d = fmaf(w[t], bb[t], d);
   }
-  if (gw == 0) {
+  if (gw == 0 && active) {
     reinterpret_cast<float4*>(packed + kPackedLnOff)[lane] = g;
     reinterpret_cast<float4*>(packed + kPackedLnOff + 512)[lane] = b;
   }
-  uint2 ov;
-  ov.x = static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 16);
-  ov.y = static_cast<uint32_t>(o[2]) | (static_cast<uint32_t>(o[3]) << 16);
-  reinterpret_cast<uint2*>(packed + static_cast<size_t>(m) * 32768)[row * 32 + lane] = ov;
+  if (active) {
+    uint2 ov;
+    ov.x = static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 16);
+    ov.y = static_cast<uint32_t>(o[2]) | (static_cast<uint32_t>(o[3]) << 16);
+    reinterpret_cast<uint2*>(packed + packed_matrix_offset(m, a.c))[row * (k / 4) + lane] = ov;
+  }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
     s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
@@ -369,7 +382,7 @@ const char* b200_trimul_strerror(int code) {
     case B200_TRIMUL_OK: return "ok";
     case B200_TRIMUL_E_NULL: return "a required pointer is null";
     case B200_TRIMUL_E_SHAPE: return "bad shape, row range or direction";
-    case B200_TRIMUL_E_UNSUPPORTED: return "unsupported size: d_pair = d_hidden = 128 and N a multiple of 8 are required";
+    case B200_TRIMUL_E_UNSUPPORTED: return "unsupported size: N a multiple of 8 and d_pair = d_hidden = 128 (or d_pair = 64 with 128 contracted channels in total) are required";
     case B200_TRIMUL_E_ALIGN: return "pointer not aligned (16 bytes; workspace and packed weights 1024)";
     case B200_TRIMUL_E_WORKSPACE: return "workspace too small";
     case B200_TRIMUL_E_CUDA: return "CUDA call failed (see b200_trimul_last_cuda_error)";
@@ -405,15 +418,19 @@ int b200_trimul_workspace_layout(int B, int N, size_t out_offsets[5]) {
 
 int b200_trimul_workspace_bytes(int B, int N, int d_pair, int d_hidden, int direction, size_t* out_bytes) {
   if (out_bytes == nullptr) return B200_TRIMUL_E_NULL;
-  if (d_pair != kC || d_hidden != kC) return B200_TRIMUL_E_UNSUPPORTED;
   if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING && direction != B200_TRIMUL_BIDIRECTIONAL)
     return B200_TRIMUL_E_SHAPE;
+  // supported widths: d_pair = d_hidden = 128 (every direction); d_pair = 64 with 128 contracted channels in total,
+  // i.e. d_hidden = 128 for one direction or d_hidden = 64 per direction for the bidirectional module
+  const bool wide = d_pair == kC && d_hidden == kC;
+  const bool narrow = d_pair == 64 && d_hidden == (direction == B200_TRIMUL_BIDIRECTIONAL ? 64 : kC);
+  if (!wide && !narrow) return B200_TRIMUL_E_UNSUPPORTED;
   size_t off[5];
   int rc = b200_trimul_workspace_layout(B, N, off);
   if (rc != B200_TRIMUL_OK) return rc;
   *out_bytes = off[4] + plane_tensor_bytes(B, N, N);
   // bidirectional: a second packed block and a second tri tensor (left / right are reused by the two halves)
-  if (direction == B200_TRIMUL_BIDIRECTIONAL) *out_bytes += kPackedBytes + plane_tensor_bytes(B, N, N);
+  if (direction == B200_TRIMUL_BIDIRECTIONAL && wide) *out_bytes += kPackedBytes + plane_tensor_bytes(B, N, N);
   return B200_TRIMUL_OK;
 }
 
@@ -434,7 +451,7 @@ int b200_trimul_read_status(const int* status, void* cuda_stream, int* host_stat
 // Launch the pack kernel. w / bias in MATRIX order: left, left gate, right, right gate, out, gate.
 static int pack_impl(const void* const w[6], const int ld[6], int weight_dtype, const float* ln_in_w, const float* ln_in_b,
                      const float* ln_out_w, const float* ln_out_b, const float* const bias[6], void* packed,
-                     void* cuda_stream) {
+                     void* cuda_stream, int c = kC) {
   if (!ln_in_w || !ln_in_b || !ln_out_w || !ln_out_b || !packed) return B200_TRIMUL_E_NULL;
   if (weight_dtype != B200_TRIMUL_DTYPE_BF16 && weight_dtype != B200_TRIMUL_DTYPE_F32) return B200_TRIMUL_E_SHAPE;
   PackArgs a;
@@ -453,6 +470,7 @@ static int pack_impl(const void* const w[6], const int ld[6], int weight_dtype, 
   a.ln_out_w = ln_out_w;
   a.ln_out_b = ln_out_b;
   a.f32_weights = weight_dtype == B200_TRIMUL_DTYPE_F32;
+  a.c = c;
   pack_kernel<<<192, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(a, static_cast<uint8_t*>(packed));
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
@@ -514,7 +532,8 @@ enum PrologueMode { kLocal, kGatherRight, kChannels };
 static int prologue_impl(const void* z, const void* packed, const uint8_t* token_mask, const uint8_t* pair_mask,
                          void* const* left_dst, int n_left, void* const* right_dst, int n_right, PrologueMode mode,
                          int B, int N, int row_begin, int rows, float eps_in, int has_bias, int* status,
-                         void* cuda_stream) {
+                         void* cuda_stream, int d_pair = kC) {
+  if (d_pair != kC && d_pair != 64) return B200_TRIMUL_E_UNSUPPORTED;
   if (!z || !packed || !left_dst || !right_dst || !status) return B200_TRIMUL_E_NULL;
   if (n_left < 1 || n_left > kMaxDst || n_right < 1 || n_right > kMaxDst) return B200_TRIMUL_E_SHAPE;
   if (mode != kLocal && B != 1) return B200_TRIMUL_E_SHAPE;
@@ -530,8 +549,9 @@ static int prologue_impl(const void* z, const void* packed, const uint8_t* token
   CUtensorMap map_z, map_w;
   OutputMaps out;
   {
-    const uint64_t dims[3] = {static_cast<uint64_t>(kC), static_cast<uint64_t>(N), static_cast<uint64_t>(B) * rows};
-    const uint64_t strides[2] = {kC * 2ull, static_cast<uint64_t>(N) * kC * 2ull};
+    const uint64_t dp = static_cast<uint64_t>(d_pair);
+    const uint64_t dims[3] = {dp, static_cast<uint64_t>(N), static_cast<uint64_t>(B) * rows};
+    const uint64_t strides[2] = {dp * 2ull, static_cast<uint64_t>(N) * dp * 2ull};
     const uint32_t box[3] = {64, 64, 1};  // each CTA of a pair loads 64 of a tile's 128 positions
     rc = make_map(&map_z, z, 3, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
@@ -563,8 +583,9 @@ static int prologue_impl(const void* z, const void* packed, const uint8_t* token
     out.shift_right = mode == kLocal ? 0 : row_begin;
   }
   {
-    const uint64_t dims[2] = {static_cast<uint64_t>(kC), 6ull * 128};
-    const uint64_t strides[1] = {kC * 2ull};
+    // the four left / right matrices [128, d_pair], one after the other at the start of the packed block
+    const uint64_t dims[2] = {static_cast<uint64_t>(d_pair), 4ull * 128};
+    const uint64_t strides[1] = {static_cast<uint64_t>(d_pair) * 2ull};
     const uint32_t box[2] = {64, 128};
     rc = make_map(&map_w, packed, 2, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
@@ -586,15 +607,20 @@ static int prologue_impl(const void* z, const void* packed, const uint8_t* token
   const int pairs = p.num_tiles < info.sms / 2 ? p.num_tiles : info.sms / 2;
   const int grid = 2 * pairs;  // clusters of two CTAs: CTA 0 produces `left`, CTA 1 `right`
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (has_bias) {
-    rc = set_smem(prologue_kernel<true>, kProSmemBytes, info.device);
-    if (rc != B200_TRIMUL_OK) return rc;
-    prologue_kernel<true><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, out, p);
+#define TRIMUL_LAUNCH_PROLOGUE(BIAS, DP)                                                              \
+  do {                                                                                               \
+    rc = set_smem(prologue_kernel<BIAS, DP>, kProSmemBytes, info.device);                            \
+    if (rc != B200_TRIMUL_OK) return rc;                                                             \
+    prologue_kernel<BIAS, DP><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, out, p);   \
+  } while (0)
+  if (d_pair == kC) {
+    if (has_bias) TRIMUL_LAUNCH_PROLOGUE(true, 128);
+    else TRIMUL_LAUNCH_PROLOGUE(false, 128);
   } else {
-    rc = set_smem(prologue_kernel<false>, kProSmemBytes, info.device);
-    if (rc != B200_TRIMUL_OK) return rc;
-    prologue_kernel<false><<<grid, kProThreads, kProSmemBytes, stream>>>(map_z, map_w, out, p);
+    if (has_bias) TRIMUL_LAUNCH_PROLOGUE(true, 64);
+    else TRIMUL_LAUNCH_PROLOGUE(false, 64);
   }
+#undef TRIMUL_LAUNCH_PROLOGUE
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
 }
@@ -631,9 +657,11 @@ int b200_trimul_prologue_channels(const void* z, const void* packed, const uint8
 // partial sum). `channels` is the channel count of the operands (128, or a group of 128/P in the channel-sharded
 // form). With n_owners > 0 (all rows, B = 1) the result does not go to `tri` but, row block by row block, to
 // owner_dst[s] + slot * (N/n_owners) * channels * N * 2 bytes: slot `slot` of GPU s's [n_owners][N/n_owners][channels][N].
+// `row_channels` (0 = `channels`): channels per pair row in memory when the call works on a sub-range of them (left,
+// right and tri then point at the first channel of the range).
 static int contract_impl(const void* left, const void* right, void* tri, void* const* owner_dst, int n_owners, int slot,
                          int channels, int B, int N, int row_begin, int rows, int k_rows, int direction, int* status,
-                         void* cuda_stream) {
+                         void* cuda_stream, int row_channels = 0) {
   if (!left || !right || !status) return B200_TRIMUL_E_NULL;
   if (n_owners == 0 && !tri) return B200_TRIMUL_E_NULL;
   if (n_owners < 0 || n_owners > kMaxOwners || (n_owners > 0 && !owner_dst)) return B200_TRIMUL_E_SHAPE;
@@ -654,7 +682,7 @@ static int contract_impl(const void* left, const void* right, void* tri, void* c
   const int bn = use_pair ? ((N + 255) / 256 * 256 <= (N + 127) / 128 * 128 ? 256 : 128) : choose_bn(N);
   const uint64_t n64 = static_cast<uint64_t>(N);
   const uint64_t ch64 = static_cast<uint64_t>(channels);
-  const uint64_t row_stride = ch64 * n64 * 2;  // bytes between consecutive pair rows
+  const uint64_t row_stride = static_cast<uint64_t>(row_channels > 0 ? row_channels : channels) * n64 * 2;  // bytes between pair rows
   const uint64_t h_stride = n64 * 2;
   const uint64_t left_rows = incoming ? static_cast<uint64_t>(k_rows) : static_cast<uint64_t>(rows);
   const uint64_t right_rows = incoming ? static_cast<uint64_t>(k_rows) : n64;
@@ -805,8 +833,9 @@ int b200_trimul_reduce_partials(void* tri, const void* const* partials, int n_sr
 // `groups` = 1: tri is [B*rows][128][N]. groups = P (B = 1): tri is [P][rows][128/P][N], channel group g of every row
 // in slab g (what the channel-sharded contraction of GPU g stored there).
 static int epilogue_impl(const void* tri, const void* z, const void* packed, void* y, int B, int N, int rows, int groups,
-                         float eps_in, float eps_out, int residual, int* status, void* cuda_stream) {
+                         float eps_in, float eps_out, int residual, int* status, void* cuda_stream, int d_pair = kC) {
   if (!tri || !z || !packed || !y || !status) return B200_TRIMUL_E_NULL;
+  if (d_pair != kC && d_pair != 64) return B200_TRIMUL_E_UNSUPPORTED;
   if (groups < 1 || groups > 8 || kC % groups != 0 || (groups > 1 && B != 1)) return B200_TRIMUL_E_SHAPE;
   int rc = check_bn(B, N);
   if (rc != B200_TRIMUL_OK) return rc;
@@ -818,7 +847,7 @@ static int epilogue_impl(const void* tri, const void* z, const void* packed, voi
   const uint64_t n64 = static_cast<uint64_t>(N);
   const uint64_t nrows = static_cast<uint64_t>(B) * rows;
 
-  CUtensorMap map_t, map_z, map_y, map_w;
+  CUtensorMap map_t, map_z, map_y, map_wo, map_wg;
   {
     const uint64_t cg = static_cast<uint64_t>(kC / groups);
     const uint64_t dims[4] = {n64, cg, static_cast<uint64_t>(groups), nrows};
@@ -827,9 +856,10 @@ static int epilogue_impl(const void* tri, const void* z, const void* packed, voi
     rc = make_map(&map_t, tri, 4, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
   }
+  const uint64_t dp = static_cast<uint64_t>(d_pair);
   {
-    const uint64_t dims[3] = {static_cast<uint64_t>(kC), n64, nrows};
-    const uint64_t strides[2] = {kC * 2ull, n64 * kC * 2ull};
+    const uint64_t dims[3] = {dp, n64, nrows};
+    const uint64_t strides[2] = {dp * 2ull, n64 * dp * 2ull};
     const uint32_t box[3] = {64, 128, 1};
     rc = make_map(&map_z, z, 3, dims, strides, box);
     if (rc != B200_TRIMUL_OK) return rc;
@@ -837,10 +867,16 @@ static int epilogue_impl(const void* tri, const void* z, const void* packed, voi
     if (rc != B200_TRIMUL_OK) return rc;
   }
   {
-    const uint64_t dims[2] = {static_cast<uint64_t>(kC), 6ull * 128};
-    const uint64_t strides[1] = {kC * 2ull};
-    const uint32_t box[2] = {64, 128};
-    rc = make_map(&map_w, packed, 2, dims, strides, box);
+    // Wo' [d_pair, 128] and Wg' [d_pair, d_pair] of the packed block, each loaded in 64-wide k halves
+    const uint8_t* pk = static_cast<const uint8_t*>(packed);
+    const uint64_t dims_o[2] = {128ull, dp};
+    const uint64_t strides_o[1] = {128 * 2ull};
+    const uint64_t dims_g[2] = {dp, dp};
+    const uint64_t strides_g[1] = {dp * 2ull};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(d_pair)};
+    rc = make_map(&map_wo, pk + packed_matrix_offset(4, d_pair), 2, dims_o, strides_o, box);
+    if (rc != B200_TRIMUL_OK) return rc;
+    rc = make_map(&map_wg, pk + packed_matrix_offset(5, d_pair), 2, dims_g, strides_g, box);
     if (rc != B200_TRIMUL_OK) return rc;
   }
   EpilogueParams p;
@@ -851,11 +887,17 @@ static int epilogue_impl(const void* tri, const void* z, const void* packed, voi
   p.eps_out = eps_out * (kTriScale * kTriScale);  // tri arrives scaled by kTriScale
   p.residual = residual;
   p.status = status;
-  rc = set_smem(epilogue_kernel, kEpiSmemBytes, info.device);
-  if (rc != B200_TRIMUL_OK) return rc;
   const int grid = p.num_tiles < info.sms ? p.num_tiles : info.sms;
-  epilogue_kernel<<<grid, kEpilogueThreads, kEpiSmemBytes, static_cast<cudaStream_t>(cuda_stream)>>>(map_t, map_z, map_y,
-                                                                                                       map_w, p);
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (d_pair == kC) {
+    rc = set_smem(epilogue_kernel<128>, kEpiSmemBytes, info.device);
+    if (rc != B200_TRIMUL_OK) return rc;
+    epilogue_kernel<128><<<grid, kEpilogueThreads, kEpiSmemBytes, stream>>>(map_t, map_z, map_y, map_wo, map_wg, p);
+  } else {
+    rc = set_smem(epilogue_kernel<64>, kEpiSmemBytes, info.device);
+    if (rc != B200_TRIMUL_OK) return rc;
+    epilogue_kernel<64><<<grid, kEpilogueThreads, kEpiSmemBytes, stream>>>(map_t, map_z, map_y, map_wo, map_wg, p);
+  }
   TRIMUL_CUDA(cudaGetLastError());
   return B200_TRIMUL_OK;
 }
@@ -980,6 +1022,40 @@ int b200_trimul_forward_ex(const void* z, const void* w_left, const void* w_left
   int has_bias = 0;
   if (bias_opt != nullptr)
     for (int i = 0; i < 4; ++i) has_bias |= bias_opt[i] != nullptr;
+  if (d_pair == 64) {
+    // Narrow pair stacks: 64 input channels, 128 contracted channels in one [rows, 128, N] tensor. The parameter
+    // shapes are to_left / to_left_gate / to_right / to_right_gate [128, 64], ln_out [128], to_out [64, 128],
+    // to_gate [64, 64] for both forms; the bidirectional module contracts channels 0-63 outgoing and 64-127 incoming.
+    if (drop_scale != nullptr) return B200_TRIMUL_E_UNSUPPORTED;
+    if (!w_left || !w_left_gate || !w_right || !w_right_gate || !w_gate || !w_out) return B200_TRIMUL_E_NULL;
+    const void* w[6] = {w_left, w_left_gate, w_right, w_right_gate, w_out, w_gate};
+    const int ld[6] = {64, 64, 64, 64, kC, 64};
+    const float* bias[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    if (bias_opt != nullptr) {
+      for (int i = 0; i < 4; ++i) bias[i] = static_cast<const float*>(bias_opt[i]);
+      bias[5] = static_cast<const float*>(bias_opt[4]);
+      bias[4] = static_cast<const float*>(bias_opt[5]);
+    }
+    rc = pack_impl(w, ld, weight_dtype, ln_in_w, ln_in_b, ln_out_w, ln_out_b, bias, packed, cuda_stream, 64);
+    if (rc != B200_TRIMUL_OK) return rc;
+    void* l[1] = {left};
+    void* r[1] = {right};
+    rc = prologue_impl(z, packed, token_mask, pair_mask, l, 1, r, 1, kLocal, B, N, 0, N, eps_in, has_bias, status,
+                       cuda_stream, 64);
+    if (rc != B200_TRIMUL_OK) return rc;
+    if (direction == B200_TRIMUL_BIDIRECTIONAL) {
+      const size_t half = static_cast<size_t>(64) * N * 2;  // bytes from channel 0 to channel 64 of a pair row
+      rc = contract_impl(left, right, tri, nullptr, 0, 0, 64, B, N, 0, N, N, B200_TRIMUL_OUTGOING, status, cuda_stream, kC);
+      if (rc != B200_TRIMUL_OK) return rc;
+      rc = contract_impl(static_cast<uint8_t*>(left) + half, static_cast<uint8_t*>(right) + half,
+                         static_cast<uint8_t*>(tri) + half, nullptr, 0, 0, 64, B, N, 0, N, N, B200_TRIMUL_INCOMING, status,
+                         cuda_stream, kC);
+    } else {
+      rc = b200_trimul_contract(left, right, tri, B, N, 0, N, direction, status, cuda_stream);
+    }
+    if (rc != B200_TRIMUL_OK) return rc;
+    return epilogue_impl(tri, z, packed, y, B, N, N, 1, eps_in, eps_out, residual, status, cuda_stream, 64);
+  }
   if (direction == B200_TRIMUL_BIDIRECTIONAL) {
     // workspace tail: second tri tensor, then the second packed block
     const size_t plane = plane_tensor_bytes(B, N, N);

@@ -48,9 +48,10 @@ def _direction(outgoing: Optional[bool]) -> int:
     return _lib.OUTGOING if outgoing else _lib.INCOMING
 
 
-def workspace_bytes(B: int, N: int, outgoing: Optional[bool] = True) -> int:
+def workspace_bytes(B: int, N: int, outgoing: Optional[bool] = True, d_pair: int = D) -> int:
     out = c_size_t(0)
-    rc = _lib.load().b200_trimul_workspace_bytes(B, N, D, D, _direction(outgoing), ctypes.byref(out))
+    d_hidden = D if (d_pair == D or outgoing is not None) else 64
+    rc = _lib.load().b200_trimul_workspace_bytes(B, N, d_pair, d_hidden, _direction(outgoing), ctypes.byref(out))
     _lib.check(rc, "b200_trimul_workspace_bytes")
     return int(out.value)
 
@@ -79,13 +80,20 @@ def as_mask_u8(mask: Optional[torch.Tensor], device: torch.device) -> Optional[t
 class _Weights:
     """Validated pointers of one parameter set (all weights in one dtype, LN affine fp32)."""
 
-    def __init__(self, params: dict, biases: Optional[dict], device: torch.device, bidirectional: bool = False):
+    def __init__(self, params: dict, biases: Optional[dict], device: torch.device, bidirectional: bool = False,
+                 d_pair: int = D):
         self.bidirectional = bool(bidirectional)
-        wide = 2 * D if bidirectional else D  # the four left / right matrices, ln_out and the columns of to_out
-        shapes = {"to_left.weight": (wide, D), "to_left_gate.weight": (wide, D), "to_right.weight": (wide, D),
-                  "to_right_gate.weight": (wide, D), "to_gate.weight": (D, D), "to_out.weight": (D, wide),
-                  "ln_pair.weight": (D,), "ln_pair.bias": (D,), "ln_out.weight": (wide,), "ln_out.bias": (wide,)}
-        bias_len = {"to_left": wide, "to_left_gate": wide, "to_right": wide, "to_right_gate": wide, "to_gate": D, "to_out": D}
+        if d_pair not in (D, 64):
+            raise RuntimeError(f"d_pair must be {D} or 64, got {d_pair}")
+        self.d_pair = C = int(d_pair)
+        # contracted channels in total: 128, except the 128-wide bidirectional module (128 per direction). With
+        # d_pair = 64 that is d_hidden = 128 for one direction, or 64 per direction for the bidirectional module.
+        wide = 2 * D if (bidirectional and C == D) else D
+        self.d_hidden = D if (C == D or not bidirectional) else 64
+        shapes = {"to_left.weight": (wide, C), "to_left_gate.weight": (wide, C), "to_right.weight": (wide, C),
+                  "to_right_gate.weight": (wide, C), "to_gate.weight": (C, C), "to_out.weight": (C, wide),
+                  "ln_pair.weight": (C,), "ln_pair.bias": (C,), "ln_out.weight": (wide,), "ln_out.bias": (wide,)}
+        bias_len = {"to_left": wide, "to_left_gate": wide, "to_right": wide, "to_right_gate": wide, "to_gate": C, "to_out": C}
         ws = [params[k] for k in WEIGHT_KEYS]
         dt = ws[0].dtype
         if dt not in (torch.bfloat16, torch.float32):
@@ -96,7 +104,8 @@ class _Weights:
             if w.dtype != dt:
                 raise RuntimeError("all six linear weights must share one dtype")
             if tuple(w.shape) != shapes[k]:
-                raise RuntimeError(f"{k}: expected shape {shapes[k]}, got {tuple(w.shape)} (only d_pair = d_hidden = 128 is supported)")
+                raise RuntimeError(f"{k}: expected shape {shapes[k]}, got {tuple(w.shape)} (d_pair = {C}, "
+                                   f"{'bidirectional' if bidirectional else 'one direction'})")
             if not w.is_contiguous():
                 # a silent .contiguous() copy would be cached by the caller and go stale after an in-place update
                 raise RuntimeError(f"{k} must be contiguous (the kernels read the parameter's own storage on every call)")
@@ -133,12 +142,12 @@ class _Weights:
             self.bias_array = arr
 
 
-def _check_z(z: torch.Tensor) -> tuple[int, int]:
+def _check_z(z: torch.Tensor, widths=(D,)) -> tuple[int, int]:
     _require_cuda(z, "pair tensor")
     if z.dtype != torch.bfloat16:
         raise RuntimeError(f"pair tensor must be bf16, got {z.dtype}")
-    if z.dim() != 4 or z.shape[3] != D:
-        raise RuntimeError(f"pair tensor must be [B, rows, N, {D}], got {tuple(z.shape)}")
+    if z.dim() != 4 or z.shape[3] not in widths:
+        raise RuntimeError(f"pair tensor must be [B, rows, N, {' or '.join(str(w) for w in widths)}], got {tuple(z.shape)}")
     if not z.is_contiguous():
         raise RuntimeError("pair tensor must be contiguous")
     return int(z.shape[0]), int(z.shape[2])
@@ -432,20 +441,23 @@ def trimul_forward(
     ``check=True`` synchronises and raises if a device-side wait gave up. ``weights`` is an already validated
     :class:`_Weights` of the same parameters (it only holds pointers: the values are packed on the GPU in every call).
     """
-    B, N = _check_z(z)
+    B, N = _check_z(z, widths=(D, 64))
     if z.shape[1] != N:
         raise RuntimeError(f"pair tensor must be square in its token dims, got {tuple(z.shape)}")
     dev = z.device
-    w = weights if weights is not None else _Weights(params, biases, dev, bidirectional=outgoing is None)
-    if w.bidirectional != (outgoing is None):
-        raise RuntimeError("the validated weights belong to the other module kind (bidirectional vs one direction)")
+    C = int(z.shape[3])
+    w = weights if weights is not None else _Weights(params, biases, dev, bidirectional=outgoing is None, d_pair=C)
+    if w.bidirectional != (outgoing is None) or w.d_pair != C:
+        raise RuntimeError("the validated weights belong to another module kind (direction or width)")
+    if C != D and drop_scale is not None:
+        raise RuntimeError("the row-shared dropout scale is only implemented for d_pair = 128")
     ds = None
     if drop_scale is not None:
         _require_cuda(drop_scale, "drop_scale")
-        if drop_scale.numel() != B * N * D or drop_scale.shape[-1] != D or drop_scale.shape[0] != B:
+        if drop_scale.numel() != B * N * D or drop_scale.shape[-1] != D or drop_scale.shape[0] != B:  # d_pair = 128 here
             raise RuntimeError(f"drop_scale must be [B, 1, N, {D}] = ({B}, 1, {N}, {D}), got {tuple(drop_scale.shape)}")
         ds = drop_scale.detach().to(torch.bfloat16).contiguous()
-    need = workspace_bytes(B, N, outgoing)
+    need = workspace_bytes(B, N, outgoing, C)
     if workspace is None:
         workspace = aligned_empty(need, dev)
     elif workspace.numel() * workspace.element_size() < need:
@@ -473,8 +485,8 @@ def trimul_forward(
             workspace.numel() * workspace.element_size(),
             B,
             N,
-            D,
-            D,
+            C,
+            w.d_hidden,
             _direction(outgoing),
             float(eps_in),
             float(eps_out),

@@ -109,10 +109,19 @@ class TriangleMultiplication(nn.Module):
         super().__init__()
         wide = 2 if self._bidirectional else 1
         d_hidden = d_pair if d_hidden is None else d_hidden
-        if d_pair != D_SUPPORTED or d_hidden != D_SUPPORTED:
+        # the kernels contract 128 channels per call of the contraction stage and take 128 or 64 input channels:
+        #   d_pair 128, d_hidden 128 (either module);  d_pair 64 with d_hidden 128 (one direction: the template
+        #   blocks of the Protenix harness, benchmarks/protenix_finetune/patch_engine.py:283-295);  d_pair 64 with
+        #   d_hidden 64 (bidirectional: the (L, D) = (384, 64) case of the reference's validation,
+        #   docs/archive/engine2-validation-20260923/validate_bidir_reference.py:11)
+        ok = (d_pair, d_hidden) == (D_SUPPORTED, D_SUPPORTED) or (d_pair, wide * d_hidden) == (64, D_SUPPORTED)
+        if not ok:
             raise NotImplementedError(
-                f"only d_pair = d_hidden = {D_SUPPORTED} is implemented on this path (got {d_pair}, {d_hidden})"
+                f"implemented widths: d_pair = d_hidden = {D_SUPPORTED}; d_pair = 64 with d_hidden = 128 (one direction) or "
+                f"64 (bidirectional); got d_pair = {d_pair}, d_hidden = {d_hidden}"
             )
+        if d_pair != D_SUPPORTED and p_drop > 0.0:
+            raise NotImplementedError("the row-shared dropout of the training forward is only implemented for d_pair = 128")
         impl = getattr(implementation, "value", implementation)
         impl = impl.lower() if isinstance(impl, str) else impl
         if impl not in _ACCEPTED_IMPLEMENTATIONS:
@@ -158,7 +167,8 @@ class TriangleMultiplication(nn.Module):
         params = self._params()
         key = tuple((v.data_ptr(), v.dtype, v.device, v.is_contiguous()) for v in params.values()) + (device,)
         if self._wcache is None or self._wcache[0] != key:
-            self._wcache = (key, F_._Weights(params, self._biases, device, bidirectional=self._bidirectional))
+            self._wcache = (key, F_._Weights(params, self._biases, device, bidirectional=self._bidirectional,
+                                             d_pair=self.d_pair))
         return self._wcache[1]
 
     def _params(self) -> dict:
@@ -197,7 +207,7 @@ class TriangleMultiplication(nn.Module):
         return keep.to(torch.bfloat16) / (1.0 - p)
 
     def _get_workspace(self, B: int, N: int, device: torch.device) -> torch.Tensor:
-        need = F_.workspace_bytes(B, N, self._direction())
+        need = F_.workspace_bytes(B, N, self._direction(), self.d_pair)
         ws = self._workspace
         if ws is None or ws.device != device or ws.numel() < need:
             ws = F_.aligned_empty(need, device)

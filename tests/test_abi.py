@@ -55,7 +55,9 @@ def test_workspace_size_and_layout(lib):
 @pytest.mark.parametrize(
     "args,code",
     [
-        ((1, 384, 64, 128, 1), -3),   # d_pair != 128
+        ((1, 384, 64, 64, 1), -3),    # d_pair 64 needs 128 contracted channels in total
+        ((1, 384, 64, 128, 0), -3),   # ... so 64 per direction when bidirectional
+        ((1, 384, 32, 128, 1), -3),   # d_pair not 64 or 128
         ((1, 384, 128, 256, 1), -3),  # d_hidden != 128
         ((1, 100, 128, 128, 1), -3),  # N not a multiple of 8
         ((0, 384, 128, 128, 1), -2),  # B < 1

@@ -226,7 +226,7 @@ def test_errors_are_loud():
     with pytest.raises(RuntimeError):
         F_.trimul_forward(torch.zeros(1, 12, 12, 128, dtype=torch.bfloat16, device=DEV), params_to(p, DEV))  # N % 8
     with pytest.raises(NotImplementedError):
-        mw.TriangleMultiplication(64)
+        mw.TriangleMultiplication(64)  # 64 contracted channels in one direction is not a shape the kernels take
     zz = torch.zeros(1, 16, 16, 128, dtype=torch.bfloat16, device=DEV, requires_grad=True)
     with pytest.raises(NotImplementedError):
         m(zz, None)

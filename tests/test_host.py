@@ -64,9 +64,17 @@ def test_openfold_alias_round_trip():
 
 def test_unsupported_configurations_raise():
     with pytest.raises(NotImplementedError):
-        mw.TriangleMultiplication(64)
+        mw.TriangleMultiplication(64)  # 64 contracted channels in one direction
     with pytest.raises(NotImplementedError):
         mw.TriangleMultiplication(128, d_hidden=256)
+    with pytest.raises(NotImplementedError):
+        mw.BidirectionalTriangleMultiplication(64, d_hidden=128)
+    with pytest.raises(NotImplementedError):
+        mw.TriangleMultiplication(64, d_hidden=128, p_drop=0.25)
+    m64 = mw.TriangleMultiplication(64, d_hidden=128)  # the template blocks' shape
+    assert m64.to_left.weight.shape == (128, 64) and m64.to_out.weight.shape == (64, 128) and m64.ln_out.weight.shape == (128,)
+    b64 = mw.BidirectionalTriangleMultiplication(64)
+    assert b64.to_left.weight.shape == (128, 64) and b64.to_gate.weight.shape == (64, 64) and b64.ln_out.weight.shape == (128,)
     with pytest.raises(ValueError):
         mw.TriangleMultiplication(128, implementation="cuequivariance")
     m = mw.TriangleMultiplication(128)

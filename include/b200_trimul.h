@@ -117,6 +117,18 @@ int b200_trimul_contract(const void* left, const void* right, void* tri, int B, 
                          int direction, int* status, void* cuda_stream);
 
 /*
+ * Gradients of stage 2 with respect to its operands (the reference's backward runs these four products as cuBLAS
+ * calls, "B5-B6" in docs/kernels/trimul/TRIMUL_STATUS.md:47): given dtri = d loss / d tri in the layout of `tri`
+ * ([B, N, 128, N] fp16, in any scale the caller chose so that it fits fp16),
+ *   outgoing:  dleft[b,i,h,k] = sum_j dtri[b,i,h,j] right[b,j,h,k],   dright[b,j,h,k] = sum_i dtri[b,i,h,j] left[b,i,h,k]
+ *   incoming:  dleft[b,k,h,i] = sum_j dtri[b,i,h,j] right[b,k,h,j],   dright[b,k,h,j] = sum_i dtri[b,i,h,j] left[b,k,h,i]
+ * written like every contraction output of this library: times 2^-4, saturated to the fp16 range. Whole tensors only
+ * (all N rows). Two launches of the stage-2 kernels; one of the four products has a K-major and an MN-major operand.
+ */
+int b200_trimul_contract_backward(const void* dtri, const void* left, const void* right, void* dleft, void* dright,
+                                  int B, int N, int direction, int* status, void* cuda_stream);
+
+/*
  * Stage 2, partial form for the incoming direction when the pair rows k are spread over several GPUs:
  * left / right: [B, k_rows, 128, N] fp16, the k_rows pair rows this GPU holds (any contiguous slab of k);
  * tri_partial: [B, N, 128, N] fp16 = 2^-4 * sum over those k of left[k, :, i] * right[k, :, j] for ALL (i, j).

@@ -1,4 +1,5 @@
-"""B200-native forward path of MiniWorld's Pairformer triangle multiplicative update.
+"""B200-native path of MiniWorld's Pairformer triangle multiplicative update (forward; backward of the unidirectional
+module in :mod:`miniworld_b200.training`).
 
 Public surface: the module classes (drop-in for ``miniworld_engine.modules.TriangleMultiplication`` as
 MiniWorld's blocks use it), the functional entry points over the C ABI, and the row-sharded /

@@ -37,6 +37,10 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     ),
+    "b200_trimul_contract_backward": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
     "b200_trimul_contract_partial": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],

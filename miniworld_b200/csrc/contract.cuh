@@ -2,6 +2,8 @@
 //
 //   outgoing: t[b,i,h,j] = sum_k a[b,i,h,k] * b[b,j,h,k]     (both operands K-major in shared memory)
 //   incoming: t[b,i,h,j] = sum_k a[b,k,h,i] * b[b,k,h,j]     (both operands MN-major, no transpose pass)
+//   mixed:    t[b,i,h,j] = sum_k a[b,i,h,k] * b[b,k,h,j]     (a K-major, b MN-major: a plain per-plane product,
+//                                                              which the gradients of the two forms above need)
 //
 // a, b and t are stored "row-plane": [B, rows, H, N] fp16 (for each row a [H, N] slab), so the rows of
 // a row-sharded operand gathered from several ranks are one uniform strided dimension.  fp16 rather than
@@ -49,6 +51,10 @@ constexpr int kContractStages = 4;
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 
+constexpr int kContractOutgoing = 0;
+constexpr int kContractIncoming = 1;
+constexpr int kContractMixed = 2;
+
 constexpr float kTriScale = 0.0625f;  // t is stored as t * 2^-4
 
 // two fp32 accumulators -> scaled, saturated fp16 pair
@@ -67,12 +73,14 @@ struct ContractSmem {
   static constexpr int kTotal = kContractStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
 
-template <int BN, bool INCOMING>
+template <int BN, int MODE>
 __global__ void __launch_bounds__(kContractThreads, 1)
 contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_t, const ContractParams p) {
   using L = ContractSmem<BN>;
   constexpr int S = kContractStages;
+  constexpr bool A_MN = MODE == kContractIncoming;  // A operand MN-major (its k index is the tensor's row)
+  constexpr bool B_MN = MODE != kContractOutgoing;  // B operand MN-major
   constexpr uint32_t kTmemCols = (2 * BN > 256) ? 512u : 256u;
   constexpr uint32_t kAccStride = kTmemCols / 2;
 
@@ -145,13 +153,16 @@ contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t sa = stage_base + s * L::kStageBytes;
           const uint32_t sb = sa + L::kABytes;
           const int k0 = kb * kBK;
-          if constexpr (!INCOMING) {
+          if constexpr (!A_MN) {
             tma_load_4d(sa, &map_a, full_bar(s), k0, m0, hh, bb);
-            tma_load_4d(sb, &map_b, full_bar(s), k0, n0, hh, bb);
           } else {
 #pragma unroll
             for (int hf = 0; hf < kBM / 64; ++hf)
               tma_load_4d(sa + hf * 8192, &map_a, full_bar(s), p.a_col_off + m0 + 64 * hf, k0, hh, bb);
+          }
+          if constexpr (!B_MN) {
+            tma_load_4d(sb, &map_b, full_bar(s), k0, n0, hh, bb);
+          } else {
 #pragma unroll
             for (int hf = 0; hf < BN / 64; ++hf)
               tma_load_4d(sb + hf * 8192, &map_b, full_bar(s), n0 + 64 * hf, k0, hh, bb);
@@ -183,7 +194,7 @@ contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(kBM, BN, INCOMING, INCOMING, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc = umma_idesc(kBM, BN, A_MN, B_MN, kFmtF16, kFmtF16);
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -202,20 +213,15 @@ contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           tc_fence_after();
           const uint32_t sa = stage_base + s * L::kStageBytes;
           const uint32_t sb = sa + L::kABytes;
-          uint64_t da, db;
-          uint32_t kstep;  // descriptor start-address step per 16-deep MMA, in 16-byte units
-          if constexpr (!INCOMING) {
-            da = umma_desc_kmajor(sa);
-            db = umma_desc_kmajor(sb);
-            kstep = 32 >> 4;
-          } else {
-            da = umma_desc_mnmajor(sa, 8192);
-            db = umma_desc_mnmajor(sb, 8192);
-            kstep = 2048 >> 4;
-          }
+          // descriptor start-address step per 16-deep MMA, in 16-byte units: 32 bytes along a K-major row, sixteen
+          // 128-byte rows of an MN-major tile
+          const uint64_t da = A_MN ? umma_desc_mnmajor(sa, 8192) : umma_desc_kmajor(sa);
+          const uint64_t db = B_MN ? umma_desc_mnmajor(sb, 8192) : umma_desc_kmajor(sb);
+          constexpr uint32_t kstep_a = A_MN ? (2048 >> 4) : (32 >> 4);
+          constexpr uint32_t kstep_b = B_MN ? (2048 >> 4) : (32 >> 4);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
-            umma_bf16(d_tmem, da + static_cast<uint64_t>(k * kstep), db + static_cast<uint64_t>(k * kstep), idesc,
+            umma_bf16(d_tmem, da + static_cast<uint64_t>(k * kstep_a), db + static_cast<uint64_t>(k * kstep_b), idesc,
                       (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(s));

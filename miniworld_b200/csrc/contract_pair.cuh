@@ -28,13 +28,15 @@ struct PairSmem {
 };
 
 // ContractParams::m_tiles counts 256-row pair tiles here.
-template <int BN, bool INCOMING>
+template <int BN, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kContractThreads, 1)
 contract_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_t, const __grid_constant__ TriOwners own,
                      const ContractParams p) {
   using L = PairSmem<BN>;
   constexpr int S = kPairStages;
+  constexpr bool A_MN = MODE == kContractIncoming;  // A operand MN-major (its k index is the tensor's row)
+  constexpr bool B_MN = MODE != kContractOutgoing;  // B operand MN-major
   constexpr uint32_t kTmemCols = (2 * BN > 256) ? 512u : 256u;
   constexpr uint32_t kAccStride = kTmemCols / 2;
   constexpr int kHalfN = BN / 2;
@@ -113,13 +115,16 @@ contract_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint32_t sa = stage_base + s * L::kStageBytes;
           const uint32_t sb = sa + L::kABytes;
           const int k0 = kb * kBK;
-          if constexpr (!INCOMING) {
+          if constexpr (!A_MN) {
             tma_load_4d_pair(sa, &map_a, lead_full, k0, m0, hh, bb);
-            tma_load_4d_pair(sb, &map_b, lead_full, k0, n0, hh, bb);
           } else {
 #pragma unroll
             for (int hf = 0; hf < kBM / 64; ++hf)
               tma_load_4d_pair(sa + hf * 8192, &map_a, lead_full, p.a_col_off + m0 + 64 * hf, k0, hh, bb);
+          }
+          if constexpr (!B_MN) {
+            tma_load_4d_pair(sb, &map_b, lead_full, k0, n0, hh, bb);
+          } else {
 #pragma unroll
             for (int hf = 0; hf < kHalfN / 64; ++hf)
               tma_load_4d_pair(sb + hf * 8192, &map_b, lead_full, n0 + 64 * hf, k0, hh, bb);
@@ -154,7 +159,7 @@ contract_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc(256, BN, INCOMING, INCOMING, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc = umma_idesc(256, BN, A_MN, B_MN, kFmtF16, kFmtF16);
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -173,20 +178,13 @@ contract_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           tc_fence_after();
           const uint32_t sa = stage_base + s * L::kStageBytes;
           const uint32_t sb = sa + L::kABytes;
-          uint64_t da, db;
-          uint32_t kstep;
-          if constexpr (!INCOMING) {
-            da = umma_desc_kmajor(sa);
-            db = umma_desc_kmajor(sb);
-            kstep = 32 >> 4;
-          } else {
-            da = umma_desc_mnmajor(sa, 8192);
-            db = umma_desc_mnmajor(sb, 8192);
-            kstep = 2048 >> 4;
-          }
+          const uint64_t da = A_MN ? umma_desc_mnmajor(sa, 8192) : umma_desc_kmajor(sa);
+          const uint64_t db = B_MN ? umma_desc_mnmajor(sb, 8192) : umma_desc_kmajor(sb);
+          constexpr uint32_t kstep_a = A_MN ? (2048 >> 4) : (32 >> 4);
+          constexpr uint32_t kstep_b = B_MN ? (2048 >> 4) : (32 >> 4);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
-            umma_pair(d_tmem, da + static_cast<uint64_t>(k * kstep), db + static_cast<uint64_t>(k * kstep), idesc,
+            umma_pair(d_tmem, da + static_cast<uint64_t>(k * kstep_a), db + static_cast<uint64_t>(k * kstep_b), idesc,
                       (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(s));

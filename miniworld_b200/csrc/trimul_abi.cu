@@ -338,11 +338,11 @@ static int choose_bn(int N) {
   return best;
 }
 
-template <int BN, bool INCOMING>
+template <int BN, int MODE>
 static int launch_contract(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mt, const ContractParams& p,
                            const DeviceInfo& info, cudaStream_t stream) {
   const int sms = info.sms;
-  auto kernel = contract_kernel<BN, INCOMING>;
+  auto kernel = contract_kernel<BN, MODE>;
   constexpr int smem = ContractSmem<BN>::kTotal;
   int rc = set_smem(kernel, smem, info.device);
   if (rc != B200_TRIMUL_OK) return rc;
@@ -353,12 +353,12 @@ static int launch_contract(const CUtensorMap& ma, const CUtensorMap& mb, const C
   return B200_TRIMUL_OK;
 }
 
-template <int BN, bool INCOMING>
+template <int BN, int MODE>
 static int launch_contract_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mt,
                                 const TriOwners& own, const ContractParams& p, const DeviceInfo& info,
                                 cudaStream_t stream) {
   const int sms = info.sms;
-  auto kernel = contract_pair_kernel<BN, INCOMING>;
+  auto kernel = contract_pair_kernel<BN, MODE>;
   constexpr int smem = PairSmem<BN>::kTotal;
   int rc = set_smem(kernel, smem, info.device);
   if (rc != B200_TRIMUL_OK) return rc;
@@ -659,6 +659,9 @@ int b200_trimul_prologue_channels(const void* z, const void* packed, const uint8
 // owner_dst[s] + slot * (N/n_owners) * channels * N * 2 bytes: slot `slot` of GPU s's [n_owners][N/n_owners][channels][N].
 // `row_channels` (0 = `channels`): channels per pair row in memory when the call works on a sub-range of them (left,
 // right and tri then point at the first channel of the range).
+// internal third operand form of contract_impl (not a module direction): t[i][j] = sum_k a[i][k] b[k][j] per plane
+constexpr int kDirMixed = 3;
+
 static int contract_impl(const void* left, const void* right, void* tri, void* const* owner_dst, int n_owners, int slot,
                          int channels, int B, int N, int row_begin, int rows, int k_rows, int direction, int* status,
                          void* cuda_stream, int row_channels = 0) {
@@ -670,12 +673,17 @@ static int contract_impl(const void* left, const void* right, void* tri, void* c
   if (rc != B200_TRIMUL_OK) return rc;
   if (rows < 1 || row_begin < 0 || row_begin + rows > N) return B200_TRIMUL_E_SHAPE;
   if (k_rows < 1 || k_rows > N) return B200_TRIMUL_E_SHAPE;
-  if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING) return B200_TRIMUL_E_SHAPE;
+  if (direction != B200_TRIMUL_OUTGOING && direction != B200_TRIMUL_INCOMING && direction != kDirMixed)
+    return B200_TRIMUL_E_SHAPE;
+  if (direction == kDirMixed && (k_rows != N || n_owners != 0)) return B200_TRIMUL_E_SHAPE;
   if (!aligned(left, 16) || !aligned(right, 16) || (tri && !aligned(tri, 16))) return B200_TRIMUL_E_ALIGN;
   DeviceInfo info;
   rc = device_info(&info);
   if (rc != B200_TRIMUL_OK) return rc;
-  const bool incoming = direction == B200_TRIMUL_INCOMING;
+  // operand forms: a is MN-major (its k index is the tensor's row) for the incoming contraction only, b for the
+  // incoming and the mixed one
+  const bool a_mn = direction == B200_TRIMUL_INCOMING;
+  const bool b_mn = direction != B200_TRIMUL_OUTGOING;
   // CTA pairs work on 256-row tiles: used when that pads the rows by at most a quarter.
   const int pair_rows = (rows + 255) / 256 * 256;
   const bool use_pair = rows >= 256 && (pair_rows - rows) * 4 <= rows;
@@ -684,8 +692,8 @@ static int contract_impl(const void* left, const void* right, void* tri, void* c
   const uint64_t ch64 = static_cast<uint64_t>(channels);
   const uint64_t row_stride = static_cast<uint64_t>(row_channels > 0 ? row_channels : channels) * n64 * 2;  // bytes between pair rows
   const uint64_t h_stride = n64 * 2;
-  const uint64_t left_rows = incoming ? static_cast<uint64_t>(k_rows) : static_cast<uint64_t>(rows);
-  const uint64_t right_rows = incoming ? static_cast<uint64_t>(k_rows) : n64;
+  const uint64_t left_rows = a_mn ? static_cast<uint64_t>(k_rows) : static_cast<uint64_t>(rows);
+  const uint64_t right_rows = b_mn ? static_cast<uint64_t>(k_rows) : n64;
 
   CUtensorMap map_a, map_b, map_t;
   {
@@ -693,7 +701,7 @@ static int contract_impl(const void* left, const void* right, void* tri, void* c
     const uint64_t strides[3] = {row_stride, h_stride, left_rows * row_stride};
     const uint32_t box_out[4] = {64, 128, 1, 1};
     const uint32_t box_in[4] = {64, 64, 1, 1};
-    rc = make_map(&map_a, left, 4, dims, strides, incoming ? box_in : box_out);
+    rc = make_map(&map_a, left, 4, dims, strides, a_mn ? box_in : box_out);
     if (rc != B200_TRIMUL_OK) return rc;
   }
   {
@@ -701,7 +709,7 @@ static int contract_impl(const void* left, const void* right, void* tri, void* c
     const uint64_t strides[3] = {row_stride, h_stride, right_rows * row_stride};
     const uint32_t box_out[4] = {64, static_cast<uint32_t>(use_pair ? bn / 2 : bn), 1, 1};  // a CTA of a pair loads half
     const uint32_t box_in[4] = {64, 64, 1, 1};
-    rc = make_map(&map_b, right, 4, dims, strides, incoming ? box_in : box_out);
+    rc = make_map(&map_b, right, 4, dims, strides, b_mn ? box_in : box_out);
     if (rc != B200_TRIMUL_OK) return rc;
   }
   TriOwners own;
@@ -739,32 +747,49 @@ static int contract_impl(const void* left, const void* right, void* tri, void* c
   p.m_tiles = use_pair ? pair_rows / 256 : (rows + kBM - 1) / kBM;
   p.m_rows = rows;
   p.n_tiles = (N + bn - 1) / bn;
-  p.num_kb = ((incoming ? k_rows : N) + kBK - 1) / kBK;  // rows past k_rows read as zero (TMA out-of-bounds fill)
-  p.a_col_off = incoming ? row_begin : 0;
+  p.num_kb = ((b_mn ? k_rows : N) + kBK - 1) / kBK;  // rows past k_rows read as zero (TMA out-of-bounds fill)
+  p.a_col_off = a_mn ? row_begin : 0;
   p.n_cols = N;
   p.status = status;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (use_pair) {
-    if (!incoming) {
-      if (bn == 256) return launch_contract_pair<256, false>(map_a, map_b, map_t, own, p, info, stream);
-      return launch_contract_pair<128, false>(map_a, map_b, map_t, own, p, info, stream);
-    }
-    if (bn == 256) return launch_contract_pair<256, true>(map_a, map_b, map_t, own, p, info, stream);
-    return launch_contract_pair<128, true>(map_a, map_b, map_t, own, p, info, stream);
-  }
-  if (!incoming) {
-    if (bn == 256) return launch_contract<256, false>(map_a, map_b, map_t, p, info, stream);
-    if (bn == 192) return launch_contract<192, false>(map_a, map_b, map_t, p, info, stream);
-    return launch_contract<128, false>(map_a, map_b, map_t, p, info, stream);
-  }
-  if (bn == 256) return launch_contract<256, true>(map_a, map_b, map_t, p, info, stream);
-  if (bn == 192) return launch_contract<192, true>(map_a, map_b, map_t, p, info, stream);
-  return launch_contract<128, true>(map_a, map_b, map_t, p, info, stream);
+#define TRIMUL_CONTRACT_MODE(MODE)                                                                       \
+  do {                                                                                                   \
+    if (use_pair) {                                                                                      \
+      if (bn == 256) return launch_contract_pair<256, MODE>(map_a, map_b, map_t, own, p, info, stream); \
+      return launch_contract_pair<128, MODE>(map_a, map_b, map_t, own, p, info, stream);                \
+    }                                                                                                    \
+    if (bn == 256) return launch_contract<256, MODE>(map_a, map_b, map_t, p, info, stream);             \
+    if (bn == 192) return launch_contract<192, MODE>(map_a, map_b, map_t, p, info, stream);             \
+    return launch_contract<128, MODE>(map_a, map_b, map_t, p, info, stream);                            \
+  } while (0)
+  if (direction == B200_TRIMUL_OUTGOING) TRIMUL_CONTRACT_MODE(kContractOutgoing);
+  if (direction == B200_TRIMUL_INCOMING) TRIMUL_CONTRACT_MODE(kContractIncoming);
+  TRIMUL_CONTRACT_MODE(kContractMixed);
+#undef TRIMUL_CONTRACT_MODE
 }
 
 int b200_trimul_contract(const void* left, const void* right, void* tri, int B, int N, int row_begin, int rows,
                          int direction, int* status, void* cuda_stream) {
   return contract_impl(left, right, tri, nullptr, 0, 0, kC, B, N, row_begin, rows, N, direction, status, cuda_stream);
+}
+
+int b200_trimul_contract_backward(const void* dtri, const void* left, const void* right, void* dleft, void* dright, int B,
+                                  int N, int direction, int* status, void* cuda_stream) {
+  if (!dtri || !left || !right || !dleft || !dright) return B200_TRIMUL_E_NULL;
+  int rc;
+  if (direction == B200_TRIMUL_OUTGOING) {
+    // t_ij = sum_k l_ik r_jk:  dl_ik = sum_j dt_ij r_jk (mixed),  dr_jk = sum_i dt_ij l_ik (the incoming form)
+    rc = contract_impl(dtri, right, dleft, nullptr, 0, 0, kC, B, N, 0, N, N, kDirMixed, status, cuda_stream);
+    if (rc != B200_TRIMUL_OK) return rc;
+    return contract_impl(dtri, left, dright, nullptr, 0, 0, kC, B, N, 0, N, N, B200_TRIMUL_INCOMING, status, cuda_stream);
+  }
+  if (direction == B200_TRIMUL_INCOMING) {
+    // t_ij = sum_k l_ki r_kj:  dl_ki = sum_j r_kj dt_ij (the outgoing form),  dr_kj = sum_i l_ki dt_ij (mixed)
+    rc = contract_impl(right, dtri, dleft, nullptr, 0, 0, kC, B, N, 0, N, N, B200_TRIMUL_OUTGOING, status, cuda_stream);
+    if (rc != B200_TRIMUL_OK) return rc;
+    return contract_impl(left, dtri, dright, nullptr, 0, 0, kC, B, N, 0, N, N, kDirMixed, status, cuda_stream);
+  }
+  return B200_TRIMUL_E_SHAPE;
 }
 
 int b200_trimul_contract_partial(const void* left, const void* right, void* tri_partial, int B, int N, int k_rows,

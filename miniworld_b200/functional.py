@@ -291,6 +291,24 @@ def contract(
     _lib.check(rc, "b200_trimul_contract")
 
 
+def contract_backward(
+    dtri: torch.Tensor, left: torch.Tensor, right: torch.Tensor, dleft: torch.Tensor, dright: torch.Tensor,
+    status: torch.Tensor, B: int, N: int, outgoing: bool,
+) -> None:
+    """Gradients of the contraction with respect to ``left`` and ``right`` (all [B, N, 128, N] fp16): ``dleft`` and
+    ``dright`` receive the sums times 2^-4, saturated, in whatever scale ``dtri`` carries."""
+    for name, t in (("dtri", dtri), ("left", left), ("right", right), ("dleft", dleft), ("dright", dright)):
+        _require_cuda(t, name)
+        if t.dtype != torch.float16 or tuple(t.shape) != (B, N, D, N) or not t.is_contiguous():
+            raise RuntimeError(f"{name} must be a contiguous fp16 [B, N, {D}, N] tensor, got {t.dtype} {tuple(t.shape)}")
+    with torch.cuda.device(dtri.device):
+        rc = _lib.load().b200_trimul_contract_backward(
+            _ptr(dtri), _ptr(left), _ptr(right), _ptr(dleft), _ptr(dright), B, N,
+            _lib.OUTGOING if outgoing else _lib.INCOMING, _ptr(status), _stream(dtri.device),
+        )
+    _lib.check(rc, "b200_trimul_contract_backward")
+
+
 def contract_partial(
     left: torch.Tensor, right: torch.Tensor, tri_partial: torch.Tensor, status: torch.Tensor, B: int, N: int, k_rows: int
 ) -> None:

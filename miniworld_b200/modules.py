@@ -214,14 +214,28 @@ class TriangleMultiplication(nn.Module):
             self._workspace = ws
         return ws
 
+    def _backward_supported(self) -> bool:
+        return not self._bidirectional and self.d_pair == D_SUPPORTED and self.d_hidden == D_SUPPORTED
+
     def _run(self, pair: torch.Tensor, token_mask, pair_mask) -> torch.Tensor:
-        if torch.is_grad_enabled() and pair.requires_grad:
-            raise NotImplementedError("backward is not implemented: call under torch.no_grad() or with an input that does not require grad")
+        # the differentiable path is taken when the input requires grad, or in training mode when a parameter does
+        train = torch.is_grad_enabled() and (
+            pair.requires_grad or (self.training and any(q.requires_grad for q in self.parameters()))
+        )
+        if train and not self._backward_supported():
+            if pair.requires_grad:
+                raise NotImplementedError(
+                    "backward is implemented for the unidirectional module with d_pair = d_hidden = 128 only: call under "
+                    "torch.no_grad() or with an input that does not require grad"
+                )
+            train = False
         if pair.dim() != 4 or pair.shape[1] != pair.shape[2] or pair.shape[3] != self.d_pair:
             raise RuntimeError(f"pair must be [B, N, N, {self.d_pair}], got {tuple(pair.shape)}")
         if not pair.is_cuda:
             raise RuntimeError("pair must be a CUDA tensor: this module has no CPU implementation")
         in_dtype = pair.dtype
+        if train:
+            return self._run_train(pair, token_mask, pair_mask)
         z = pair.detach()
         if z.dtype != torch.bfloat16:
             z = z.to(torch.bfloat16)
@@ -266,6 +280,37 @@ class TriangleMultiplication(nn.Module):
             )
         if pad:
             y = y[:, :N, :N].contiguous()
+        return y if in_dtype == torch.bfloat16 else y.to(in_dtype)
+
+    def _run_train(self, pair: torch.Tensor, token_mask, pair_mask) -> torch.Tensor:
+        """Differentiable forward (:mod:`miniworld_b200.training`): the stage tensors of this call are kept for the
+        backward in a workspace of their own; padding, cropping and dtype casts are ordinary differentiable ops."""
+        from .training import trimul_train
+
+        in_dtype = pair.dtype
+        z = pair if pair.dtype == torch.bfloat16 else pair.to(torch.bfloat16)
+        z = z.contiguous()
+        B, N = int(z.shape[0]), int(z.shape[1])
+        pad = (-N) % 8
+        scale = None
+        if self.training and self.p_drop > 0.0:
+            scale = self._make_drop_row_scale(z, self.p_drop).to(device=z.device, dtype=torch.bfloat16)
+            if pad:
+                scale = nn.functional.pad(scale, (0, 0, 0, pad))
+            scale = scale.contiguous()
+        if pad:
+            z = nn.functional.pad(z, (0, 0, 0, pad, 0, pad))
+            tm = torch.ones(B, N, dtype=torch.bool, device=z.device) if token_mask is None else token_mask.to(z.device) != 0
+            token_mask = nn.functional.pad(tm, (0, pad))
+            if pair_mask is not None:
+                pair_mask = nn.functional.pad(pair_mask.to(z.device) != 0, (0, pad, 0, pad))
+        y = trimul_train(
+            z, self._params(), token_mask, outgoing=self.outgoing, eps_in=float(self.ln_pair.eps),
+            eps_out=float(self.ln_out.eps), pair_mask=pair_mask, residual=self.residual, biases=self._biases,
+            drop_scale=scale, check=self.check_status,
+        )
+        if pad:
+            y = y[:, :N, :N]
         return y if in_dtype == torch.bfloat16 else y.to(in_dtype)
 
     def forward(self, pair: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:

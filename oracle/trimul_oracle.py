@@ -97,8 +97,14 @@ def trimul_forward_stages(
     round_intermediates: bool = False,
     k_chunk: int = 0,
     drop_scale: Optional[torch.Tensor] = None,
+    differentiable: bool = False,
 ) -> Stages:
     """fp32 forward of TriangleMultiplication, returning every stage.
+
+    ``differentiable`` keeps ``z`` and ``params`` attached to the autograd graph (they must then be fp32 leaves), so
+    that ``out.backward(dy)`` gives the oracle's gradients: autograd through this restatement is the backward oracle,
+    as the reference validates its backward against autograd through its PyTorch module
+    (``docs/archive/engine2-validation-20260923/validate_bidir_reference.py:30-34``).
 
     ``z`` [B,N,N,C] (any float dtype; computed in fp32), ``mask`` Bool[B,N] or None, ``pair_mask``
     [B,N,N] (non-zero = valid) or None.  ``params`` uses the reference's state_dict keys.
@@ -108,12 +114,13 @@ def trimul_forward_stages(
     residual is added, as the training path does (``scripts/check_trimul_module_reference.py:43,114-116``
     in the reference project: a zero scale returns the input exactly).
     """
-    p = {k: v.detach().to(torch.float32) for k, v in params.items()}
+    keep = (lambda v: v.to(torch.float32)) if differentiable else (lambda v: v.detach().to(torch.float32))
+    p = {k: keep(v) for k, v in params.items()}
     bz = {k: None for k in BIAS_KEYS}
     if biases:
         for k, v in biases.items():
             bz[k] = None if v is None else v.detach().to(torch.float32)
-    zf = z.detach().to(torch.float32)
+    zf = keep(z)
     B, N, N2, C = zf.shape
     assert N == N2
     H = p["to_left.weight"].shape[0]

@@ -97,6 +97,35 @@ def test_contract_matches_einsum(B, N, outgoing):
 
 
 @pytest.mark.parametrize("outgoing", [True, False])
+@pytest.mark.parametrize("B,N", [(2, 64), (1, 136), (1, 200), (1, 384), (1, 512)])
+def test_contract_backward_matches_einsum(B, N, outgoing):
+    """Gradients of the contraction with respect to both operands (one product with a K-major and an MN-major operand,
+    one in the other direction's form) against fp32 einsums, which is what autograd gives for the forward einsum."""
+    g = torch.Generator().manual_seed(150 + N)
+    left = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    right = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    dtri = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)
+    dleft, dright = _nan_f16(B, N, 128, N), _nan_f16(B, N, 128, N)
+    st = _status()
+    F_.contract_backward(dtri, left, right, dleft, dright, st, B, N, outgoing)
+    F_.check_status(st, "contract_backward")
+    lf, rf, df = left.float(), right.float(), dtri.float()
+    if outgoing:  # t[b,i,h,j] = sum_k l[b,i,h,k] r[b,j,h,k]
+        ref_l = torch.einsum("bihj,bjhk->bihk", df, rf)
+        ref_r = torch.einsum("bihj,bihk->bjhk", df, lf)
+    else:  # t[b,i,h,j] = sum_k l[b,k,h,i] r[b,k,h,j]
+        ref_l = torch.einsum("bihj,bkhj->bkhi", df, rf)
+        ref_r = torch.einsum("bihj,bkhi->bkhj", df, lf)
+    for name, got16, ref in (("dleft", dleft, ref_l), ("dright", dright, ref_r)):
+        got = got16.float() / TRI_SCALE
+        assert torch.isfinite(got).all(), name
+        assert oracle.rel_frobenius(got.cpu(), ref.cpu()) < 4e-4, name
+        err = (got - ref).abs()
+        tol = ref.abs() * 2**-10 + 2e-3
+        assert bool((err <= tol).all()), (name, float((err - tol).max()))
+
+
+@pytest.mark.parametrize("outgoing", [True, False])
 def test_contract_row_range(outgoing):
     """A row range of the output (what one rank of a row-sharded run computes) equals the slice of the full result."""
     B, N, r0, rows = 1, 192, 64, 72

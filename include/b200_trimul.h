@@ -290,6 +290,33 @@ int b200_trimul_forward_static(const void* z, const void* w_left, const void* w_
                                void* cuda_stream);
 
 /*
+ * Backward of the unidirectional module (d_pair = d_hidden = 128): the reference's training path, stages B1-B12 of
+ * docs/kernels/trimul/TRIMUL_STATUS.md:43-52 (its B5-B6, the contraction gradients, are cuBLAS calls there). Given
+ * dy = d loss / d y ([B, N, N, 128] bf16), the inputs of the forward call and the workspace that
+ * b200_trimul_forward / _forward_ex left behind for these inputs (it holds left, right and tri), it writes
+ *   dz  [B, N, N, 128] bf16          d loss / d z, the residual path included when `residual` is non-zero
+ *   dw[6] fp32 [128, 128] each       gradients of w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out (that order)
+ *   d_ln_in_w / _b, d_ln_out_w / _b  fp32 [128] each
+ * Every output is overwritten, not accumulated into. Biases are constants (no gradient). drop_scale as in the forward.
+ * Launches: weight packing, max |dy| and the power-of-two scale the fp16 gradient tiles carry, the epilogue's backward
+ * (one kernel: both LayerNorm-folded GEMMs recomputed, four gradient GEMMs on the tensor cores), the two contraction
+ * gradient launches, the prologue's backward once per side, partial-sum reductions, the parameter gradients.
+ * The result is deterministic (fixed summation order). Workspace: b200_trimul_backward_workspace_bytes, 1024-byte
+ * aligned; _layout gives its 11 region offsets + the total (status, packed weights, scale, reduced sums M and S, per-CTA
+ * partials of M and S, dtri, dleft, dright, d x_hat) for tests.
+ */
+int b200_trimul_backward_workspace_bytes(int B, int N, size_t* out_bytes);
+int b200_trimul_backward_workspace_layout(int B, int N, size_t* offsets12);
+int b200_trimul_backward(const void* dy, const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
+                         const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
+                         const float* ln_in_w, const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,
+                         const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask,
+                         const void* drop_scale, const void* forward_workspace, void* dz, void* const* dw,
+                         float* d_ln_in_w, float* d_ln_in_b, float* d_ln_out_w, float* d_ln_out_b, void* workspace,
+                         size_t workspace_bytes, int B, int N, int direction, float eps_in, float eps_out, int residual,
+                         void* cuda_stream);
+
+/*
  * Pair Transition, the operator on the other side of the triangle update in every block
  * (src/miniworld/modules/mini_pairformer.py:81-84,108 in the reference project; the engine's fused kernel is
  * `transition_fused_fwd_sm100a`, docs/phase2-b200-training-speed.md:165):

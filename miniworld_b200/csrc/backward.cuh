@@ -1,0 +1,873 @@
+// Backward of the triangle update around the contraction: the epilogue's gradients (output LayerNorm, output
+// projection, output gate) and the prologue's gradients (input LayerNorm, the four gated projections, the mask).
+//
+// Both kernels walk tiles of 128 consecutive columns j of one pair row, one CTA per SM, 256 threads: thread = one
+// position (its TMEM lane) and 64 of the 128 channels. A tile goes through a fixed sequence of phases separated by
+// CTA-wide barriers; one thread issues the TMA copies and the MMAs. Per tile:
+//   1. TMA loads of the tile's inputs; the LayerNorm inputs are normalised in place in shared memory (fp16),
+//   2. the forward GEMMs are recomputed on the tensor cores (weights with the LayerNorm gamma folded in, fp16),
+//   3. the threads turn the upstream gradient into the gradients of the GEMM outputs (fp16 tiles in shared memory),
+//   4. the tensor cores compute, from those tiles, the gradients with respect to the normalised inputs (the same weight
+//      tiles read MN-major) and accumulate the weight gradients M = dOut^T x_hat over all tiles of the CTA in TMEM,
+//   5. the threads finish (LayerNorm backward) and the results leave through TMA stores.
+// Column sums of the dOut tiles (the bias-like terms) are accumulated per thread in registers. At the end every CTA
+// writes its partial M and column sums; a small kernel adds the partials and forms the parameter gradients.
+//
+// Gradients travel in fp16 tiles, so the upstream gradient is multiplied by a power of two c (read from device
+// memory, chosen from max |dy| by `grad_scale_kernel`); every output of these kernels carries that factor, and the
+// final kernels divide it out in fp32.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace trimul {
+
+constexpr int kBwdThreads = 256;
+constexpr int kBwdTile = 32768;  // one [128][128] 16-bit tile
+constexpr int kBwdSmemBytes = 6 * kBwdTile + 4096 /* exchange */ + 1024 /* constants */ + 256 /* barriers */ + 1024;
+
+// swizzled byte offset of element (r, e) in a [128 rows][128 elements] 16-bit tile stored as two halves of 64 elements,
+// each [128 rows][128 bytes] with the 128-byte TMA swizzle
+__device__ __forceinline__ uint32_t tile_off(int r, int e) {
+  return static_cast<uint32_t>((e >> 6) * 16384 + r * 128 + ((((e & 63) >> 3) ^ (r & 7)) << 4) + (e & 7) * 2);
+}
+// offset of the 16-byte chunk holding elements 8*ch .. 8*ch+7 (ch = 0..15) of row r
+__device__ __forceinline__ uint32_t tile_chunk(int r, int ch) {
+  return static_cast<uint32_t>((ch >> 3) * 16384 + r * 128 + (((ch & 7) ^ (r & 7)) << 4));
+}
+
+__device__ __forceinline__ float ld_f16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ void st_f16_sat(uint32_t addr, float x) {
+  const uint16_t v = __half_as_ushort(__float2half_rn(fminf(fmaxf(x, -65504.f), 65504.f)));
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_chunk(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void st_chunk(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ float sigmoid_fast(float x) { return fmaf(tanh_approx(0.5f * x), 0.5f, 0.5f); }
+
+// CTA-wide bounded wait on an mbarrier: one lane per warp polls, the decision is shared by all 256 threads.
+__device__ __forceinline__ bool cta_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  const bool got = mbar_wait_warp(bar, parity, abort_flag, status, code);
+  return named_bar_and(1, kBwdThreads, got);
+}
+
+// Normalise the 128 channels of every position of a tile in place (fp16 result), the thread covering 64 of them.
+// ROWS_ARE_POSITIONS: element (pos, c) (a [pos][c] tile, input bf16 or fp16), else element (c, pos) (a [c][pos] tile,
+// fp16). Returns rstd of the thread's position. `xchg` holds float2 [2][128].
+template <bool ROWS_ARE_POSITIONS, bool IN_BF16>
+__device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, int pos, int half, float eps) {
+  float pv = 0.f, s1 = 0.f, s2 = 0.f;
+  if constexpr (ROWS_ARE_POSITIONS) {
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      const uint4 v = ld_chunk(tile + tile_chunk(pos, half * 8 + ch));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 x = IN_BF16 ? bf16x2_to_float2(w[t]) : f16x2_to_float2(w[t]);
+        if (ch == 0 && t == 0) pv = x.x;
+        const float d0 = x.x - pv, d1 = x.y - pv;
+        s1 += d0 + d1;
+        s2 = fmaf(d0, d0, fmaf(d1, d1, s2));
+      }
+    }
+  } else {
+#pragma unroll 8
+    for (int cc = 0; cc < 64; ++cc) {
+      const float x = ld_f16(tile + tile_off(half * 64 + cc, pos));
+      if (cc == 0) pv = x;
+      const float d = x - pv;
+      s1 += d;
+      s2 = fmaf(d, d, s2);
+    }
+  }
+  const float mean_h = pv + s1 * (1.0f / 64.0f);
+  const float m2_h = fmaxf(s2 - s1 * s1 * (1.0f / 64.0f), 0.f);
+  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (half * 128 + pos) * 8), "f"(mean_h), "f"(m2_h) : "memory");
+  named_bar_sync(1, kBwdThreads);
+  float ma, qa, mb, qb;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(ma), "=f"(qa) : "r"(xchg + pos * 8));
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(mb), "=f"(qb) : "r"(xchg + (128 + pos) * 8));
+  const float mean = 0.5f * (ma + mb);
+  const float dlt = ma - mb;
+  const float m2 = qa + qb + dlt * dlt * 32.0f;  // n_a n_b / (n_a + n_b) = 32
+  const float rstd = rsqrtf(m2 * (1.0f / 128.0f) + eps);
+  const float nmr = -mean * rstd;
+  if constexpr (ROWS_ARE_POSITIONS) {
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      const uint32_t addr = tile + tile_chunk(pos, half * 8 + ch);
+      const uint4 v = ld_chunk(addr);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 x = IN_BF16 ? bf16x2_to_float2(w[t]) : f16x2_to_float2(w[t]);
+        o[t] = pack_f16x2_sat(make_float2(fmaf(x.x, rstd, nmr), fmaf(x.y, rstd, nmr)));
+      }
+      st_chunk(addr, o[0], o[1], o[2], o[3]);
+    }
+  } else {
+#pragma unroll 8
+    for (int cc = 0; cc < 64; ++cc) {
+      const uint32_t addr = tile + tile_off(half * 64 + cc, pos);
+      st_f16_sat(addr, fmaf(ld_f16(addr), rstd, nmr));
+    }
+  }
+  named_bar_sync(1, kBwdThreads);  // the exchange buffer may be reused
+  return rstd;
+}
+
+// Sum the per-thread column partials of a CTA over its 128 positions: `acc` holds this thread's 64 channels (half
+// `half`) for two vectors; scratch is float[256][129] (a tile region, padded against bank conflicts).
+__device__ __forceinline__ void flush_colsums(const float (&a0)[64], const float (&a1)[64], uint8_t* scratch, int pos, int half,
+                                              float* out0, float* out1) {
+  float* s = reinterpret_cast<float*>(scratch);
+  // rows: (vector * 128 + channel), columns: position
+#pragma unroll
+  for (int c = 0; c < 64; ++c) {
+    s[(0 * 128 + half * 64 + c) * 129 + pos] = a0[c];
+    s[(1 * 128 + half * 64 + c) * 129 + pos] = a1[c];
+  }
+  __syncthreads();
+  const int r = threadIdx.x;  // 0..255: vector r / 128, channel r % 128
+  float sum = 0.f;
+  for (int p = 0; p < 128; ++p) sum += s[r * 129 + p];
+  (r < 128 ? out0 : out1)[r & 127] = sum;
+  __syncthreads();
+}
+
+struct BwdEpilogueParams {
+  int tiles_per_row;   // ceil(N / 128)
+  int num_tiles;       // B * N * tiles_per_row
+  int n;               // N
+  const float* consts;      // [2][128]: d_out = W_out beta_out + bias_out, d_gate = W_gate beta_in + bias_gate
+  const float* grad_scale;  // [2]: c, 1 / c
+  const uint16_t* drop_scale;  // [B][N][128] bf16 or null
+  float eps_in;
+  float eps_out;       // scaled by 2^-8: tri is stored times 2^-4
+  float* part_m;       // [grid][2][128][128]: per-CTA partial sums of dproj^T t_hat and dgate^T x_hat
+  float* part_s;       // [grid][2][128]: per-CTA column sums of dproj and dgate
+  int* status;
+};
+
+// Epilogue backward. Inputs: tri [B*N][128][N] fp16 (times 2^-4), z and dy [B*N][N][128] bf16. Outputs:
+//   dtri [B*N][128][N] fp16 = c * d loss / d t,  dxg [B*N][N][128] fp16 = c * (d loss / d x_hat through the output gate)
+// and the per-CTA partials. Shared memory: W_out' , W_gate' (fp16, gamma folded), then four tiles: t, z, dy, dgate.
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_z,
+                    const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_wo,
+                    const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ CUtensorMap map_dt,
+                    const __grid_constant__ CUtensorMap map_dx, const BwdEpilogueParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t wo_s = smem_base, wg_s = smem_base + kBwdTile;
+  const uint32_t t_s = smem_base + 2 * kBwdTile, z_s = t_s + kBwdTile, dy_s = z_s + kBwdTile, dg_s = dy_s + kBwdTile;
+  const uint32_t xchg = smem_base + 6 * kBwdTile;
+  const uint32_t const_s = xchg + 4096;
+  const uint32_t bar_base = const_s + 1024;
+  const uint32_t w_full = bar_base, in_full = bar_base + 8, mma_bar = bar_base + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + 4096 + 1024 + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + 4096);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = warp & 3, half = warp >> 2;
+  const int pos = q * 32 + lane;
+  const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+
+  if (threadIdx.x == 0) {
+    mbar_init(w_full, 1);
+    mbar_init(in_full, 1);
+    mbar_init(mma_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&map_t);
+    prefetch_tmap(&map_z);
+    prefetch_tmap(&map_dy);
+    prefetch_tmap(&map_dt);
+    prefetch_tmap(&map_dx);
+  }
+  const_ptr[threadIdx.x] = p.consts[threadIdx.x];
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const float gc = p.grad_scale[0];
+
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(w_full, 2 * kBwdTile);
+#pragma unroll
+    for (int kh = 0; kh < 2; ++kh) {
+      tma_load_2d(wo_s + kh * 16384, &map_wo, w_full, kh * 64, 0);
+      tma_load_2d(wg_s + kh * 16384, &map_wg, w_full, kh * 64, 0);
+    }
+  }
+  float acc_so[64], acc_sg[64];
+#pragma unroll
+  for (int c = 0; c < 64; ++c) acc_so[c] = 0.f, acc_sg[c] = 0.f;
+
+  bool ok = true;
+  int it = 0;
+  bool loads_pending = false;
+  for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+    const int row = tile / p.tiles_per_row;
+    const int j0 = (tile - row * p.tiles_per_row) * 128;
+    if (threadIdx.x == 0) {
+      mbar_arrive_expect_tx(in_full, 3 * kBwdTile);
+#pragma unroll
+      for (int kh = 0; kh < 2; ++kh) {
+        tma_load_3d(t_s + kh * 16384, &map_t, in_full, j0 + kh * 64, 0, row);
+        tma_load_3d(z_s + kh * 16384, &map_z, in_full, kh * 64, j0, row);
+        tma_load_3d(dy_s + kh * 16384, &map_dy, in_full, kh * 64, j0, row);
+      }
+      loads_pending = true;
+    }
+    if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
+    if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    loads_pending = false;
+    // ---- phase 1: normalise t (rows = channels) and z (rows = positions) in place
+    const float rstd_out = normalise_tile<false, false>(t_s, xchg, pos, half, p.eps_out);
+    normalise_tile<true, true>(z_s, xchg, pos, half, p.eps_in);
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // ---- phase 2: P = t_hat Wo'^T (columns 0-127), G = x_hat Wg'^T (columns 128-255)
+    if (threadIdx.x == 0) {
+      tc_fence_after();
+      constexpr uint32_t idesc_p = umma_idesc(128, 128, true, false, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_g = umma_idesc(128, 128, false, false, kFmtF16, kFmtF16);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+        umma_bf16(tmem_base, umma_desc_mnmajor(t_s + ks * 2048, 16384), umma_desc_kmajor(wo_s + (ks >> 2) * 16384) + kb,
+                  idesc_p, ks != 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+        umma_bf16(tmem_base + 128, umma_desc_kmajor(z_s + (ks >> 2) * 16384) + kb,
+                  umma_desc_kmajor(wg_s + (ks >> 2) * 16384) + kb, idesc_g, ks != 0 ? 1u : 0u);
+      }
+      umma_commit(mma_bar);
+    }
+    if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
+    tc_fence_after();
+    // ---- phase 3: dproj = c du gate, dgate = c du proj gate (1 - gate); du = dy (* dropout scale)
+    {
+      const int j = j0 + pos;
+      const uint4* sc = nullptr;
+      if (p.drop_scale != nullptr && j < p.n) {
+        const int b = row / p.n;
+        sc = reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * 128 + half * 64);
+      }
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t vp[8], vg[8];
+        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, vp);
+        tmem_ld8(tmem_base + lane_sel + 128 + half * 64 + ch * 8, vg);
+        const uint32_t addr = tile_chunk(pos, half * 8 + ch);
+        const uint4 dyv = ld_chunk(dy_s + addr);
+        uint4 scv = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);  // bf16 ones
+        if (sc != nullptr) scv = __ldg(sc + ch);
+        tmem_ld_wait();
+        const uint32_t dw[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
+        const uint32_t sw[4] = {scv.x, scv.y, scv.z, scv.w};
+        uint32_t op[4], og[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 d2 = bf16x2_to_float2(dw[t]);
+          const float2 s2 = bf16x2_to_float2(sw[t]);
+          float dpv[2], dgv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int c = half * 64 + ch * 8 + t * 2 + e;
+            const float proj = __uint_as_float(vp[t * 2 + e]) + const_ptr[c];
+            const float gate = sigmoid_fast(__uint_as_float(vg[t * 2 + e]) + const_ptr[128 + c]);
+            const float du = (e == 0 ? d2.x * s2.x : d2.y * s2.y) * gc;
+            dpv[e] = du * gate;
+            dgv[e] = du * proj * gate * (1.0f - gate);
+            acc_so[ch * 8 + t * 2 + e] += dpv[e];
+            acc_sg[ch * 8 + t * 2 + e] += dgv[e];
+          }
+          op[t] = pack_f16x2_sat(make_float2(dpv[0], dpv[1]));
+          og[t] = pack_f16x2_sat(make_float2(dgv[0], dgv[1]));
+        }
+        st_chunk(dy_s + addr, op[0], op[1], op[2], op[3]);
+        st_chunk(dg_s + addr, og[0], og[1], og[2], og[3]);
+      }
+    }
+    tc_fence_before();
+    fence_proxy_async_smem();
+    __syncthreads();
+    // ---- phase 4: dt_hat = dproj Wo' (0-127), dxg = dgate Wg' (128-255); Mo += dproj^T t_hat (256-383),
+    //      Mg += dgate^T x_hat (384-511)
+    if (threadIdx.x == 0) {
+      tc_fence_after();
+      constexpr uint32_t idesc_d = umma_idesc(128, 128, false, true, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_mo = umma_idesc(128, 128, true, false, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_mg = umma_idesc(128, 128, true, true, kFmtF16, kFmtF16);
+      const uint32_t accum = it != 0 ? 1u : 0u;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+        umma_bf16(tmem_base, umma_desc_kmajor(dy_s + (ks >> 2) * 16384) + kb, umma_desc_mnmajor(wo_s + ks * 2048, 16384),
+                  idesc_d, ks != 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+        umma_bf16(tmem_base + 128, umma_desc_kmajor(dg_s + (ks >> 2) * 16384) + kb,
+                  umma_desc_mnmajor(wg_s + ks * 2048, 16384), idesc_d, ks != 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+        umma_bf16(tmem_base + 256, umma_desc_mnmajor(dy_s + ks * 2048, 16384),
+                  umma_desc_kmajor(t_s + (ks >> 2) * 16384) + kb, idesc_mo, (ks != 0 ? 1u : 0u) | accum);
+      }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        umma_bf16(tmem_base + 384, umma_desc_mnmajor(dg_s + ks * 2048, 16384), umma_desc_mnmajor(z_s + ks * 2048, 16384),
+                  idesc_mg, (ks != 0 ? 1u : 0u) | accum);
+      }
+      umma_commit(mma_bar);
+    }
+    if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
+    tc_fence_after();
+    // ---- phase 5: LayerNorm backward of the output normalisation, in place over t_hat; dxg over x_hat
+    {
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t v[8];
+        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float d = __uint_as_float(v[e]);
+          s1 += d;
+          s2 = fmaf(d, ld_f16(t_s + tile_off(half * 64 + ch * 8 + e, pos)), s2);
+        }
+      }
+      asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (half * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
+      named_bar_sync(1, kBwdThreads);
+      float a1, a2, b1, b2;
+      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a1), "=f"(a2) : "r"(xchg + pos * 8));
+      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(b1), "=f"(b2) : "r"(xchg + (128 + pos) * 8));
+      const float m1 = (a1 + b1) * (1.0f / 128.0f), m2 = (a2 + b2) * (1.0f / 128.0f);
+      const float rs = rstd_out * 0.0625f;  // d / d t of the stored t / 16
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t v[8], x[8];
+        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, v);
+        tmem_ld8(tmem_base + lane_sel + 128 + half * 64 + ch * 8, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const uint32_t addr = t_s + tile_off(half * 64 + ch * 8 + e, pos);
+          st_f16_sat(addr, rs * (__uint_as_float(v[e]) - m1 - ld_f16(addr) * m2));
+        }
+        st_chunk(z_s + tile_chunk(pos, half * 8 + ch),
+                 pack_f16x2_sat(make_float2(__uint_as_float(x[0]), __uint_as_float(x[1]))),
+                 pack_f16x2_sat(make_float2(__uint_as_float(x[2]), __uint_as_float(x[3]))),
+                 pack_f16x2_sat(make_float2(__uint_as_float(x[4]), __uint_as_float(x[5]))),
+                 pack_f16x2_sat(make_float2(__uint_as_float(x[6]), __uint_as_float(x[7]))));
+      }
+    }
+    tc_fence_before();
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+      for (int kh = 0; kh < 2; ++kh) {
+        if (j0 + kh * 64 < p.n) tma_store_3d(&map_dt, t_s + kh * 16384, j0 + kh * 64, 0, row);
+        tma_store_3d(&map_dx, z_s + kh * 16384, kh * 64, j0, row);
+      }
+      bulk_commit();
+      bulk_wait_read<0>();
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (loads_pending) {  // a wait gave up with copies in flight: they must land before the CTA exits
+      const long long t0 = clock64();
+      while (!mbar_try_wait(in_full, it & 1) || !mbar_try_wait(w_full, 0)) {
+        if (clock64() - t0 > kWaitLimitCycles) {
+          atomicCAS(p.status, 0, kDevTimeoutDrain);
+          break;
+        }
+      }
+    }
+    bulk_wait<0>();
+  }
+  __syncthreads();
+  if (ok && it > 0) {
+    // weight-gradient accumulators: lane = output row of the matrix, this thread's 64 columns
+    tc_fence_after();
+    float* pm = p.part_m + static_cast<size_t>(blockIdx.x) * 2 * 128 * 128;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t v[8];
+        tmem_ld8(tmem_base + lane_sel + 256 + m * 128 + half * 64 + ch * 8, v);
+        tmem_ld_wait();
+        float4* dst = reinterpret_cast<float4*>(pm + (m * 128 + pos) * 128 + half * 64 + ch * 8);
+        dst[0] = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]), __uint_as_float(v[3]));
+        dst[1] = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]), __uint_as_float(v[6]), __uint_as_float(v[7]));
+      }
+    }
+  }
+  {
+    float* ps = p.part_s + static_cast<size_t>(blockIdx.x) * 2 * 128;
+    flush_colsums(acc_so, acc_sg, smem, pos, half, ps, ps + 128);  // every tile region is free by now
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+struct BwdPrologueParams {
+  int tiles_per_row;
+  int num_tiles;
+  int n;
+  const float* consts;        // [2][128]: d_value = W beta_in + bias, d_gate likewise (this side's two matrices)
+  const float* grad_scale;    // [2]: c, 1 / c
+  const uint8_t* token_mask;  // [B][N] or null
+  const uint8_t* pair_mask;   // [B][N][N] or null
+  const uint16_t* dx_in;      // [B*N][N][128] fp16: c * d loss / d x_hat gathered so far (read)
+  const uint16_t* dy;         // LAST only: upstream gradient [B*N][N][128] bf16 (the residual path), or null
+  float eps_in;
+  float* part_m;              // [grid][2][128][128]: partial dvalue^T x_hat, dgate^T x_hat
+  float* part_s;              // [grid][2][128]
+  int* status;
+};
+
+// Prologue backward for one side (left or right). Inputs: z [B*N][N][128] bf16, dO = the contraction's gradient for
+// this side [B*N][128][N] fp16 (times c / 16). It recomputes value / gate, forms dvalue = dO sig m, dgate = dO value
+// sig (1 - sig) m, adds dvalue W_v' + dgate W_g' to the running d x_hat, and accumulates the two weight gradients.
+// !LAST: the running d x_hat (fp16, times c) is written back through map_out. LAST: the input LayerNorm's backward
+// and the residual finish d loss / d z (bf16, unscaled) through map_out.
+template <bool LAST>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_do,
+                    const __grid_constant__ CUtensorMap map_wv, const __grid_constant__ CUtensorMap map_wg,
+                    const __grid_constant__ CUtensorMap map_out, const BwdPrologueParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t wv_s = smem_base, wg_s = smem_base + kBwdTile;
+  const uint32_t z_s = smem_base + 2 * kBwdTile, do_s = z_s + kBwdTile, dv_s = do_s + kBwdTile, dg_s = dv_s + kBwdTile;
+  const uint32_t xchg = smem_base + 6 * kBwdTile;
+  const uint32_t const_s = xchg + 4096;
+  const uint32_t bar_base = const_s + 1024;
+  const uint32_t w_full = bar_base, in_full = bar_base + 8, mma_bar = bar_base + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + 4096 + 1024 + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + 4096);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = warp & 3, half = warp >> 2;
+  const int pos = q * 32 + lane;
+  const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+
+  if (threadIdx.x == 0) {
+    mbar_init(w_full, 1);
+    mbar_init(in_full, 1);
+    mbar_init(mma_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&map_z);
+    prefetch_tmap(&map_do);
+    prefetch_tmap(&map_out);
+  }
+  const_ptr[threadIdx.x] = p.consts[threadIdx.x];
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const float gc_inv = p.grad_scale[1];
+
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(w_full, 2 * kBwdTile);
+#pragma unroll
+    for (int kh = 0; kh < 2; ++kh) {
+      tma_load_2d(wv_s + kh * 16384, &map_wv, w_full, kh * 64, 0);
+      tma_load_2d(wg_s + kh * 16384, &map_wg, w_full, kh * 64, 0);
+    }
+  }
+  float acc_sv[64], acc_sg[64];
+#pragma unroll
+  for (int c = 0; c < 64; ++c) acc_sv[c] = 0.f, acc_sg[c] = 0.f;
+
+  bool ok = true;
+  int it = 0;
+  bool loads_pending = false;
+  for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+    const int row = tile / p.tiles_per_row;
+    const int j0 = (tile - row * p.tiles_per_row) * 128;
+    if (threadIdx.x == 0) {
+      mbar_arrive_expect_tx(in_full, 2 * kBwdTile);
+#pragma unroll
+      for (int kh = 0; kh < 2; ++kh) {
+        tma_load_3d(z_s + kh * 16384, &map_z, in_full, kh * 64, j0, row);
+        tma_load_3d(do_s + kh * 16384, &map_do, in_full, j0 + kh * 64, 0, row);
+      }
+      loads_pending = true;
+    }
+    if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
+    if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    loads_pending = false;
+    // ---- phase 1: x_hat in place
+    const float rstd_in = normalise_tile<true, true>(z_s, xchg, pos, half, p.eps_in);
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // ---- phase 2: value = x_hat Wv'^T (columns 0-127), gate = x_hat Wg'^T (128-255)
+    if (threadIdx.x == 0) {
+      tc_fence_after();
+      constexpr uint32_t idesc = umma_idesc(128, 128, false, false, kFmtF16, kFmtF16);
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+          umma_bf16(tmem_base + m * 128, umma_desc_kmajor(z_s + (ks >> 2) * 16384) + kb,
+                    umma_desc_kmajor((m == 0 ? wv_s : wg_s) + (ks >> 2) * 16384) + kb, idesc, ks != 0 ? 1u : 0u);
+        }
+      }
+      umma_commit(mma_bar);
+    }
+    if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
+    tc_fence_after();
+    // ---- phase 3: dvalue, dgate for this thread's position and 64 contracted channels
+    const int j = j0 + pos;
+    {
+      const int b = row / p.n;
+      const int i = row - b * p.n;
+      bool valid = j < p.n;
+      if (valid && p.token_mask != nullptr)
+        valid = p.token_mask[static_cast<size_t>(b) * p.n + i] != 0 && p.token_mask[static_cast<size_t>(b) * p.n + j] != 0;
+      if (valid && p.pair_mask != nullptr) valid = p.pair_mask[(static_cast<size_t>(b) * p.n + i) * p.n + j] != 0;
+      const float vm = valid ? 16.0f : 0.f;  // the contraction's outputs are stored times 2^-4
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t vv[8], vg[8];
+        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, vv);
+        tmem_ld8(tmem_base + lane_sel + 128 + half * 64 + ch * 8, vg);
+        tmem_ld_wait();
+        float dvv[8], dgv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int h = half * 64 + ch * 8 + e;
+          const float val = __uint_as_float(vv[e]) + const_ptr[h];
+          const float sg = sigmoid_fast(__uint_as_float(vg[e]) + const_ptr[128 + h]);
+          const float d_o = ld_f16(do_s + tile_off(h, pos)) * vm;
+          dvv[e] = d_o * sg;
+          dgv[e] = d_o * val * sg * (1.0f - sg);
+          acc_sv[ch * 8 + e] += dvv[e];
+          acc_sg[ch * 8 + e] += dgv[e];
+        }
+        const uint32_t addr = tile_chunk(pos, half * 8 + ch);
+        st_chunk(dv_s + addr, pack_f16x2_sat(make_float2(dvv[0], dvv[1])), pack_f16x2_sat(make_float2(dvv[2], dvv[3])),
+                 pack_f16x2_sat(make_float2(dvv[4], dvv[5])), pack_f16x2_sat(make_float2(dvv[6], dvv[7])));
+        st_chunk(dg_s + addr, pack_f16x2_sat(make_float2(dgv[0], dgv[1])), pack_f16x2_sat(make_float2(dgv[2], dgv[3])),
+                 pack_f16x2_sat(make_float2(dgv[4], dgv[5])), pack_f16x2_sat(make_float2(dgv[6], dgv[7])));
+      }
+    }
+    tc_fence_before();
+    fence_proxy_async_smem();
+    __syncthreads();
+    // ---- phase 4: d x_hat = dvalue Wv' + dgate Wg' (columns 0-127); Mv += dvalue^T x_hat (256-383), Mg += dgate^T x_hat
+    if (threadIdx.x == 0) {
+      tc_fence_after();
+      constexpr uint32_t idesc_d = umma_idesc(128, 128, false, true, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_m = umma_idesc(128, 128, true, true, kFmtF16, kFmtF16);
+      const uint32_t accum = it != 0 ? 1u : 0u;
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+          umma_bf16(tmem_base, umma_desc_kmajor((m == 0 ? dv_s : dg_s) + (ks >> 2) * 16384) + kb,
+                    umma_desc_mnmajor((m == 0 ? wv_s : wg_s) + ks * 2048, 16384), idesc_d, (m | ks) != 0 ? 1u : 0u);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          umma_bf16(tmem_base + 256 + m * 128, umma_desc_mnmajor((m == 0 ? dv_s : dg_s) + ks * 2048, 16384),
+                    umma_desc_mnmajor(z_s + ks * 2048, 16384), idesc_m, (ks != 0 ? 1u : 0u) | accum);
+        }
+      }
+      umma_commit(mma_bar);
+    }
+    if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
+    tc_fence_after();
+    // ---- phase 5: add the running d x_hat; !LAST: write it back, LAST: LayerNorm backward + residual -> dz
+    {
+      const bool inside = j < p.n;
+      const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * 128 + half * 64);
+      float tot[64];
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t v[8];
+        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, v);
+        uint4 in = make_uint4(0u, 0u, 0u, 0u);
+        if (inside) in = __ldg(src + ch);
+        uint4 xh = make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (LAST) xh = ld_chunk(z_s + tile_chunk(pos, half * 8 + ch));
+        tmem_ld_wait();
+        const uint32_t iw[4] = {in.x, in.y, in.z, in.w};
+        const uint32_t xw[4] = {xh.x, xh.y, xh.z, xh.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 a = f16x2_to_float2(iw[t]);
+          const float t0 = __uint_as_float(v[2 * t]) + a.x, t1 = __uint_as_float(v[2 * t + 1]) + a.y;
+          tot[ch * 8 + 2 * t] = t0;
+          tot[ch * 8 + 2 * t + 1] = t1;
+          if constexpr (LAST) {
+            const float2 x = f16x2_to_float2(xw[t]);
+            s1 += t0 + t1;
+            s2 = fmaf(t0, x.x, fmaf(t1, x.y, s2));
+          }
+        }
+      }
+      if constexpr (!LAST) {
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          st_chunk(dv_s + tile_chunk(pos, half * 8 + ch), pack_f16x2_sat(make_float2(tot[ch * 8], tot[ch * 8 + 1])),
+                   pack_f16x2_sat(make_float2(tot[ch * 8 + 2], tot[ch * 8 + 3])),
+                   pack_f16x2_sat(make_float2(tot[ch * 8 + 4], tot[ch * 8 + 5])),
+                   pack_f16x2_sat(make_float2(tot[ch * 8 + 6], tot[ch * 8 + 7])));
+      } else {
+        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (half * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
+        named_bar_sync(1, kBwdThreads);
+        float a1, a2, b1, b2;
+        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a1), "=f"(a2) : "r"(xchg + pos * 8));
+        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(b1), "=f"(b2) : "r"(xchg + (128 + pos) * 8));
+        const float m1 = (a1 + b1) * (1.0f / 128.0f), m2 = (a2 + b2) * (1.0f / 128.0f);
+        const float rs = rstd_in * gc_inv;
+        const uint4* dyp = p.dy == nullptr ? nullptr
+                                           : reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * 128 + half * 64);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint4 xh = ld_chunk(z_s + tile_chunk(pos, half * 8 + ch));
+          uint4 dyv = make_uint4(0u, 0u, 0u, 0u);
+          if (dyp != nullptr && inside) dyv = __ldg(dyp + ch);
+          const uint32_t xw[4] = {xh.x, xh.y, xh.z, xh.w};
+          const uint32_t dw[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 x = f16x2_to_float2(xw[t]);
+            const float2 r = bf16x2_to_float2(dw[t]);
+            o[t] = pack_bf16x2(fmaf(rs, tot[ch * 8 + 2 * t] - m1 - x.x * m2, r.x),
+                               fmaf(rs, tot[ch * 8 + 2 * t + 1] - m1 - x.y * m2, r.y));
+          }
+          st_chunk(dv_s + tile_chunk(pos, half * 8 + ch), o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+    tc_fence_before();
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+      for (int kh = 0; kh < 2; ++kh) tma_store_3d(&map_out, dv_s + kh * 16384, kh * 64, j0, row);
+      bulk_commit();
+      bulk_wait_read<0>();
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (loads_pending) {
+      const long long t0 = clock64();
+      while (!mbar_try_wait(in_full, it & 1) || !mbar_try_wait(w_full, 0)) {
+        if (clock64() - t0 > kWaitLimitCycles) {
+          atomicCAS(p.status, 0, kDevTimeoutDrain);
+          break;
+        }
+      }
+    }
+    bulk_wait<0>();
+  }
+  __syncthreads();
+  if (ok && it > 0) {
+    tc_fence_after();
+    float* pm = p.part_m + static_cast<size_t>(blockIdx.x) * 2 * 128 * 128;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t v[8];
+        tmem_ld8(tmem_base + lane_sel + 256 + m * 128 + half * 64 + ch * 8, v);
+        tmem_ld_wait();
+        float4* dst = reinterpret_cast<float4*>(pm + (m * 128 + pos) * 128 + half * 64 + ch * 8);
+        dst[0] = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]), __uint_as_float(v[3]));
+        dst[1] = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]), __uint_as_float(v[6]), __uint_as_float(v[7]));
+      }
+    }
+  }
+  {
+    float* ps = p.part_s + static_cast<size_t>(blockIdx.x) * 2 * 128;
+    flush_colsums(acc_sv, acc_sg, smem, pos, half, ps, ps + 128);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ small kernels
+// Largest |dy| (bf16) as the bits of a non-negative float: `amax_bits` must be zero before the launch.
+__global__ void __launch_bounds__(256) bwd_amax_kernel(const uint4* dy, size_t n_chunks, unsigned int* amax_bits) {
+  float m = 0.f;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n_chunks;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const uint4 v = __ldg(dy + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 x = bf16x2_to_float2(w[t]);
+      m = fmaxf(m, fmaxf(fabsf(x.x), fabsf(x.y)));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+  if ((threadIdx.x & 31) == 0 && m > 0.f && m <= 3.0e38f) atomicMax(amax_bits, __float_as_uint(m));
+}
+// scale[0] = c = the power of two that brings max |dy| into [8, 16), scale[1] = 1 / c (c = 1 for a zero gradient)
+__global__ void bwd_scale_kernel(const unsigned int* amax_bits, float* scale) {
+  const float amax = __uint_as_float(*amax_bits);
+  float c = 1.0f;
+  if (amax > 0.f) {
+    int e = 0;
+    frexpf(amax, &e);           // amax = f * 2^e, f in [0.5, 1)
+    e = 4 - e;                  // amax * 2^(4 - e) in [8, 16)
+    e = e > 100 ? 100 : (e < -100 ? -100 : e);
+    c = ldexpf(1.0f, e);
+  }
+  scale[0] = c;
+  scale[1] = 1.0f / c;
+}
+
+// Weights for the backward kernels: all six matrices (PackArgs order: left, left gate, right, right gate, out, gate)
+// as dense fp16 [128][128] with the LayerNorm gamma of their input folded in, W'[r][k] = W[r][k] gamma[k], and
+// d[m][r] = sum_k W[r][k] beta[k] + bias[m][r] (fp32) behind them. One warp per matrix row.
+constexpr size_t kBwdPackedD = 6 * 32768;
+constexpr size_t kBwdPackedBytes = kBwdPackedD + 3072;  // 199680, a multiple of 1024
+__global__ void __launch_bounds__(128) bwd_pack_kernel(const PackArgs a, uint8_t* packed) {
+  const int gw = blockIdx.x * 4 + (threadIdx.x >> 5);  // 0 .. 767
+  const int lane = threadIdx.x & 31;
+  const int m = gw >> 7, row = gw & 127;
+  const float* gamma = (m == 4) ? a.ln_out_w : a.ln_in_w;
+  const float* beta = (m == 4) ? a.ln_out_b : a.ln_in_b;
+  float w[4];
+  if (a.f32_weights) {
+    const float4 v = reinterpret_cast<const float4*>(static_cast<const float*>(a.w[m]) + static_cast<size_t>(row) * a.ld[m])[lane];
+    w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+  } else {
+    const uint2 v = reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(a.w[m]) + static_cast<size_t>(row) * a.ld[m])[lane];
+    w[0] = bf16_lo(v.x), w[1] = bf16_hi(v.x), w[2] = bf16_lo(v.y), w[3] = bf16_hi(v.y);
+  }
+  const float4 g = reinterpret_cast<const float4*>(gamma)[lane];
+  const float4 b = reinterpret_cast<const float4*>(beta)[lane];
+  const float gg[4] = {g.x, g.y, g.z, g.w}, bb[4] = {b.x, b.y, b.z, b.w};
+  float d = 0.f;
+  uint16_t o[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    o[t] = __half_as_ushort(__float2half_rn(fminf(fmaxf(w[t] * gg[t], -65504.f), 65504.f)));
+    d = fmaf(w[t], bb[t], d);
+  }
+  uint2 ov;
+  ov.x = static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 16);
+  ov.y = static_cast<uint32_t>(o[2]) | (static_cast<uint32_t>(o[3]) << 16);
+  reinterpret_cast<uint2*>(packed + static_cast<size_t>(m) * 32768)[row * 32 + lane] = ov;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
+  if (lane == 0)
+    reinterpret_cast<float*>(packed + kBwdPackedD)[m * 128 + row] = d + (a.bias[m] != nullptr ? a.bias[m][row] : 0.f);
+}
+
+// out[e] = sum over the CTAs' partials, in CTA order (deterministic)
+__global__ void __launch_bounds__(256) bwd_reduce_kernel(const float* parts, int n_parts, size_t stride, float* out, int count) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= count) return;
+  float s = 0.f;
+  for (int i = 0; i < n_parts; ++i) s += parts[static_cast<size_t>(i) * stride + e];
+  out[e] = s;
+}
+
+// Parameter gradients from the reduced sums M[m] = dOut_m^T x_hat (times c) and S[m] = column sums of dOut_m (times c):
+//   dW_m[r][k] = (M[m][r][k] gamma[k] + S[m][r] beta[k]) / c
+//   dgamma[k]  = sum_m sum_r W_m[r][k] M[m][r][k] / c,   dbeta[k] = sum_m sum_r W_m[r][k] S[m][r] / c
+// over the matrices that read that LayerNorm (the output one: matrix 4; the input one: the other five).
+// One block of 128 threads, thread = column k; the sums run in a fixed order.
+struct BwdFinalArgs {
+  PackArgs w;           // raw weights and LayerNorm parameters
+  const float* m_all;   // [6][128][128]
+  const float* s_all;   // [6][128]
+  const float* scale;   // [2]
+  float* dw[6];         // [128][128] fp32 each
+  float* d_ln_in_w;
+  float* d_ln_in_b;
+  float* d_ln_out_w;
+  float* d_ln_out_b;
+};
+__global__ void __launch_bounds__(128) bwd_finalize_kernel(const BwdFinalArgs a) {
+  const int k = threadIdx.x;
+  const float cinv = a.scale[1];
+  float g_in = 0.f, b_in = 0.f, g_out = 0.f, b_out = 0.f;
+  for (int m = 0; m < 6; ++m) {
+    const float gamma = (m == 4 ? a.w.ln_out_w : a.w.ln_in_w)[k];
+    const float beta = (m == 4 ? a.w.ln_out_b : a.w.ln_in_b)[k];
+    float ag = 0.f, ab = 0.f;
+    for (int r = 0; r < 128; ++r) {
+      const size_t wi = static_cast<size_t>(r) * a.w.ld[m] + k;
+      const float w = a.w.f32_weights ? static_cast<const float*>(a.w.w[m])[wi]
+                                      : __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(a.w.w[m])[wi]) << 16);
+      const float mv = a.m_all[(m * 128 + r) * 128 + k] * cinv;
+      const float sv = a.s_all[m * 128 + r] * cinv;
+      a.dw[m][r * 128 + k] = fmaf(mv, gamma, sv * beta);
+      ag = fmaf(w, mv, ag);
+      ab = fmaf(w, sv, ab);
+    }
+    if (m == 4) g_out += ag, b_out += ab;
+    else g_in += ag, b_in += ab;
+  }
+  a.d_ln_in_w[k] = g_in;
+  a.d_ln_in_b[k] = b_in;
+  a.d_ln_out_w[k] = g_out;
+  a.d_ln_out_b[k] = b_out;
+}
+
+}  // namespace trimul

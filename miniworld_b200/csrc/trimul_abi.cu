@@ -371,6 +371,8 @@ static int launch_contract_pair(const CUtensorMap& ma, const CUtensorMap& mb, co
 
 }  // namespace trimul
 
+#include "backward.cuh"  // after PackArgs
+
 using namespace trimul;
 
 extern "C" {
@@ -1274,3 +1276,5 @@ extern "C" int b200_trimul_forward_static(const void* z, const void* w_left, con
                              kStaticWorkspaceBytes, B, N, d_pair, d_hidden, direction, eps_in, eps_out, residual,
                              cuda_stream);
 }
+
+#include "backward_host.inc"

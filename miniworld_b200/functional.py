@@ -517,6 +517,78 @@ def trimul_forward(
     return out
 
 
+def backward_workspace_bytes(B: int, N: int) -> int:
+    out = c_size_t(0)
+    _lib.check(_lib.load().b200_trimul_backward_workspace_bytes(B, N, ctypes.byref(out)), "b200_trimul_backward_workspace_bytes")
+    return int(out.value)
+
+
+def trimul_backward(
+    dy: torch.Tensor,
+    z: torch.Tensor,
+    params: dict,
+    forward_workspace: torch.Tensor,
+    mask: Optional[torch.Tensor] = None,
+    *,
+    outgoing: bool = True,
+    eps_in: float = 1e-5,
+    eps_out: float = 1e-5,
+    pair_mask: Optional[torch.Tensor] = None,
+    residual: bool = True,
+    biases: Optional[dict] = None,
+    drop_scale: Optional[torch.Tensor] = None,
+    workspace: Optional[torch.Tensor] = None,
+    check: bool = False,
+):
+    """Backward of :func:`trimul_forward` for the unidirectional module (``b200_trimul_backward``).
+
+    ``forward_workspace`` is the workspace the forward call used for the same inputs (it holds ``left``, ``right``,
+    ``tri``). Returns ``(dz bf16 [B,N,N,128], grads)`` with ``grads`` a dict of fp32 tensors under the parameter keys.
+    """
+    B, N = _check_z(z)
+    if z.shape[1] != N:
+        raise RuntimeError(f"pair tensor must be square in its token dims, got {tuple(z.shape)}")
+    dev = z.device
+    _require_cuda(dy, "dy")
+    if dy.dtype != torch.bfloat16 or tuple(dy.shape) != tuple(z.shape):
+        raise RuntimeError(f"dy must be bf16 of the input's shape {tuple(z.shape)}, got {dy.dtype} {tuple(dy.shape)}")
+    dy = dy.contiguous()
+    if not z.is_contiguous():
+        raise RuntimeError("the pair tensor must be contiguous")
+    w = _Weights(params, biases, dev)
+    ds = None
+    if drop_scale is not None:
+        if drop_scale.numel() != B * N * D or drop_scale.shape[-1] != D or drop_scale.shape[0] != B:
+            raise RuntimeError(f"drop_scale must be [B, 1, N, {D}], got {tuple(drop_scale.shape)}")
+        ds = drop_scale.detach().to(device=dev, dtype=torch.bfloat16).contiguous()
+    need = backward_workspace_bytes(B, N)
+    if workspace is None:
+        workspace = aligned_empty(need, dev)
+    elif workspace.numel() * workspace.element_size() < need:
+        raise RuntimeError(f"workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
+    if forward_workspace.numel() * forward_workspace.element_size() < workspace_bytes(B, N, outgoing):
+        raise RuntimeError("forward_workspace is smaller than the forward's workspace for this shape")
+    tm = as_mask_u8(mask, dev)
+    pm = as_mask_u8(pair_mask, dev)
+    dz = torch.empty_like(z)
+    dws = [torch.empty(D, D, dtype=torch.float32, device=dev) for _ in range(6)]
+    dln = [torch.empty(D, dtype=torch.float32, device=dev) for _ in range(4)]
+    dw_arr = (c_void_p * 6)(*[t.data_ptr() for t in dws])
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200_trimul_backward(
+            _ptr(dy), _ptr(z), *[_ptr(t) for t in w.weights], w.dtype_code, *[_ptr(t) for t in w.lns], w.bias_array,
+            _ptr(tm), _ptr(pm), _ptr(ds), _ptr(forward_workspace), _ptr(dz), dw_arr, *[_ptr(t) for t in dln],
+            _ptr(workspace), workspace.numel() * workspace.element_size(), B, N, _direction(outgoing), float(eps_in),
+            float(eps_out), int(bool(residual)), _stream(dev),
+        )
+    _lib.check(rc, "b200_trimul_backward")
+    if check:
+        check_status(workspace[:4].view(torch.int32), "b200_trimul_backward")
+    grads = dict(zip(WEIGHT_KEYS, dws))
+    grads.update(zip(LN_KEYS, dln))
+    return dz, grads
+
+
 # ------------------------------------------------------------------------------------------ pair Transition
 TRANSITION_KEYS = ("ln_in.weight", "ln_in.bias", "expand_a.weight", "expand_b.weight", "squeeze.weight")
 

@@ -94,3 +94,80 @@ def test_module_training_step_with_dropout_padding_and_no_residual():
     # evaluation mode with an input that does not require grad: the plain forward, nothing kept
     y3 = m.eval()(z.to(DEV), mask.to(DEV))
     assert not y3.requires_grad
+
+
+def test_biases_pair_mask_fp32_masters_and_determinism():
+    """fp32 master weights, gate / output / projection biases (constants: no gradient), a pair mask on top of the token
+    mask, through the functional entry point; a second backward on the same inputs is bit-identical (fixed summation
+    order, no atomics)."""
+    from miniworld_b200 import functional as F_
+
+    N = 104
+    p = {k: v.float() for k, v in rand_params(530).items()}
+    g = torch.Generator().manual_seed(531)
+    z = torch.randn(2, N, N, 128, generator=g).to(torch.bfloat16)
+    dy = (torch.randn(2, N, N, 128, generator=g) * 3.0).to(torch.bfloat16)
+    mask = torch.rand(2, N, generator=g) > 0.15
+    pmask = torch.rand(2, N, N, generator=g) > 0.1
+    biases = {"to_left_gate": torch.ones(128), "to_right": 0.1 * torch.randn(128, generator=g),
+              "to_gate": 0.2 * torch.randn(128, generator=g), "to_out": 0.1 * torch.randn(128, generator=g)}
+    y_ref, dz_ref, gp_ref = _oracle_grads(z, p, mask, dy, True, pair_mask=pmask, biases=biases)
+    dev = lambda d: {k: t.to(DEV) for k, t in d.items()}  # noqa: E731
+    zd, pd = z.to(DEV), dev(p)
+    ws = F_.aligned_empty(F_.workspace_bytes(2, N, True), torch.device(DEV))
+    y = F_.trimul_forward(zd, pd, mask.to(DEV), outgoing=True, pair_mask=pmask.to(DEV), biases=dev(biases), workspace=ws, check=True)
+    _check("y", y, y_ref, 5e-3)
+    runs = []
+    for _ in range(2):
+        dz, grads = F_.trimul_backward(dy.to(DEV), zd, pd, ws, mask.to(DEV), outgoing=True, pair_mask=pmask.to(DEV),
+                                       biases=dev(biases), check=True)
+        runs.append((dz, grads))
+    _check("dz", runs[0][0], dz_ref)
+    for k in _PARAM_KEYS:
+        assert runs[0][1][k].dtype == torch.float32
+        _check(k, runs[0][1][k], gp_ref[k], 4e-3)  # fp32 gradients: no bf16 rounding of the result
+        assert torch.equal(runs[0][1][k], runs[1][1][k]), k
+    assert torch.equal(runs[0][0], runs[1][0])
+
+
+def test_gradient_scale_invariance_and_zero_gradient():
+    """The power-of-two scale the fp16 gradient tiles carry is invisible: dy and 2^-20 dy give gradients that differ by
+    exactly that factor; dy = 0 gives zeros (not NaN)."""
+    from miniworld_b200 import functional as F_
+
+    N = 72
+    p = rand_params(540)
+    g = torch.Generator().manual_seed(541)
+    z = torch.randn(1, N, N, 128, generator=g).to(torch.bfloat16).to(DEV)
+    dy = torch.randn(1, N, N, 128, generator=g).to(torch.bfloat16).to(DEV)
+    pd = {k: v.to(DEV) for k, v in p.items()}
+    ws = F_.aligned_empty(F_.workspace_bytes(1, N, False), torch.device(DEV))
+    F_.trimul_forward(z, pd, None, outgoing=False, workspace=ws, check=True)
+    dz1, g1 = F_.trimul_backward(dy, z, pd, ws, None, outgoing=False, residual=False, check=True)
+    dz2, g2 = F_.trimul_backward((dy.float() * 2.0**-20).to(torch.bfloat16), z, pd, ws, None, outgoing=False, residual=False, check=True)
+    assert torch.equal(dz1.float() * 2.0**-20, dz2.float())
+    for k in _PARAM_KEYS:
+        assert torch.equal(g1[k] * 2.0**-20, g2[k]), k
+    dz0, g0 = F_.trimul_backward(torch.zeros_like(dy), z, pd, ws, None, outgoing=False, residual=False, check=True)
+    assert not dz0.float().any() and all(not v.any() for v in g0.values())
+
+
+def test_gradients_at_crop_384():
+    """L = 384 (the reference's validation length), both LayerNorms with every third gamma zero."""
+    N = 384
+    p = rand_params(550)
+    p["ln_pair.weight"][::3] = 0
+    p["ln_out.weight"][::3] = 0
+    g = torch.Generator().manual_seed(551)
+    z = torch.randn(1, N, N, 128, generator=g).to(torch.bfloat16)
+    dy = (torch.randn(1, N, N, 128, generator=g) * 0.01).to(torch.bfloat16)
+    mask = torch.rand(1, N, generator=g) > 0.2
+    y_ref, dz_ref, gp_ref = _oracle_grads(z, p, mask, dy, False)
+    zd = z.to(DEV).requires_grad_(True)
+    pd = {k: v.detach().to(DEV).requires_grad_(True) for k, v in p.items()}
+    y = trimul_train(zd, pd, mask.to(DEV), outgoing=False, check=True)
+    y.backward(dy.to(DEV))
+    _check("y", y, y_ref, 5e-3)
+    _check("dz", zd.grad, dz_ref)
+    for k in _PARAM_KEYS:
+        _check(k, pd[k].grad, gp_ref[k])

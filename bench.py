@@ -581,7 +581,42 @@ def block_operators(r: "Runner", steps: int, stream, dev) -> dict:
             out[name] = entry
     if bid.device_status() != 0 or tr.device_status() != 0:
         raise SystemExit("bidirectional / transition forward reported a device status")
+    out["training"] = training_step(r, steps, stream, dev)
     return out
+
+
+def training_step(r: "Runner", steps: int, stream, dev) -> dict:
+    """CUDA-event times of one training step of the unidirectional module on the headline input: the differentiable
+    forward (stage tensors kept) and ``b200_trimul_backward`` (gradients of the input and all ten parameters)."""
+    from miniworld_b200 import functional as F_
+
+    B, N, z, mask = r.B, r.N, r.z, r.mask
+    gen = torch.Generator(device=dev).manual_seed(78)
+    dy = (torch.randn(z.shape, generator=gen, device=dev) * 0.01).to(torch.bfloat16)
+    res = {"workload": r.name}
+    for direction in r.w.directions:
+        outgoing = direction == "outgoing"
+        params = {k: v.detach() for k, v in r.mods[direction]._params().items()}
+        ws = F_.aligned_empty(F_.workspace_bytes(B, N, outgoing), dev)
+        bws = F_.aligned_empty(F_.backward_workspace_bytes(B, N), dev)
+        y = torch.empty_like(z)
+
+        def fwd():
+            F_.trimul_forward(z, params, mask, outgoing=outgoing, workspace=ws, out=y)
+
+        def bwd():
+            F_.trimul_backward(dy, z, params, ws, mask, outgoing=outgoing, workspace=bws)
+
+        entry = {}
+        for name, fn in (("forward", fwd), ("backward", bwd)):
+            for _ in range(3):
+                fn()
+            ms = sorted(time_events(fn, steps, stream) / steps for _ in range(REPEATS))
+            entry[f"ms_{name}"] = statistics.median(ms)
+        F_.check_status(bws[:64].view(torch.int32), "b200_trimul_backward")
+        entry["backward_over_forward"] = entry["ms_backward"] / entry["ms_forward"]
+        res[direction] = entry
+    return res
 
 
 def stage_roofline(r: Runner, steps: int, stream, traffic):

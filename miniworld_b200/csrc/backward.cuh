@@ -22,7 +22,13 @@
 
 namespace trimul {
 
-constexpr int kBwdThreads = 256;
+#ifndef TRIMUL_BWD_PARTS
+#define TRIMUL_BWD_PARTS 4
+#endif
+constexpr int kBwdParts = TRIMUL_BWD_PARTS;      // threads per position: each covers 128 / kBwdParts channels
+constexpr int kBwdThreads = 128 * kBwdParts;
+constexpr int kBwdCh = 128 / kBwdParts;          // channels per thread
+constexpr int kBwdChunks = kBwdCh / 8;           // 16-byte chunks (8 channels) per thread
 constexpr int kBwdTile = 32768;  // one [128][128] 16-bit tile
 constexpr int kBwdSmemBytes = 6 * kBwdTile + 4096 /* exchange */ + 1024 /* constants */ + 256 /* barriers */ + 1024;
 
@@ -63,14 +69,14 @@ __device__ __forceinline__ bool cta_wait(uint32_t bar, uint32_t parity, volatile
 
 // Normalise the 128 channels of every position of a tile in place (fp16 result), the thread covering 64 of them.
 // ROWS_ARE_POSITIONS: element (pos, c) (a [pos][c] tile, input bf16 or fp16), else element (c, pos) (a [c][pos] tile,
-// fp16). Returns rstd of the thread's position. `xchg` holds float2 [2][128].
+// fp16). Returns rstd of the thread's position. `xchg` holds float2 [kBwdParts][128].
 template <bool ROWS_ARE_POSITIONS, bool IN_BF16>
-__device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, int pos, int half, float eps) {
+__device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, int pos, int part, float eps) {
   float pv = 0.f, s1 = 0.f, s2 = 0.f;
   if constexpr (ROWS_ARE_POSITIONS) {
 #pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      const uint4 v = ld_chunk(tile + tile_chunk(pos, half * 8 + ch));
+    for (int ch = 0; ch < kBwdChunks; ++ch) {
+      const uint4 v = ld_chunk(tile + tile_chunk(pos, part * kBwdChunks + ch));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
@@ -83,30 +89,36 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
     }
   } else {
 #pragma unroll 8
-    for (int cc = 0; cc < 64; ++cc) {
-      const float x = ld_f16(tile + tile_off(half * 64 + cc, pos));
+    for (int cc = 0; cc < kBwdCh; ++cc) {
+      const float x = ld_f16(tile + tile_off(part * kBwdCh + cc, pos));
       if (cc == 0) pv = x;
       const float d = x - pv;
       s1 += d;
       s2 = fmaf(d, d, s2);
     }
   }
-  const float mean_h = pv + s1 * (1.0f / 64.0f);
-  const float m2_h = fmaxf(s2 - s1 * s1 * (1.0f / 64.0f), 0.f);
-  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (half * 128 + pos) * 8), "f"(mean_h), "f"(m2_h) : "memory");
+  const float mean_h = pv + s1 * (1.0f / kBwdCh);
+  const float m2_h = fmaxf(s2 - s1 * s1 * (1.0f / kBwdCh), 0.f);
+  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(mean_h), "f"(m2_h) : "memory");
   named_bar_sync(1, kBwdThreads);
-  float ma, qa, mb, qb;
-  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(ma), "=f"(qa) : "r"(xchg + pos * 8));
-  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(mb), "=f"(qb) : "r"(xchg + (128 + pos) * 8));
-  const float mean = 0.5f * (ma + mb);
-  const float dlt = ma - mb;
-  const float m2 = qa + qb + dlt * dlt * 32.0f;  // n_a n_b / (n_a + n_b) = 32
+  // merge the equal-sized partials of this position: mean of means, M2 = sum M2_k + n_k sum (mean_k - mean)^2
+  float mk[kBwdParts], qk[kBwdParts];
+  float mean = 0.f, m2 = 0.f;
+#pragma unroll
+  for (int k = 0; k < kBwdParts; ++k) {
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(mk[k]), "=f"(qk[k]) : "r"(xchg + (k * 128 + pos) * 8));
+    mean += mk[k];
+    m2 += qk[k];
+  }
+  mean *= 1.0f / kBwdParts;
+#pragma unroll
+  for (int k = 0; k < kBwdParts; ++k) m2 = fmaf(static_cast<float>(kBwdCh) * (mk[k] - mean), mk[k] - mean, m2);
   const float rstd = rsqrtf(m2 * (1.0f / 128.0f) + eps);
   const float nmr = -mean * rstd;
   if constexpr (ROWS_ARE_POSITIONS) {
 #pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      const uint32_t addr = tile + tile_chunk(pos, half * 8 + ch);
+    for (int ch = 0; ch < kBwdChunks; ++ch) {
+      const uint32_t addr = tile + tile_chunk(pos, part * kBwdChunks + ch);
       const uint4 v = ld_chunk(addr);
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
       uint32_t o[4];
@@ -119,8 +131,8 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
     }
   } else {
 #pragma unroll 8
-    for (int cc = 0; cc < 64; ++cc) {
-      const uint32_t addr = tile + tile_off(half * 64 + cc, pos);
+    for (int cc = 0; cc < kBwdCh; ++cc) {
+      const uint32_t addr = tile + tile_off(part * kBwdCh + cc, pos);
       st_f16_sat(addr, fmaf(ld_f16(addr), rstd, nmr));
     }
   }
@@ -128,22 +140,35 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
   return rstd;
 }
 
-// Sum the per-thread column partials of a CTA over its 128 positions: `acc` holds this thread's 64 channels (half
-// `half`) for two vectors; scratch is float[256][129] (a tile region, padded against bank conflicts).
-__device__ __forceinline__ void flush_colsums(const float (&a0)[64], const float (&a1)[64], uint8_t* scratch, int pos, int half,
-                                              float* out0, float* out1) {
+// Sum of the float2 partials the kBwdParts threads of a position left in `xchg` (fixed order).
+__device__ __forceinline__ void sum_partials(uint32_t xchg, int pos, float& a, float& b) {
+  a = 0.f, b = 0.f;
+#pragma unroll
+  for (int k = 0; k < kBwdParts; ++k) {
+    float x, y;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(x), "=f"(y) : "r"(xchg + (k * 128 + pos) * 8));
+    a += x, b += y;
+  }
+}
+
+// Sum the per-thread column partials of a CTA over its 128 positions: `acc` holds this thread's channels (part
+// `part`) for two vectors; scratch is float[256][129] (a tile region, padded against bank conflicts).
+__device__ __forceinline__ void flush_colsums(const float (&a0)[kBwdCh], const float (&a1)[kBwdCh], uint8_t* scratch, int pos,
+                                              int part, float* out0, float* out1) {
   float* s = reinterpret_cast<float*>(scratch);
   // rows: (vector * 128 + channel), columns: position
 #pragma unroll
-  for (int c = 0; c < 64; ++c) {
-    s[(0 * 128 + half * 64 + c) * 129 + pos] = a0[c];
-    s[(1 * 128 + half * 64 + c) * 129 + pos] = a1[c];
+  for (int c = 0; c < kBwdCh; ++c) {
+    s[(0 * 128 + part * kBwdCh + c) * 129 + pos] = a0[c];
+    s[(1 * 128 + part * kBwdCh + c) * 129 + pos] = a1[c];
   }
   __syncthreads();
   const int r = threadIdx.x;  // 0..255: vector r / 128, channel r % 128
-  float sum = 0.f;
-  for (int p = 0; p < 128; ++p) sum += s[r * 129 + p];
-  (r < 128 ? out0 : out1)[r & 127] = sum;
+  if (r < 256) {
+    float sum = 0.f;
+    for (int p = 0; p < 128; ++p) sum += s[r * 129 + p];
+    (r < 128 ? out0 : out1)[r & 127] = sum;
+  }
   __syncthreads();
 }
 
@@ -183,7 +208,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
   float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + 4096);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q = warp & 3, half = warp >> 2;
+  const int q = warp & 3, part = warp >> 2;
   const int pos = q * 32 + lane;
   const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
 
@@ -199,7 +224,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     prefetch_tmap(&map_dt);
     prefetch_tmap(&map_dx);
   }
-  const_ptr[threadIdx.x] = p.consts[threadIdx.x];
+  if (threadIdx.x < 256) const_ptr[threadIdx.x] = p.consts[threadIdx.x];
   if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
@@ -218,9 +243,9 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       tma_load_2d(wg_s + kh * 16384, &map_wg, w_full, kh * 64, 0);
     }
   }
-  float acc_so[64], acc_sg[64];
+  float acc_so[kBwdCh], acc_sg[kBwdCh];
 #pragma unroll
-  for (int c = 0; c < 64; ++c) acc_so[c] = 0.f, acc_sg[c] = 0.f;
+  for (int c = 0; c < kBwdCh; ++c) acc_so[c] = 0.f, acc_sg[c] = 0.f;
 
   bool ok = true;
   int it = 0;
@@ -242,8 +267,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
     loads_pending = false;
     // ---- phase 1: normalise t (rows = channels) and z (rows = positions) in place
-    const float rstd_out = normalise_tile<false, false>(t_s, xchg, pos, half, p.eps_out);
-    normalise_tile<true, true>(z_s, xchg, pos, half, p.eps_in);
+    const float rstd_out = normalise_tile<false, false>(t_s, xchg, pos, part, p.eps_out);
+    normalise_tile<true, true>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -274,14 +299,14 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       const uint4* sc = nullptr;
       if (p.drop_scale != nullptr && j < p.n) {
         const int b = row / p.n;
-        sc = reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * 128 + half * 64);
+        sc = reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * 128 + part * kBwdCh);
       }
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t vp[8], vg[8];
-        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, vp);
-        tmem_ld8(tmem_base + lane_sel + 128 + half * 64 + ch * 8, vg);
-        const uint32_t addr = tile_chunk(pos, half * 8 + ch);
+        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, vp);
+        tmem_ld8(tmem_base + lane_sel + 128 + part * kBwdCh + ch * 8, vg);
+        const uint32_t addr = tile_chunk(pos, part * kBwdChunks + ch);
         const uint4 dyv = ld_chunk(dy_s + addr);
         uint4 scv = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);  // bf16 ones
         if (sc != nullptr) scv = __ldg(sc + ch);
@@ -296,7 +321,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
           float dpv[2], dgv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int c = half * 64 + ch * 8 + t * 2 + e;
+            const int c = part * kBwdCh + ch * 8 + t * 2 + e;
             const float proj = __uint_as_float(vp[t * 2 + e]) + const_ptr[c];
             const float gate = sigmoid_fast(__uint_as_float(vg[t * 2 + e]) + const_ptr[128 + c]);
             const float du = (e == 0 ? d2.x * s2.x : d2.y * s2.y) * gc;
@@ -354,36 +379,35 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     {
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t v[8];
-        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, v);
+        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float d = __uint_as_float(v[e]);
           s1 += d;
-          s2 = fmaf(d, ld_f16(t_s + tile_off(half * 64 + ch * 8 + e, pos)), s2);
+          s2 = fmaf(d, ld_f16(t_s + tile_off(part * kBwdCh + ch * 8 + e, pos)), s2);
         }
       }
-      asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (half * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
+      asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
       named_bar_sync(1, kBwdThreads);
-      float a1, a2, b1, b2;
-      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a1), "=f"(a2) : "r"(xchg + pos * 8));
-      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(b1), "=f"(b2) : "r"(xchg + (128 + pos) * 8));
-      const float m1 = (a1 + b1) * (1.0f / 128.0f), m2 = (a2 + b2) * (1.0f / 128.0f);
+      float m1, m2;
+      sum_partials(xchg, pos, m1, m2);
+      m1 *= 1.0f / 128.0f, m2 *= 1.0f / 128.0f;
       const float rs = rstd_out * 0.0625f;  // d / d t of the stored t / 16
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t v[8], x[8];
-        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, v);
-        tmem_ld8(tmem_base + lane_sel + 128 + half * 64 + ch * 8, x);
+        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
+        tmem_ld8(tmem_base + lane_sel + 128 + part * kBwdCh + ch * 8, x);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const uint32_t addr = t_s + tile_off(half * 64 + ch * 8 + e, pos);
+          const uint32_t addr = t_s + tile_off(part * kBwdCh + ch * 8 + e, pos);
           st_f16_sat(addr, rs * (__uint_as_float(v[e]) - m1 - ld_f16(addr) * m2));
         }
-        st_chunk(z_s + tile_chunk(pos, half * 8 + ch),
+        st_chunk(z_s + tile_chunk(pos, part * kBwdChunks + ch),
                  pack_f16x2_sat(make_float2(__uint_as_float(x[0]), __uint_as_float(x[1]))),
                  pack_f16x2_sat(make_float2(__uint_as_float(x[2]), __uint_as_float(x[3]))),
                  pack_f16x2_sat(make_float2(__uint_as_float(x[4]), __uint_as_float(x[5]))),
@@ -423,11 +447,11 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t v[8];
-        tmem_ld8(tmem_base + lane_sel + 256 + m * 128 + half * 64 + ch * 8, v);
+        tmem_ld8(tmem_base + lane_sel + 256 + m * 128 + part * kBwdCh + ch * 8, v);
         tmem_ld_wait();
-        float4* dst = reinterpret_cast<float4*>(pm + (m * 128 + pos) * 128 + half * 64 + ch * 8);
+        float4* dst = reinterpret_cast<float4*>(pm + (m * 128 + pos) * 128 + part * kBwdCh + ch * 8);
         dst[0] = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]), __uint_as_float(v[3]));
         dst[1] = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]), __uint_as_float(v[6]), __uint_as_float(v[7]));
       }
@@ -435,7 +459,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
   }
   {
     float* ps = p.part_s + static_cast<size_t>(blockIdx.x) * 2 * 128;
-    flush_colsums(acc_so, acc_sg, smem, pos, half, ps, ps + 128);  // every tile region is free by now
+    flush_colsums(acc_so, acc_sg, smem, pos, part, ps, ps + 128);  // every tile region is free by now
   }
   tc_fence_before();
   __syncthreads();
@@ -486,7 +510,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + 4096);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q = warp & 3, half = warp >> 2;
+  const int q = warp & 3, part = warp >> 2;
   const int pos = q * 32 + lane;
   const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
 
@@ -500,7 +524,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     prefetch_tmap(&map_do);
     prefetch_tmap(&map_out);
   }
-  const_ptr[threadIdx.x] = p.consts[threadIdx.x];
+  if (threadIdx.x < 256) const_ptr[threadIdx.x] = p.consts[threadIdx.x];
   if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
@@ -519,9 +543,9 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       tma_load_2d(wg_s + kh * 16384, &map_wg, w_full, kh * 64, 0);
     }
   }
-  float acc_sv[64], acc_sg[64];
+  float acc_sv[kBwdCh], acc_sg[kBwdCh];
 #pragma unroll
-  for (int c = 0; c < 64; ++c) acc_sv[c] = 0.f, acc_sg[c] = 0.f;
+  for (int c = 0; c < kBwdCh; ++c) acc_sv[c] = 0.f, acc_sg[c] = 0.f;
 
   bool ok = true;
   int it = 0;
@@ -542,7 +566,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
     loads_pending = false;
     // ---- phase 1: x_hat in place
-    const float rstd_in = normalise_tile<true, true>(z_s, xchg, pos, half, p.eps_in);
+    const float rstd_in = normalise_tile<true, true>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -574,15 +598,15 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       if (valid && p.pair_mask != nullptr) valid = p.pair_mask[(static_cast<size_t>(b) * p.n + i) * p.n + j] != 0;
       const float vm = valid ? 16.0f : 0.f;  // the contraction's outputs are stored times 2^-4
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t vv[8], vg[8];
-        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, vv);
-        tmem_ld8(tmem_base + lane_sel + 128 + half * 64 + ch * 8, vg);
+        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, vv);
+        tmem_ld8(tmem_base + lane_sel + 128 + part * kBwdCh + ch * 8, vg);
         tmem_ld_wait();
         float dvv[8], dgv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int h = half * 64 + ch * 8 + e;
+          const int h = part * kBwdCh + ch * 8 + e;
           const float val = __uint_as_float(vv[e]) + const_ptr[h];
           const float sg = sigmoid_fast(__uint_as_float(vg[e]) + const_ptr[128 + h]);
           const float d_o = ld_f16(do_s + tile_off(h, pos)) * vm;
@@ -591,7 +615,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
           acc_sv[ch * 8 + e] += dvv[e];
           acc_sg[ch * 8 + e] += dgv[e];
         }
-        const uint32_t addr = tile_chunk(pos, half * 8 + ch);
+        const uint32_t addr = tile_chunk(pos, part * kBwdChunks + ch);
         st_chunk(dv_s + addr, pack_f16x2_sat(make_float2(dvv[0], dvv[1])), pack_f16x2_sat(make_float2(dvv[2], dvv[3])),
                  pack_f16x2_sat(make_float2(dvv[4], dvv[5])), pack_f16x2_sat(make_float2(dvv[6], dvv[7])));
         st_chunk(dg_s + addr, pack_f16x2_sat(make_float2(dgv[0], dgv[1])), pack_f16x2_sat(make_float2(dgv[2], dgv[3])),
@@ -631,17 +655,17 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     // ---- phase 5: add the running d x_hat; !LAST: write it back, LAST: LayerNorm backward + residual -> dz
     {
       const bool inside = j < p.n;
-      const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * 128 + half * 64);
-      float tot[64];
+      const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * 128 + part * kBwdCh);
+      float tot[kBwdCh];
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t v[8];
-        tmem_ld8(tmem_base + lane_sel + half * 64 + ch * 8, v);
+        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
         uint4 in = make_uint4(0u, 0u, 0u, 0u);
         if (inside) in = __ldg(src + ch);
         uint4 xh = make_uint4(0u, 0u, 0u, 0u);
-        if constexpr (LAST) xh = ld_chunk(z_s + tile_chunk(pos, half * 8 + ch));
+        if constexpr (LAST) xh = ld_chunk(z_s + tile_chunk(pos, part * kBwdChunks + ch));
         tmem_ld_wait();
         const uint32_t iw[4] = {in.x, in.y, in.z, in.w};
         const uint32_t xw[4] = {xh.x, xh.y, xh.z, xh.w};
@@ -660,24 +684,23 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       }
       if constexpr (!LAST) {
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch)
-          st_chunk(dv_s + tile_chunk(pos, half * 8 + ch), pack_f16x2_sat(make_float2(tot[ch * 8], tot[ch * 8 + 1])),
+        for (int ch = 0; ch < kBwdChunks; ++ch)
+          st_chunk(dv_s + tile_chunk(pos, part * kBwdChunks + ch), pack_f16x2_sat(make_float2(tot[ch * 8], tot[ch * 8 + 1])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 2], tot[ch * 8 + 3])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 4], tot[ch * 8 + 5])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 6], tot[ch * 8 + 7])));
       } else {
-        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (half * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
+        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
         named_bar_sync(1, kBwdThreads);
-        float a1, a2, b1, b2;
-        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a1), "=f"(a2) : "r"(xchg + pos * 8));
-        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(b1), "=f"(b2) : "r"(xchg + (128 + pos) * 8));
-        const float m1 = (a1 + b1) * (1.0f / 128.0f), m2 = (a2 + b2) * (1.0f / 128.0f);
+        float m1, m2;
+        sum_partials(xchg, pos, m1, m2);
+        m1 *= 1.0f / 128.0f, m2 *= 1.0f / 128.0f;
         const float rs = rstd_in * gc_inv;
         const uint4* dyp = p.dy == nullptr ? nullptr
-                                           : reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * 128 + half * 64);
+                                           : reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * 128 + part * kBwdCh);
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const uint4 xh = ld_chunk(z_s + tile_chunk(pos, half * 8 + ch));
+        for (int ch = 0; ch < kBwdChunks; ++ch) {
+          const uint4 xh = ld_chunk(z_s + tile_chunk(pos, part * kBwdChunks + ch));
           uint4 dyv = make_uint4(0u, 0u, 0u, 0u);
           if (dyp != nullptr && inside) dyv = __ldg(dyp + ch);
           const uint32_t xw[4] = {xh.x, xh.y, xh.z, xh.w};
@@ -690,7 +713,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
             o[t] = pack_bf16x2(fmaf(rs, tot[ch * 8 + 2 * t] - m1 - x.x * m2, r.x),
                                fmaf(rs, tot[ch * 8 + 2 * t + 1] - m1 - x.y * m2, r.y));
           }
-          st_chunk(dv_s + tile_chunk(pos, half * 8 + ch), o[0], o[1], o[2], o[3]);
+          st_chunk(dv_s + tile_chunk(pos, part * kBwdChunks + ch), o[0], o[1], o[2], o[3]);
         }
       }
     }
@@ -723,11 +746,11 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t v[8];
-        tmem_ld8(tmem_base + lane_sel + 256 + m * 128 + half * 64 + ch * 8, v);
+        tmem_ld8(tmem_base + lane_sel + 256 + m * 128 + part * kBwdCh + ch * 8, v);
         tmem_ld_wait();
-        float4* dst = reinterpret_cast<float4*>(pm + (m * 128 + pos) * 128 + half * 64 + ch * 8);
+        float4* dst = reinterpret_cast<float4*>(pm + (m * 128 + pos) * 128 + part * kBwdCh + ch * 8);
         dst[0] = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]), __uint_as_float(v[3]));
         dst[1] = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]), __uint_as_float(v[6]), __uint_as_float(v[7]));
       }
@@ -735,7 +758,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   }
   {
     float* ps = p.part_s + static_cast<size_t>(blockIdx.x) * 2 * 128;
-    flush_colsums(acc_sv, acc_sg, smem, pos, half, ps, ps + 128);
+    flush_colsums(acc_sv, acc_sg, smem, pos, part, ps, ps + 128);
   }
   tc_fence_before();
   __syncthreads();
@@ -818,48 +841,71 @@ __global__ void __launch_bounds__(128) bwd_pack_kernel(const PackArgs a, uint8_t
     reinterpret_cast<float*>(packed + kBwdPackedD)[m * 128 + row] = d + (a.bias[m] != nullptr ? a.bias[m][row] : 0.f);
 }
 
-// out[e] = sum over the CTAs' partials, in CTA order (deterministic)
-__global__ void __launch_bounds__(256) bwd_reduce_kernel(const float* parts, int n_parts, size_t stride, float* out, int count) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= count) return;
-  float s = 0.f;
-  for (int i = 0; i < n_parts; ++i) s += parts[static_cast<size_t>(i) * stride + e];
-  out[e] = s;
+// M[e] and S[e] = sums over the CTAs' partials, in CTA order (deterministic). Blocks 0 .. 127 take M (2 x 128 x 128
+// values), block 128 takes S (2 x 128 values).
+__global__ void __launch_bounds__(256) bwd_reduce_kernel(const float* part_m, const float* part_s, int n_parts, float* m_out,
+                                                         float* s_out) {
+  const bool is_s = blockIdx.x == 128;
+  const float* parts = is_s ? part_s : part_m;
+  const size_t stride = is_s ? 2 * 128 : 2 * 128 * 128;
+  const int e = is_s ? threadIdx.x : blockIdx.x * 256 + threadIdx.x;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int i = 0;
+  for (; i + 4 <= n_parts; i += 4) {  // four independent loads in flight; the additions keep their order
+    const float a = parts[static_cast<size_t>(i) * stride + e], b = parts[static_cast<size_t>(i + 1) * stride + e];
+    const float c = parts[static_cast<size_t>(i + 2) * stride + e], d = parts[static_cast<size_t>(i + 3) * stride + e];
+    s0 += a, s1 += b, s2 += c, s3 += d;
+  }
+  for (; i < n_parts; ++i) s0 += parts[static_cast<size_t>(i) * stride + e];
+  (is_s ? s_out : m_out)[e] = (s0 + s1) + (s2 + s3);
 }
 
 // Parameter gradients from the reduced sums M[m] = dOut_m^T x_hat (times c) and S[m] = column sums of dOut_m (times c):
 //   dW_m[r][k] = (M[m][r][k] gamma[k] + S[m][r] beta[k]) / c
 //   dgamma[k]  = sum_m sum_r W_m[r][k] M[m][r][k] / c,   dbeta[k] = sum_m sum_r W_m[r][k] S[m][r] / c
 // over the matrices that read that LayerNorm (the output one: matrix 4; the input one: the other five).
-// One block of 128 threads, thread = column k; the sums run in a fixed order.
+// Grid (6 matrices, 8 blocks of 16 rows), thread = column k; the LayerNorm sums leave as partials [6][8][2][128] that
+// bwd_finalize_ln_kernel adds in a fixed order.
 struct BwdFinalArgs {
   PackArgs w;           // raw weights and LayerNorm parameters
   const float* m_all;   // [6][128][128]
   const float* s_all;   // [6][128]
   const float* scale;   // [2]
   float* dw[6];         // [128][128] fp32 each
+  float* ln_part;       // [6][8][2][128]
   float* d_ln_in_w;
   float* d_ln_in_b;
   float* d_ln_out_w;
   float* d_ln_out_b;
 };
 __global__ void __launch_bounds__(128) bwd_finalize_kernel(const BwdFinalArgs a) {
-  const int k = threadIdx.x;
+  const int k = threadIdx.x, m = blockIdx.x, rb = blockIdx.y;
   const float cinv = a.scale[1];
+  const float gamma = (m == 4 ? a.w.ln_out_w : a.w.ln_in_w)[k];
+  const float beta = (m == 4 ? a.w.ln_out_b : a.w.ln_in_b)[k];
+  float ag = 0.f, ab = 0.f;
+#pragma unroll 4
+  for (int r = rb * 16; r < rb * 16 + 16; ++r) {
+    const size_t wi = static_cast<size_t>(r) * a.w.ld[m] + k;
+    const float w = a.w.f32_weights ? static_cast<const float*>(a.w.w[m])[wi]
+                                    : __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(a.w.w[m])[wi]) << 16);
+    const float mv = a.m_all[(m * 128 + r) * 128 + k] * cinv;
+    const float sv = a.s_all[m * 128 + r] * cinv;
+    a.dw[m][r * 128 + k] = fmaf(mv, gamma, sv * beta);
+    ag = fmaf(w, mv, ag);
+    ab = fmaf(w, sv, ab);
+  }
+  a.ln_part[((m * 8 + rb) * 2 + 0) * 128 + k] = ag;
+  a.ln_part[((m * 8 + rb) * 2 + 1) * 128 + k] = ab;
+}
+__global__ void __launch_bounds__(128) bwd_finalize_ln_kernel(const BwdFinalArgs a) {
+  const int k = threadIdx.x;
   float g_in = 0.f, b_in = 0.f, g_out = 0.f, b_out = 0.f;
   for (int m = 0; m < 6; ++m) {
-    const float gamma = (m == 4 ? a.w.ln_out_w : a.w.ln_in_w)[k];
-    const float beta = (m == 4 ? a.w.ln_out_b : a.w.ln_in_b)[k];
     float ag = 0.f, ab = 0.f;
-    for (int r = 0; r < 128; ++r) {
-      const size_t wi = static_cast<size_t>(r) * a.w.ld[m] + k;
-      const float w = a.w.f32_weights ? static_cast<const float*>(a.w.w[m])[wi]
-                                      : __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(a.w.w[m])[wi]) << 16);
-      const float mv = a.m_all[(m * 128 + r) * 128 + k] * cinv;
-      const float sv = a.s_all[m * 128 + r] * cinv;
-      a.dw[m][r * 128 + k] = fmaf(mv, gamma, sv * beta);
-      ag = fmaf(w, mv, ag);
-      ab = fmaf(w, sv, ab);
+    for (int rb = 0; rb < 8; ++rb) {
+      ag += a.ln_part[((m * 8 + rb) * 2 + 0) * 128 + k];
+      ab += a.ln_part[((m * 8 + rb) * 2 + 1) * 128 + k];
     }
     if (m == 4) g_out += ag, b_out += ab;
     else g_in += ag, b_in += ab;

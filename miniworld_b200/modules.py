@@ -15,10 +15,12 @@ LayerNorm, left / right of width 2h whose halves are contracted outgoing and inc
 contracted channels, one gate, one residual (``docs/paper/supplement.tex:125-136``); same parameter names, wider
 shapes.
 
-Forward only. In training mode with ``p_drop > 0`` the forward applies the row-shared dropout of the reference
+In training mode with ``p_drop > 0`` the forward applies the row-shared dropout of the reference
 (``x + drop_row(f(x))``: one keep-mask per (batch, column, channel), shared by all rows,
-``src/miniworld/blocks/template.py:38-40``); there is no backward: calling the module with gradients enabled on an
-input that requires them raises ``NotImplementedError``.
+``src/miniworld/blocks/template.py:38-40``). The unidirectional module with d_pair = d_hidden = 128 is differentiable
+(input and all ten parameters, :mod:`miniworld_b200.training`); the bidirectional module, the 64-wide modules and the
+Transition have no backward: calling them with gradients enabled on an input that requires them raises
+``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -86,7 +88,7 @@ class Fp32LayerNorm(nn.LayerNorm):
 
 
 class TriangleMultiplication(nn.Module):
-    """Triangle multiplicative update, forward only, on B200 kernels.
+    """Triangle multiplicative update on B200 kernels (forward; backward for d_pair = d_hidden = 128).
 
     ``forward(pair [B,N,N,d_pair] bf16, mask Bool[B,N] | None) -> pair + update`` (bf16).
     Linear weights may be bf16 or fp32 masters; LayerNorm affine parameters are kept in fp32 whatever

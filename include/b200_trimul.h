@@ -290,23 +290,28 @@ int b200_trimul_forward_static(const void* z, const void* w_left, const void* w_
                                void* cuda_stream);
 
 /*
- * Backward of the unidirectional module (d_pair = d_hidden = 128): the reference's training path, stages B1-B12 of
+ * Backward for d_pair = d_hidden = 128: the reference's training path, stages B1-B12 of
  * docs/kernels/trimul/TRIMUL_STATUS.md:43-52 (its B5-B6, the contraction gradients, are cuBLAS calls there). Given
  * dy = d loss / d y ([B, N, N, 128] bf16), the inputs of the forward call and the workspace that
- * b200_trimul_forward / _forward_ex left behind for these inputs (it holds left, right and tri), it writes
+ * b200_trimul_forward / _forward_ex left behind for these inputs (it holds the stage tensors), it writes
  *   dz  [B, N, N, 128] bf16          d loss / d z, the residual path included when `residual` is non-zero
- *   dw[6] fp32 [128, 128] each       gradients of w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out (that order)
- *   d_ln_in_w / _b, d_ln_out_w / _b  fp32 [128] each
+ *   dw[6] fp32, the parameters' shapes: gradients of w_left, w_left_gate, w_right, w_right_gate, w_gate, w_out (that
+ *                                    order): [128, 128] each, or [256, 128] x 4, [128, 128], [128, 256] for direction 0
+ *   d_ln_in_w / _b fp32 [128],  d_ln_out_w / _b fp32 [128] (direction 0: [256])
  * Every output is overwritten, not accumulated into. Biases are constants (no gradient). drop_scale as in the forward.
- * Launches: weight packing, max |dy| and the power-of-two scale the fp16 gradient tiles carry, the epilogue's backward
- * (one kernel: both LayerNorm-folded GEMMs recomputed, four gradient GEMMs on the tensor cores), the two contraction
- * gradient launches, the prologue's backward once per side, partial-sum reductions, the parameter gradients.
+ * Launches, one direction: weight packing, max |dy| and the power-of-two scale the fp16 gradient tiles carry, the
+ * epilogue's backward (one kernel: both LayerNorm-folded GEMMs recomputed, four gradient GEMMs on the tensor cores), the
+ * two contraction gradient launches, the prologue's backward once per side, partial-sum reductions, the parameter
+ * gradients. Direction 0 (the bidirectional module): the statistics of the 256-channel output LayerNorm, the epilogue's
+ * backward once per 128-channel tensor plus a kernel that finishes the first tensor's LayerNorm backward, the forward's
+ * prologue once more (left / right of the first half, which the forward overwrote), four contraction gradient launches,
+ * the prologue's backward four times (side x half).
  * The result is deterministic (fixed summation order). Workspace: b200_trimul_backward_workspace_bytes, 1024-byte
- * aligned; _layout gives its 11 region offsets + the total (status, packed weights, scale, reduced sums M and S, per-CTA
- * partials of M and S, dtri, dleft, dright, d x_hat) for tests.
+ * aligned; _layout gives its 17 region offsets + the total (status, packed weights, scale, reduced sums M and S, per-CTA
+ * partials of M and S, dtri, dleft, dright, d x_hat, then the bidirectional module's extra regions) for tests.
  */
-int b200_trimul_backward_workspace_bytes(int B, int N, size_t* out_bytes);
-int b200_trimul_backward_workspace_layout(int B, int N, size_t* offsets12);
+int b200_trimul_backward_workspace_bytes(int B, int N, int direction, size_t* out_bytes);
+int b200_trimul_backward_workspace_layout(int B, int N, int direction, size_t* offsets18);
 int b200_trimul_backward(const void* dy, const void* z, const void* w_left, const void* w_left_gate, const void* w_right,
                          const void* w_right_gate, const void* w_gate, const void* w_out, int weight_dtype,
                          const float* ln_in_w, const float* ln_in_b, const float* ln_out_w, const float* ln_out_b,

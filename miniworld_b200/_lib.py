@@ -41,8 +41,8 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     ),
-    "b200_trimul_backward_workspace_bytes": (c_int, [c_int, c_int, POINTER(c_size_t)]),
-    "b200_trimul_backward_workspace_layout": (c_int, [c_int, c_int, POINTER(c_size_t)]),
+    "b200_trimul_backward_workspace_bytes": (c_int, [c_int, c_int, c_int, POINTER(c_size_t)]),
+    "b200_trimul_backward_workspace_layout": (c_int, [c_int, c_int, c_int, POINTER(c_size_t)]),
     "b200_trimul_backward": (
         c_int,
         [c_void_p] * 8 + [c_int] + [c_void_p] * 4 + [c_void_p] * 5 + [c_void_p] * 2 + [c_void_p] * 4

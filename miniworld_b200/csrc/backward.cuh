@@ -183,12 +183,26 @@ struct BwdEpilogueParams {
   float eps_out;       // scaled by 2^-8: tri is stored times 2^-4
   float* part_m;       // [grid][2][128][128]: per-CTA partial sums of dproj^T t_hat and dgate^T x_hat
   float* part_s;       // [grid][2][128]: per-CTA column sums of dproj and dgate
+  // the two-launch form for an output LayerNorm over 256 channels (MODE 1: first 128 channels, MODE 2: the others)
+  const float2* ext_stats;  // [B*N][N]: mean and rstd of the stored t over all 256 channels
+  float2* ln_part;          // [B*N][N]: MODE 1 writes its sums of d t_hat and d t_hat * t_hat; MODE 2 adds its own and
+                            // writes back the two means over 256 channels
+  const uint16_t* p_part;   // [B*N][N][128] fp16, MODE 2: the first launch's part of the output projection
   int* status;
 };
 
 // Epilogue backward. Inputs: tri [B*N][128][N] fp16 (times 2^-4), z and dy [B*N][N][128] bf16. Outputs:
 //   dtri [B*N][128][N] fp16 = c * d loss / d t,  dxg [B*N][N][128] fp16 = c * (d loss / d x_hat through the output gate)
 // and the per-CTA partials. Shared memory: W_out' , W_gate' (fp16, gamma folded), then four tiles: t, z, dy, dgate.
+//
+// MODE 0: the whole operator (128 contracted channels). MODE 1 / 2: the bidirectional module, whose output LayerNorm
+// and projection span 256 channels held in two tensors; two launches with the statistics given (`ext_stats`):
+//   MODE 1 (first tensor):  proj part = t_hat_1 Wo_1'^T + d_1 -> through map_dx (fp16); dproj; d t_hat_1 = dproj Wo_1'
+//                           written raw through map_dt; its two LayerNorm-backward sums -> ln_part; Mo_1.
+//   MODE 2 (second tensor): proj = part + t_hat_2 Wo_2'^T + d_2; dproj, dgate; d t_hat_2, dxg, Mo_2, Mg; the
+//                           LayerNorm backward of its own 128 channels with the sums over all 256 (means -> ln_part);
+//                           `bwd_ln_finish_kernel` then finishes the first tensor's gradient.
+template <int MODE>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_z,
                     const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_wo,
@@ -267,7 +281,20 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
     loads_pending = false;
     // ---- phase 1: normalise t (rows = channels) and z (rows = positions) in place
-    const float rstd_out = normalise_tile<false, false>(t_s, xchg, pos, part, p.eps_out);
+    float rstd_out;
+    if constexpr (MODE == 0) {
+      rstd_out = normalise_tile<false, false>(t_s, xchg, pos, part, p.eps_out);
+    } else {
+      float2 st = make_float2(0.f, 0.f);
+      if (j0 + pos < p.n) st = p.ext_stats[static_cast<size_t>(row) * p.n + j0 + pos];
+      rstd_out = st.y;
+      const float nmr = -st.x * st.y;
+#pragma unroll 8
+      for (int cc = 0; cc < kBwdCh; ++cc) {
+        const uint32_t addr = t_s + tile_off(part * kBwdCh + cc, pos);
+        st_f16_sat(addr, fmaf(ld_f16(addr), st.y, nmr));
+      }
+    }
     normalise_tile<true, true>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
     tc_fence_before();
@@ -297,6 +324,10 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     {
       const int j = j0 + pos;
       const uint4* sc = nullptr;
+      const uint4* pp = nullptr;
+      if constexpr (MODE == 2) {
+        if (j < p.n) pp = reinterpret_cast<const uint4*>(p.p_part + (static_cast<size_t>(row) * p.n + j) * 128 + part * kBwdCh);
+      }
       if (p.drop_scale != nullptr && j < p.n) {
         const int b = row / p.n;
         sc = reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * 128 + part * kBwdCh);
@@ -310,6 +341,11 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         const uint4 dyv = ld_chunk(dy_s + addr);
         uint4 scv = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);  // bf16 ones
         if (sc != nullptr) scv = __ldg(sc + ch);
+        uint4 ppv = make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (MODE == 2) {
+          if (pp != nullptr) ppv = __ldg(pp + ch);
+        }
+        const uint32_t pw[4] = {ppv.x, ppv.y, ppv.z, ppv.w};
         tmem_ld_wait();
         const uint32_t dw[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
         const uint32_t sw[4] = {scv.x, scv.y, scv.z, scv.w};
@@ -318,15 +354,16 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         for (int t = 0; t < 4; ++t) {
           const float2 d2 = bf16x2_to_float2(dw[t]);
           const float2 s2 = bf16x2_to_float2(sw[t]);
+          const float2 p2 = f16x2_to_float2(pw[t]);
           float dpv[2], dgv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int c = part * kBwdCh + ch * 8 + t * 2 + e;
-            const float proj = __uint_as_float(vp[t * 2 + e]) + const_ptr[c];
+            const float proj = __uint_as_float(vp[t * 2 + e]) + const_ptr[c] + (e == 0 ? p2.x : p2.y);
             const float gate = sigmoid_fast(__uint_as_float(vg[t * 2 + e]) + const_ptr[128 + c]);
             const float du = (e == 0 ? d2.x * s2.x : d2.y * s2.y) * gc;
             dpv[e] = du * gate;
-            dgv[e] = du * proj * gate * (1.0f - gate);
+            dgv[e] = MODE == 1 ? proj : du * proj * gate * (1.0f - gate);  // MODE 1 hands its part of proj on
             acc_so[ch * 8 + t * 2 + e] += dpv[e];
             acc_sg[ch * 8 + t * 2 + e] += dgv[e];
           }
@@ -354,11 +391,13 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         umma_bf16(tmem_base, umma_desc_kmajor(dy_s + (ks >> 2) * 16384) + kb, umma_desc_mnmajor(wo_s + ks * 2048, 16384),
                   idesc_d, ks != 0 ? 1u : 0u);
       }
+      if constexpr (MODE != 1) {
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
-        umma_bf16(tmem_base + 128, umma_desc_kmajor(dg_s + (ks >> 2) * 16384) + kb,
-                  umma_desc_mnmajor(wg_s + ks * 2048, 16384), idesc_d, ks != 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+          umma_bf16(tmem_base + 128, umma_desc_kmajor(dg_s + (ks >> 2) * 16384) + kb,
+                    umma_desc_mnmajor(wg_s + ks * 2048, 16384), idesc_d, ks != 0 ? 1u : 0u);
+        }
       }
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
@@ -366,10 +405,12 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         umma_bf16(tmem_base + 256, umma_desc_mnmajor(dy_s + ks * 2048, 16384),
                   umma_desc_kmajor(t_s + (ks >> 2) * 16384) + kb, idesc_mo, (ks != 0 ? 1u : 0u) | accum);
       }
+      if constexpr (MODE != 1) {
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        umma_bf16(tmem_base + 384, umma_desc_mnmajor(dg_s + ks * 2048, 16384), umma_desc_mnmajor(z_s + ks * 2048, 16384),
-                  idesc_mg, (ks != 0 ? 1u : 0u) | accum);
+        for (int ks = 0; ks < 8; ++ks) {
+          umma_bf16(tmem_base + 384, umma_desc_mnmajor(dg_s + ks * 2048, 16384), umma_desc_mnmajor(z_s + ks * 2048, 16384),
+                    idesc_mg, (ks != 0 ? 1u : 0u) | accum);
+        }
       }
       umma_commit(mma_bar);
     }
@@ -377,6 +418,11 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     tc_fence_after();
     // ---- phase 5: LayerNorm backward of the output normalisation, in place over t_hat; dxg over x_hat
     {
+      const bool inside = j0 + pos < p.n;
+      float2 other = make_float2(0.f, 0.f);  // MODE 2: the first launch's sums (read before the barrier below)
+      if constexpr (MODE == 2) {
+        if (inside) other = p.ln_part[static_cast<size_t>(row) * p.n + j0 + pos];
+      }
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
       for (int ch = 0; ch < kBwdChunks; ++ch) {
@@ -394,19 +440,28 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       named_bar_sync(1, kBwdThreads);
       float m1, m2;
       sum_partials(xchg, pos, m1, m2);
-      m1 *= 1.0f / 128.0f, m2 *= 1.0f / 128.0f;
+      if constexpr (MODE == 1) {
+        if (part == 0 && inside) p.ln_part[static_cast<size_t>(row) * p.n + j0 + pos] = make_float2(m1, m2);
+      } else if constexpr (MODE == 2) {
+        m1 = (m1 + other.x) * (1.0f / 256.0f), m2 = (m2 + other.y) * (1.0f / 256.0f);
+        if (part == 0 && inside) p.ln_part[static_cast<size_t>(row) * p.n + j0 + pos] = make_float2(m1, m2);
+      } else {
+        m1 *= 1.0f / 128.0f, m2 *= 1.0f / 128.0f;
+      }
       const float rs = rstd_out * 0.0625f;  // d / d t of the stored t / 16
 #pragma unroll
       for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t v[8], x[8];
         tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
-        tmem_ld8(tmem_base + lane_sel + 128 + part * kBwdCh + ch * 8, x);
+        if constexpr (MODE != 1) tmem_ld8(tmem_base + lane_sel + 128 + part * kBwdCh + ch * 8, x);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const uint32_t addr = t_s + tile_off(part * kBwdCh + ch * 8 + e, pos);
-          st_f16_sat(addr, rs * (__uint_as_float(v[e]) - m1 - ld_f16(addr) * m2));
+          if constexpr (MODE == 1) st_f16_sat(addr, __uint_as_float(v[e]));  // finished by bwd_ln_finish_kernel
+          else st_f16_sat(addr, rs * (__uint_as_float(v[e]) - m1 - ld_f16(addr) * m2));
         }
+        if constexpr (MODE != 1)
         st_chunk(z_s + tile_chunk(pos, part * kBwdChunks + ch),
                  pack_f16x2_sat(make_float2(__uint_as_float(x[0]), __uint_as_float(x[1]))),
                  pack_f16x2_sat(make_float2(__uint_as_float(x[2]), __uint_as_float(x[3]))),
@@ -421,7 +476,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
 #pragma unroll
       for (int kh = 0; kh < 2; ++kh) {
         if (j0 + kh * 64 < p.n) tma_store_3d(&map_dt, t_s + kh * 16384, j0 + kh * 64, 0, row);
-        tma_store_3d(&map_dx, z_s + kh * 16384, kh * 64, j0, row);
+        tma_store_3d(&map_dx, (MODE == 1 ? dg_s : z_s) + kh * 16384, kh * 64, j0, row);
       }
       bulk_commit();
       bulk_wait_read<0>();
@@ -468,6 +523,66 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Mean and rstd of the stored t over the 256 channels of two tensors [rows][128][N] (fp16), one thread per row and
+// group of eight columns: stats[row][j] = {mean, rsqrt(var + eps)} (eps already scaled like the stored t).
+__global__ void __launch_bounds__(256) bwd_ln_stats_kernel(const uint4* t0, const uint4* t1, int n, long long groups, float eps,
+                                                           float2* stats) {
+  const long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (g >= groups) return;
+  const int per_row = n / 8;
+  const long long row = g / per_row;
+  const int jc = static_cast<int>(g - row * per_row);
+  float pv[8], s1[8], s2[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) pv[e] = 0.f, s1[e] = 0.f, s2[e] = 0.f;
+  for (int c = 0; c < 256; ++c) {
+    const uint4* src = (c < 128 ? t0 : t1) + (row * 128 + (c & 127)) * per_row + jc;
+    const uint4 v = __ldg(src);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 x = f16x2_to_float2(w[t]);
+      if (c == 0) pv[2 * t] = x.x, pv[2 * t + 1] = x.y;
+      const float d0 = x.x - pv[2 * t], d1 = x.y - pv[2 * t + 1];
+      s1[2 * t] += d0, s1[2 * t + 1] += d1;
+      s2[2 * t] = fmaf(d0, d0, s2[2 * t]), s2[2 * t + 1] = fmaf(d1, d1, s2[2 * t + 1]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float mean = pv[e] + s1[e] * (1.0f / 256.0f);
+    const float var = fmaxf(s2[e] - s1[e] * s1[e] * (1.0f / 256.0f), 0.f) * (1.0f / 256.0f);
+    stats[row * n + jc * 8 + e] = make_float2(mean, rsqrtf(var + eps));
+  }
+}
+
+// Finishes the first tensor's gradient of the 256-channel LayerNorm backward, in place over the raw d t_hat the MODE 1
+// launch left in dt [rows][128][N] (fp16, times c): dt = rstd / 16 * (d t_hat - m1 - t_hat m2), t_hat recomputed from t.
+__global__ void __launch_bounds__(256) bwd_ln_finish_kernel(uint4* dt, const uint4* t, const float2* stats, const float2* means,
+                                                            int n, long long chunks) {
+  const long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (g >= chunks) return;
+  const int per_row = n / 8;
+  const long long rc = g / per_row;  // row * 128 + channel
+  const int jc = static_cast<int>(g - rc * per_row);
+  const long long row = rc >> 7;
+  const uint4 dv = dt[g];
+  const uint4 tv = __ldg(t + g);
+  const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w}, tw[4] = {tv.x, tv.y, tv.z, tv.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 d = f16x2_to_float2(dw[q]);
+    const float2 x = f16x2_to_float2(tw[q]);
+    const float2 st0 = stats[row * n + jc * 8 + 2 * q], st1 = stats[row * n + jc * 8 + 2 * q + 1];
+    const float2 mm0 = means[row * n + jc * 8 + 2 * q], mm1 = means[row * n + jc * 8 + 2 * q + 1];
+    const float r0 = st0.y * 0.0625f * (d.x - mm0.x - (x.x - st0.x) * st0.y * mm0.y);
+    const float r1 = st1.y * 0.0625f * (d.y - mm1.x - (x.y - st1.x) * st1.y * mm1.y);
+    o[q] = pack_f16x2_sat(make_float2(r0, r1));
+  }
+  dt[g] = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 struct BwdPrologueParams {
@@ -864,22 +979,23 @@ __global__ void __launch_bounds__(256) bwd_reduce_kernel(const float* part_m, co
 //   dW_m[r][k] = (M[m][r][k] gamma[k] + S[m][r] beta[k]) / c
 //   dgamma[k]  = sum_m sum_r W_m[r][k] M[m][r][k] / c,   dbeta[k] = sum_m sum_r W_m[r][k] S[m][r] / c
 // over the matrices that read that LayerNorm (the output one: matrix 4; the input one: the other five).
+// One call covers one set of six 128 x 128 matrices ("half": the unidirectional module has one, the bidirectional module
+// two, whose matrices are row or column blocks of the module's wider parameters, hence the leading dimensions).
 // Grid (6 matrices, 8 blocks of 16 rows), thread = column k; the LayerNorm sums leave as partials [6][8][2][128] that
 // bwd_finalize_ln_kernel adds in a fixed order.
 struct BwdFinalArgs {
-  PackArgs w;           // raw weights and LayerNorm parameters
+  PackArgs w;           // raw weights (this half's blocks, with their leading dimensions) and LayerNorm parameters
   const float* m_all;   // [6][128][128]
   const float* s_all;   // [6][128]
   const float* scale;   // [2]
-  float* dw[6];         // [128][128] fp32 each
+  float* dw[6];         // fp32 gradient blocks
+  int dw_ld[6];         // their leading dimensions
   float* ln_part;       // [6][8][2][128]
-  float* d_ln_in_w;
-  float* d_ln_in_b;
-  float* d_ln_out_w;
-  float* d_ln_out_b;
+  unsigned mask;        // bit m set: matrix m is present in this half
 };
 __global__ void __launch_bounds__(128) bwd_finalize_kernel(const BwdFinalArgs a) {
   const int k = threadIdx.x, m = blockIdx.x, rb = blockIdx.y;
+  if (((a.mask >> m) & 1u) == 0u) return;
   const float cinv = a.scale[1];
   const float gamma = (m == 4 ? a.w.ln_out_w : a.w.ln_in_w)[k];
   const float beta = (m == 4 ? a.w.ln_out_b : a.w.ln_in_b)[k];
@@ -891,29 +1007,42 @@ __global__ void __launch_bounds__(128) bwd_finalize_kernel(const BwdFinalArgs a)
                                     : __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(a.w.w[m])[wi]) << 16);
     const float mv = a.m_all[(m * 128 + r) * 128 + k] * cinv;
     const float sv = a.s_all[m * 128 + r] * cinv;
-    a.dw[m][r * 128 + k] = fmaf(mv, gamma, sv * beta);
+    a.dw[m][static_cast<size_t>(r) * a.dw_ld[m] + k] = fmaf(mv, gamma, sv * beta);
     ag = fmaf(w, mv, ag);
     ab = fmaf(w, sv, ab);
   }
   a.ln_part[((m * 8 + rb) * 2 + 0) * 128 + k] = ag;
   a.ln_part[((m * 8 + rb) * 2 + 1) * 128 + k] = ab;
 }
-__global__ void __launch_bounds__(128) bwd_finalize_ln_kernel(const BwdFinalArgs a) {
+struct BwdLnArgs {
+  const float* ln_part[2];  // per half
+  unsigned mask[2];
+  int halves;
+  float* d_ln_in_w;   // [128]
+  float* d_ln_in_b;
+  float* d_ln_out_w;  // [128 * halves]: half h at + 128 h
+  float* d_ln_out_b;
+};
+__global__ void __launch_bounds__(128) bwd_finalize_ln_kernel(const BwdLnArgs a) {
   const int k = threadIdx.x;
-  float g_in = 0.f, b_in = 0.f, g_out = 0.f, b_out = 0.f;
-  for (int m = 0; m < 6; ++m) {
-    float ag = 0.f, ab = 0.f;
-    for (int rb = 0; rb < 8; ++rb) {
-      ag += a.ln_part[((m * 8 + rb) * 2 + 0) * 128 + k];
-      ab += a.ln_part[((m * 8 + rb) * 2 + 1) * 128 + k];
+  float g_in = 0.f, b_in = 0.f;
+  for (int h = 0; h < a.halves; ++h) {
+    float g_out = 0.f, b_out = 0.f;
+    for (int m = 0; m < 6; ++m) {
+      if (((a.mask[h] >> m) & 1u) == 0u) continue;
+      float ag = 0.f, ab = 0.f;
+      for (int rb = 0; rb < 8; ++rb) {
+        ag += a.ln_part[h][((m * 8 + rb) * 2 + 0) * 128 + k];
+        ab += a.ln_part[h][((m * 8 + rb) * 2 + 1) * 128 + k];
+      }
+      if (m == 4) g_out += ag, b_out += ab;
+      else g_in += ag, b_in += ab;
     }
-    if (m == 4) g_out += ag, b_out += ab;
-    else g_in += ag, b_in += ab;
+    a.d_ln_out_w[h * 128 + k] = g_out;
+    a.d_ln_out_b[h * 128 + k] = b_out;
   }
   a.d_ln_in_w[k] = g_in;
   a.d_ln_in_b[k] = b_in;
-  a.d_ln_out_w[k] = g_out;
-  a.d_ln_out_b[k] = b_out;
 }
 
 }  // namespace trimul

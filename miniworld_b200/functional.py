@@ -517,9 +517,10 @@ def trimul_forward(
     return out
 
 
-def backward_workspace_bytes(B: int, N: int) -> int:
+def backward_workspace_bytes(B: int, N: int, outgoing: Optional[bool] = True) -> int:
     out = c_size_t(0)
-    _lib.check(_lib.load().b200_trimul_backward_workspace_bytes(B, N, ctypes.byref(out)), "b200_trimul_backward_workspace_bytes")
+    _lib.check(_lib.load().b200_trimul_backward_workspace_bytes(B, N, _direction(outgoing), ctypes.byref(out)),
+               "b200_trimul_backward_workspace_bytes")
     return int(out.value)
 
 
@@ -530,7 +531,7 @@ def trimul_backward(
     forward_workspace: torch.Tensor,
     mask: Optional[torch.Tensor] = None,
     *,
-    outgoing: bool = True,
+    outgoing: Optional[bool] = True,
     eps_in: float = 1e-5,
     eps_out: float = 1e-5,
     pair_mask: Optional[torch.Tensor] = None,
@@ -540,10 +541,12 @@ def trimul_backward(
     workspace: Optional[torch.Tensor] = None,
     check: bool = False,
 ):
-    """Backward of :func:`trimul_forward` for the unidirectional module (``b200_trimul_backward``).
+    """Backward of :func:`trimul_forward` for d_pair = d_hidden = 128 (``b200_trimul_backward``); ``outgoing=None`` is
+    the bidirectional module.
 
-    ``forward_workspace`` is the workspace the forward call used for the same inputs (it holds ``left``, ``right``,
-    ``tri``). Returns ``(dz bf16 [B,N,N,128], grads)`` with ``grads`` a dict of fp32 tensors under the parameter keys.
+    ``forward_workspace`` is the workspace the forward call used for the same inputs (it holds the stage tensors).
+    Returns ``(dz bf16 [B,N,N,128], grads)`` with ``grads`` a dict of fp32 tensors of the parameters' shapes under the
+    parameter keys.
     """
     B, N = _check_z(z)
     if z.shape[1] != N:
@@ -555,13 +558,14 @@ def trimul_backward(
     dy = dy.contiguous()
     if not z.is_contiguous():
         raise RuntimeError("the pair tensor must be contiguous")
-    w = _Weights(params, biases, dev)
+    bidir = outgoing is None
+    w = _Weights(params, biases, dev, bidirectional=bidir)
     ds = None
     if drop_scale is not None:
         if drop_scale.numel() != B * N * D or drop_scale.shape[-1] != D or drop_scale.shape[0] != B:
             raise RuntimeError(f"drop_scale must be [B, 1, N, {D}], got {tuple(drop_scale.shape)}")
         ds = drop_scale.detach().to(device=dev, dtype=torch.bfloat16).contiguous()
-    need = backward_workspace_bytes(B, N)
+    need = backward_workspace_bytes(B, N, outgoing)
     if workspace is None:
         workspace = aligned_empty(need, dev)
     elif workspace.numel() * workspace.element_size() < need:
@@ -571,8 +575,10 @@ def trimul_backward(
     tm = as_mask_u8(mask, dev)
     pm = as_mask_u8(pair_mask, dev)
     dz = torch.empty_like(z)
-    dws = [torch.empty(D, D, dtype=torch.float32, device=dev) for _ in range(6)]
-    dln = [torch.empty(D, dtype=torch.float32, device=dev) for _ in range(4)]
+    wide = 2 * D if bidir else D
+    shapes = [(wide, D)] * 4 + [(D, D), (D, wide)]
+    dws = [torch.empty(sh, dtype=torch.float32, device=dev) for sh in shapes]
+    dln = [torch.empty(n, dtype=torch.float32, device=dev) for n in (D, D, wide, wide)]
     dw_arr = (c_void_p * 6)(*[t.data_ptr() for t in dws])
     with torch.cuda.device(dev):
         rc = _lib.load().b200_trimul_backward(

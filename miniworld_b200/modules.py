@@ -217,7 +217,7 @@ class TriangleMultiplication(nn.Module):
         return ws
 
     def _backward_supported(self) -> bool:
-        return not self._bidirectional and self.d_pair == D_SUPPORTED and self.d_hidden == D_SUPPORTED
+        return self.d_pair == D_SUPPORTED and self.d_hidden == D_SUPPORTED
 
     def _run(self, pair: torch.Tensor, token_mask, pair_mask) -> torch.Tensor:
         # the differentiable path is taken when the input requires grad, or in training mode when a parameter does
@@ -227,7 +227,7 @@ class TriangleMultiplication(nn.Module):
         if train and not self._backward_supported():
             if pair.requires_grad:
                 raise NotImplementedError(
-                    "backward is implemented for the unidirectional module with d_pair = d_hidden = 128 only: call under "
+                    "backward is implemented for d_pair = d_hidden = 128 only: call under "
                     "torch.no_grad() or with an input that does not require grad"
                 )
             train = False
@@ -307,7 +307,7 @@ class TriangleMultiplication(nn.Module):
             if pair_mask is not None:
                 pair_mask = nn.functional.pad(pair_mask.to(z.device) != 0, (0, pad, 0, pad))
         y = trimul_train(
-            z, self._params(), token_mask, outgoing=self.outgoing, eps_in=float(self.ln_pair.eps),
+            z, self._params(), token_mask, outgoing=self._direction(), eps_in=float(self.ln_pair.eps),
             eps_out=float(self.ln_out.eps), pair_mask=pair_mask, residual=self.residual, biases=self._biases,
             drop_scale=scale, check=self.check_status,
         )

@@ -65,11 +65,13 @@ class TriMulFunction(torch.autograd.Function):
         return tuple(out)
 
 
-def trimul_train(z: torch.Tensor, params: dict, token_mask: Optional[torch.Tensor] = None, *, outgoing: bool = True,
+def trimul_train(z: torch.Tensor, params: dict, token_mask: Optional[torch.Tensor] = None, *,
+                 outgoing: Optional[bool] = True,
                  eps_in: float = 1e-5, eps_out: float = 1e-5, pair_mask: Optional[torch.Tensor] = None,
                  residual: bool = True, biases: Optional[dict] = None, drop_scale: Optional[torch.Tensor] = None,
                  check: bool = False) -> torch.Tensor:
-    """Differentiable forward: ``z`` [B, N, N, 128] bf16 (N a multiple of 8) and the ten parameters may require grad."""
-    cfg = {"outgoing": bool(outgoing), "eps_in": float(eps_in), "eps_out": float(eps_out), "residual": bool(residual),
+    """Differentiable forward: ``z`` [B, N, N, 128] bf16 (N a multiple of 8) and the ten parameters may require grad;
+    ``outgoing=None`` is the bidirectional module (parameters of its wider shapes)."""
+    cfg = {"outgoing": None if outgoing is None else bool(outgoing), "eps_in": float(eps_in), "eps_out": float(eps_out), "residual": bool(residual),
            "biases": biases, "check": bool(check)}
     return TriMulFunction.apply(z, token_mask, pair_mask, drop_scale, cfg, *[params[k] for k in _PARAM_KEYS])

@@ -237,6 +237,7 @@ def bidir_forward_stages(
     pair_mask: Optional[torch.Tensor] = None,
     residual: bool = True,
     drop_scale: Optional[torch.Tensor] = None,
+    differentiable: bool = False,
 ) -> Stages:
     """fp32 forward of BidirectionalTriangleMultiplication (``docs/paper/supplement.tex:125-136`` of the
     reference project; the module MiniWorld's trunk builds, ``src/miniworld/modules/mini_pairformer.py:76-80``).
@@ -247,8 +248,9 @@ def bidir_forward_stages(
     ``to_gate`` [C, C] on the normalised input, residual included. Mask semantics as in the unidirectional
     module: the pair validity multiplies l and r only.
     """
-    p = {k: v.detach().to(torch.float32) for k, v in params.items()}
-    zf = z.detach().to(torch.float32)
+    keep = (lambda v: v.to(torch.float32)) if differentiable else (lambda v: v.detach().to(torch.float32))
+    p = {k: keep(v) for k, v in params.items()}
+    zf = keep(z)  # differentiable: z and params stay attached to the autograd graph (the backward oracle)
     B, N, N2, C = zf.shape
     assert N == N2
     H2 = p["to_left.weight"].shape[0]

@@ -171,3 +171,84 @@ def test_gradients_at_crop_384():
     _check("dz", zd.grad, dz_ref)
     for k in _PARAM_KEYS:
         _check(k, pd[k].grad, gp_ref[k])
+
+
+def _bidir_params(seed, beta_scale=0.05):
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *sh: torch.randn(*sh, generator=g)  # noqa: E731
+    bf = torch.bfloat16
+    return {
+        "ln_pair.weight": 1.0 + 0.1 * rn(128), "ln_pair.bias": beta_scale * rn(128),
+        "to_left.weight": (rn(256, 128) * 128**-0.5).to(bf), "to_left_gate.weight": (rn(256, 128) * 128**-0.5).to(bf),
+        "to_right.weight": (rn(256, 128) * 128**-0.5).to(bf), "to_right_gate.weight": (rn(256, 128) * 128**-0.5).to(bf),
+        "ln_out.weight": 1.0 + 0.1 * rn(256), "ln_out.bias": beta_scale * rn(256),
+        "to_gate.weight": (rn(128, 128) * 128**-0.5).to(bf), "to_out.weight": (rn(128, 256) * 256**-0.5).to(bf),
+    }
+
+
+def _bidir_oracle_grads(z, p, mask, dy, **kw):
+    zf = z.detach().float().requires_grad_(True)
+    pf = {k: v.detach().clone().float().requires_grad_(True) for k, v in p.items()}
+    y = oracle.bidir_forward(zf, pf, mask, differentiable=True, **kw)
+    y.backward(dy.float())
+    return y.detach(), zf.grad, {k: v.grad for k, v in pf.items()}
+
+
+@pytest.mark.parametrize("N,mask_kind", [(64, "none"), (136, "random"), (200, "holes"), (384, "random")])
+def test_bidirectional_gradients_match_the_oracle(N, mask_kind):
+    """The module MiniWorld's trunk builds (256 contracted channels, one LayerNorm over them): gradients for the input
+    and all ten parameters of the wide shapes, as the reference validates its own backward
+    (docs/archive/engine2-validation-20260923/validate_bidir_reference.py:11-38 in the reference project: L = 384,
+    random token mask, relative L2 of every gradient)."""
+    p = _bidir_params(600 + N)
+    g = torch.Generator().manual_seed(601 + N)
+    z = torch.randn(1, N, N, 128, generator=g).to(torch.bfloat16)
+    dy = (torch.randn(1, N, N, 128, generator=g) * 0.01).to(torch.bfloat16)
+    mask = None
+    if mask_kind == "random":
+        mask = torch.rand(1, N, generator=g) > 0.2
+    elif mask_kind == "holes":
+        mask = torch.ones(1, N, dtype=torch.bool)
+        mask[:, ::3] = False
+    y_ref, dz_ref, gp_ref = _bidir_oracle_grads(z, p, mask, dy)
+    zd = z.to(DEV).requires_grad_(True)
+    pd = {k: v.detach().to(DEV).requires_grad_(True) for k, v in p.items()}
+    y = trimul_train(zd, pd, None if mask is None else mask.to(DEV), outgoing=None, check=True)
+    y.backward(dy.to(DEV))
+    _check("y", y, y_ref, 5e-3)
+    _check("dz", zd.grad, dz_ref)
+    for k in _PARAM_KEYS:
+        assert pd[k].grad is not None and pd[k].grad.shape == pd[k].shape, k
+        _check(k, pd[k].grad, gp_ref[k])
+
+
+def test_bidirectional_module_training_step_dropout_zero_gamma_and_determinism():
+    """`BidirectionalTriangleMultiplication` in training mode: every third gamma of both LayerNorms zero, a fixed
+    row-shared dropout scale, N not a multiple of 8, a batch of two; two backward passes are bit-identical."""
+    N = 77
+    p = _bidir_params(620)
+    p["ln_pair.weight"][::3] = 0
+    p["ln_out.weight"][::3] = 0
+    g = torch.Generator().manual_seed(621)
+    z = torch.randn(2, N, N, 128, generator=g).to(torch.bfloat16)
+    dy = (torch.randn(2, N, N, 128, generator=g) * 0.5).to(torch.bfloat16)
+    mask = torch.rand(2, N, generator=g) > 0.2
+    scale = ((torch.rand(2, 1, N, 128, generator=g) > 0.25).float() / 0.75).to(torch.bfloat16)
+    y_ref, dz_ref, gp_ref = _bidir_oracle_grads(z, p, mask, dy, drop_scale=scale)
+    m = mw.BidirectionalTriangleMultiplication(128, p_drop=0.25, check_status=True)
+    m.load_state_dict(p)
+    m = m.to(DEV).to(torch.bfloat16).train()
+    m._make_drop_row_scale = lambda pair, pdrop: scale.to(DEV)
+    grads = []
+    for _ in range(2):
+        m.zero_grad()
+        zd = z.to(DEV).requires_grad_(True)
+        y = m(zd, mask.to(DEV))
+        y.backward(dy.to(DEV))
+        grads.append((zd.grad.clone(), {k: v.grad.clone() for k, v in m.named_parameters()}))
+    _check("y", y, y_ref, 5e-3)
+    _check("dz", grads[0][0], dz_ref)
+    for k in _PARAM_KEYS:
+        _check(k, grads[0][1][k], gp_ref[k])
+        assert torch.equal(grads[0][1][k], grads[1][1][k]), k
+    assert torch.equal(grads[0][0], grads[1][0])

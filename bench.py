@@ -581,24 +581,26 @@ def block_operators(r: "Runner", steps: int, stream, dev) -> dict:
             out[name] = entry
     if bid.device_status() != 0 or tr.device_status() != 0:
         raise SystemExit("bidirectional / transition forward reported a device status")
-    out["training"] = training_step(r, steps, stream, dev)
+    out["training"] = training_step(r, steps, stream, dev, bid)
     return out
 
 
-def training_step(r: "Runner", steps: int, stream, dev) -> dict:
-    """CUDA-event times of one training step of the unidirectional module on the headline input: the differentiable
-    forward (stage tensors kept) and ``b200_trimul_backward`` (gradients of the input and all ten parameters)."""
+def training_step(r: "Runner", steps: int, stream, dev, bid) -> dict:
+    """CUDA-event times of one training step on the headline input, for the two unidirectional modules and for the
+    bidirectional one: the forward with its stage tensors kept, and ``b200_trimul_backward`` (gradients of the input and
+    all ten parameters)."""
     from miniworld_b200 import functional as F_
 
     B, N, z, mask = r.B, r.N, r.z, r.mask
     gen = torch.Generator(device=dev).manual_seed(78)
     dy = (torch.randn(z.shape, generator=gen, device=dev) * 0.01).to(torch.bfloat16)
     res = {"workload": r.name}
-    for direction in r.w.directions:
-        outgoing = direction == "outgoing"
-        params = {k: v.detach() for k, v in r.mods[direction]._params().items()}
+    for direction in tuple(r.w.directions) + ("bidirectional",):
+        outgoing = None if direction == "bidirectional" else direction == "outgoing"
+        mod = bid if outgoing is None else r.mods[direction]
+        params = {k: v.detach() for k, v in mod._params().items()}
         ws = F_.aligned_empty(F_.workspace_bytes(B, N, outgoing), dev)
-        bws = F_.aligned_empty(F_.backward_workspace_bytes(B, N), dev)
+        bws = F_.aligned_empty(F_.backward_workspace_bytes(B, N, outgoing), dev)
         y = torch.empty_like(z)
 
         def fwd():

@@ -17,9 +17,8 @@ shapes.
 
 In training mode with ``p_drop > 0`` the forward applies the row-shared dropout of the reference
 (``x + drop_row(f(x))``: one keep-mask per (batch, column, channel), shared by all rows,
-``src/miniworld/blocks/template.py:38-40``). The unidirectional module with d_pair = d_hidden = 128 is differentiable
-(input and all ten parameters, :mod:`miniworld_b200.training`); the bidirectional module, the 64-wide modules and the
-Transition have no backward: calling them with gradients enabled on an input that requires them raises
+``src/miniworld/blocks/template.py:38-40``). The modules with d_pair = d_hidden = 128 (unidirectional and bidirectional) are differentiable
+(input and all ten parameters, :mod:`miniworld_b200.training`); the 64-wide modules and the Transition have no backward: calling them with gradients enabled on an input that requires them raises
 ``NotImplementedError``.
 """
 

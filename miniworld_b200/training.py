@@ -1,5 +1,6 @@
-"""Training path of the unidirectional triangle update: forward on the library's kernels with the stage tensors
-kept, backward for the input and all ten parameters through ``b200_trimul_backward``.
+"""Training path of the triangle update (d_pair = d_hidden = 128, unidirectional and bidirectional): forward on the
+library's kernels with the stage tensors kept, backward for the input and all ten parameters through
+``b200_trimul_backward``.
 
 The reference's backward is stages B1-B12 of ``docs/kernels/trimul/TRIMUL_STATUS.md:43-52`` (reference project): its
 LayerNorm / projection gradients are CUDA kernels and its contraction gradients cuBLAS calls. Here all of it runs on

@@ -212,11 +212,11 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t wo_s = smem_base, wg_s = smem_base + kBwdTile;
-  const uint32_t t_s = smem_base + 2 * kBwdTile, z_s = t_s + kBwdTile, dy_s = z_s + kBwdTile, dg_s = dy_s + kBwdTile;
+  const uint32_t tiles_s = smem_base + 2 * kBwdTile;  // four tile buffers whose roles rotate from tile to tile
   const uint32_t xchg = smem_base + 6 * kBwdTile;
   const uint32_t const_s = xchg + 4096;
   const uint32_t bar_base = const_s + 1024;
-  const uint32_t w_full = bar_base, in_full = bar_base + 8, mma_bar = bar_base + 16;
+  const uint32_t w_full = bar_base, tz_full = bar_base + 8, mma_bar = bar_base + 16, dy_full = bar_base + 24;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + 4096 + 1024 + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + 4096);
@@ -228,7 +228,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
-    mbar_init(in_full, 1);
+    mbar_init(tz_full, 1);
+    mbar_init(dy_full, 1);
     mbar_init(mma_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -261,25 +262,36 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
 #pragma unroll
   for (int c = 0; c < kBwdCh; ++c) acc_so[c] = 0.f, acc_sg[c] = 0.f;
 
+  // Buffer roles of tile `it`: t, z, dy, dgate = buffers (0, 1, 2, 3) for even it and (2, 3, 0, 1) for odd it. The
+  // outputs of a tile are written over its t and z buffers and stored from there; its dy and dgate buffers are free
+  // once the gradient GEMMs are done, and receive the next tile's t and z while this tile finishes. The next tile's dy
+  // goes into this tile's t buffer as soon as the store has read it.
+  auto issue_tz = [&](int tile_i, int it_i) {
+    const int row_i = tile_i / p.tiles_per_row;
+    const int j_i = (tile_i - row_i * p.tiles_per_row) * 128;
+    const uint32_t t_i = tiles_s + ((it_i & 1) * 2) * kBwdTile, z_i = t_i + kBwdTile;
+    mbar_arrive_expect_tx(tz_full, 2 * kBwdTile);
+#pragma unroll
+    for (int kh = 0; kh < 2; ++kh) {
+      tma_load_3d(t_i + kh * 16384, &map_t, tz_full, j_i + kh * 64, 0, row_i);
+      tma_load_3d(z_i + kh * 16384, &map_z, tz_full, kh * 64, j_i, row_i);
+    }
+  };
   bool ok = true;
   int it = 0;
-  bool loads_pending = false;
+  int tz_pending = -1, dy_pending = -1;  // thread 0: iteration whose copies are in flight, or -1
+  if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < p.num_tiles) {
+    issue_tz(blockIdx.x, 0);
+    tz_pending = 0;
+  }
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
     const int row = tile / p.tiles_per_row;
     const int j0 = (tile - row * p.tiles_per_row) * 128;
-    if (threadIdx.x == 0) {
-      mbar_arrive_expect_tx(in_full, 3 * kBwdTile);
-#pragma unroll
-      for (int kh = 0; kh < 2; ++kh) {
-        tma_load_3d(t_s + kh * 16384, &map_t, in_full, j0 + kh * 64, 0, row);
-        tma_load_3d(z_s + kh * 16384, &map_z, in_full, kh * 64, j0, row);
-        tma_load_3d(dy_s + kh * 16384, &map_dy, in_full, kh * 64, j0, row);
-      }
-      loads_pending = true;
-    }
+    const uint32_t t_s = tiles_s + ((it & 1) * 2) * kBwdTile, z_s = t_s + kBwdTile;
+    const uint32_t dy_s = tiles_s + (((it & 1) ^ 1) * 2) * kBwdTile, dg_s = dy_s + kBwdTile;
     if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
-    if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
-    loads_pending = false;
+    if (!cta_wait(tz_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    if (threadIdx.x == 0) tz_pending = -1;
     // ---- phase 1: normalise t (rows = channels) and z (rows = positions) in place
     float rstd_out;
     if constexpr (MODE == 0) {
@@ -294,6 +306,15 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         const uint32_t addr = t_s + tile_off(part * kBwdCh + cc, pos);
         st_f16_sat(addr, fmaf(ld_f16(addr), st.y, nmr));
       }
+    }
+    if (threadIdx.x == 0) {
+      // this tile's dy and dgate buffers held the previous tile's outputs: their store (issued a normalisation pass
+      // ago) must have read them before the dy copy lands there
+      bulk_wait_read<0>();
+      mbar_arrive_expect_tx(dy_full, kBwdTile);
+#pragma unroll
+      for (int kh = 0; kh < 2; ++kh) tma_load_3d(dy_s + kh * 16384, &map_dy, dy_full, kh * 64, j0, row);
+      dy_pending = it;
     }
     normalise_tile<true, true>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
@@ -319,6 +340,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       umma_commit(mma_bar);
     }
     if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
+    if (!cta_wait(dy_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    if (threadIdx.x == 0) dy_pending = -1;
     tc_fence_after();
     // ---- phase 3: dproj = c du gate, dgate = c du proj gate (1 - gate); du = dy (* dropout scale)
     {
@@ -371,7 +394,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
           og[t] = pack_f16x2_sat(make_float2(dgv[0], dgv[1]));
         }
         st_chunk(dy_s + addr, op[0], op[1], op[2], op[3]);
-        st_chunk(dg_s + addr, og[0], og[1], og[2], og[3]);
+        // MODE 1: the part of proj leaves through the z buffer (x_hat is only needed by the G GEMM, which is done)
+        st_chunk((MODE == 1 ? z_s : dg_s) + addr, og[0], og[1], og[2], og[3]);
       }
     }
     tc_fence_before();
@@ -416,6 +440,10 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     }
     if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
+    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
+      issue_tz(tile + gridDim.x, it + 1);  // into this tile's dy and dgate buffers, which the GEMMs have finished with
+      tz_pending = it + 1;
+    }
     // ---- phase 5: LayerNorm backward of the output normalisation, in place over t_hat; dxg over x_hat
     {
       const bool inside = j0 + pos < p.n;
@@ -476,16 +504,16 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
 #pragma unroll
       for (int kh = 0; kh < 2; ++kh) {
         if (j0 + kh * 64 < p.n) tma_store_3d(&map_dt, t_s + kh * 16384, j0 + kh * 64, 0, row);
-        tma_store_3d(&map_dx, (MODE == 1 ? dg_s : z_s) + kh * 16384, kh * 64, j0, row);
+        tma_store_3d(&map_dx, z_s + kh * 16384, kh * 64, j0, row);
       }
       bulk_commit();
-      bulk_wait_read<0>();
     }
   }
   if (threadIdx.x == 0) {
-    if (loads_pending) {  // a wait gave up with copies in flight: they must land before the CTA exits
+    if (!ok) {  // a wait gave up: copies in flight must land before the CTA exits
       const long long t0 = clock64();
-      while (!mbar_try_wait(in_full, it & 1) || !mbar_try_wait(w_full, 0)) {
+      while (!mbar_try_wait(w_full, 0) || (tz_pending >= 0 && !mbar_try_wait(tz_full, tz_pending & 1)) ||
+             (dy_pending >= 0 && !mbar_try_wait(dy_full, dy_pending & 1))) {
         if (clock64() - t0 > kWaitLimitCycles) {
           atomicCAS(p.status, 0, kDevTimeoutDrain);
           break;
@@ -615,7 +643,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t wv_s = smem_base, wg_s = smem_base + kBwdTile;
-  const uint32_t z_s = smem_base + 2 * kBwdTile, do_s = z_s + kBwdTile, dv_s = do_s + kBwdTile, dg_s = dv_s + kBwdTile;
+  const uint32_t tiles_s = smem_base + 2 * kBwdTile;  // four tile buffers whose roles rotate from tile to tile
   const uint32_t xchg = smem_base + 6 * kBwdTile;
   const uint32_t const_s = xchg + 4096;
   const uint32_t bar_base = const_s + 1024;
@@ -662,24 +690,39 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 #pragma unroll
   for (int c = 0; c < kBwdCh; ++c) acc_sv[c] = 0.f, acc_sg[c] = 0.f;
 
+  // Buffer roles (z, dO, dvalue, dgate) of tile `it`, one nibble each, period 4: the next tile's z and dO are copied
+  // into this tile's dO buffer (free after phase 3) and dgate buffer (free after the gradient GEMMs) while this tile
+  // finishes; its dvalue scratch is this tile's z buffer and its dgate scratch this tile's dvalue buffer, which holds
+  // the output until the store has read it.
+  auto role = [&](int it_i, int r) {
+    const uint32_t rr = static_cast<uint32_t>(0x1302012320313210ull >> (16 * (it_i & 3))) & 0xFFFFu;
+    return tiles_s + ((rr >> (4 * r)) & 0xFu) * kBwdTile;
+  };
+  auto issue_in = [&](int tile_i, int it_i) {
+    const int row_i = tile_i / p.tiles_per_row;
+    const int j_i = (tile_i - row_i * p.tiles_per_row) * 128;
+    const uint32_t z_i = role(it_i, 0), do_i = role(it_i, 1);
+    mbar_arrive_expect_tx(in_full, 2 * kBwdTile);
+#pragma unroll
+    for (int kh = 0; kh < 2; ++kh) {
+      tma_load_3d(z_i + kh * 16384, &map_z, in_full, kh * 64, j_i, row_i);
+      tma_load_3d(do_i + kh * 16384, &map_do, in_full, j_i + kh * 64, 0, row_i);
+    }
+  };
   bool ok = true;
   int it = 0;
-  bool loads_pending = false;
+  int in_pending = -1;  // thread 0: iteration whose copies are in flight, or -1
+  if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < p.num_tiles) {
+    issue_in(blockIdx.x, 0);
+    in_pending = 0;
+  }
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
     const int row = tile / p.tiles_per_row;
     const int j0 = (tile - row * p.tiles_per_row) * 128;
-    if (threadIdx.x == 0) {
-      mbar_arrive_expect_tx(in_full, 2 * kBwdTile);
-#pragma unroll
-      for (int kh = 0; kh < 2; ++kh) {
-        tma_load_3d(z_s + kh * 16384, &map_z, in_full, kh * 64, j0, row);
-        tma_load_3d(do_s + kh * 16384, &map_do, in_full, j0 + kh * 64, 0, row);
-      }
-      loads_pending = true;
-    }
+    const uint32_t z_s = role(it, 0), do_s = role(it, 1), dv_s = role(it, 2), dg_s = role(it, 3);
     if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
-    loads_pending = false;
+    if (threadIdx.x == 0) in_pending = -1;
     // ---- phase 1: x_hat in place
     const float rstd_in = normalise_tile<true, true>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
@@ -687,6 +730,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     __syncthreads();
     // ---- phase 2: value = x_hat Wv'^T (columns 0-127), gate = x_hat Wg'^T (128-255)
     if (threadIdx.x == 0) {
+      // this tile's dgate scratch held the previous tile's output: its store must have read it before phase 3
+      bulk_wait_read<0>();
       tc_fence_after();
       constexpr uint32_t idesc = umma_idesc(128, 128, false, false, kFmtF16, kFmtF16);
 #pragma unroll
@@ -767,6 +812,10 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     }
     if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
+    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
+      issue_in(tile + gridDim.x, it + 1);  // into this tile's dO and dgate buffers
+      in_pending = it + 1;
+    }
     // ---- phase 5: add the running d x_hat; !LAST: write it back, LAST: LayerNorm backward + residual -> dz
     {
       const bool inside = j < p.n;
@@ -839,13 +888,12 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 #pragma unroll
       for (int kh = 0; kh < 2; ++kh) tma_store_3d(&map_out, dv_s + kh * 16384, kh * 64, j0, row);
       bulk_commit();
-      bulk_wait_read<0>();
     }
   }
   if (threadIdx.x == 0) {
-    if (loads_pending) {
+    if (!ok) {  // a wait gave up: copies in flight must land before the CTA exits
       const long long t0 = clock64();
-      while (!mbar_try_wait(in_full, it & 1) || !mbar_try_wait(w_full, 0)) {
+      while (!mbar_try_wait(w_full, 0) || (in_pending >= 0 && !mbar_try_wait(in_full, in_pending & 1))) {
         if (clock64() - t0 > kWaitLimitCycles) {
           atomicCAS(p.status, 0, kDevTimeoutDrain);
           break;

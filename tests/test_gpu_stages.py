@@ -74,7 +74,7 @@ def test_pack_weights(wdtype):
 
 
 @pytest.mark.parametrize("outgoing", [True, False])
-@pytest.mark.parametrize("B,N", [(1, 16), (2, 64), (1, 136), (1, 256), (1, 384), (1, 200)])
+@pytest.mark.parametrize("B,N", [(1, 16), (2, 64), (1, 136), (1, 256), (1, 384), (1, 200), (1, 512), (1, 768)])
 def test_contract_matches_einsum(B, N, outgoing):
     g = torch.Generator().manual_seed(100 + N)
     left = torch.randn(B, N, 128, N, generator=g).to(torch.float16).to(DEV)

@@ -290,7 +290,9 @@ int b200_trimul_forward_static(const void* z, const void* w_left, const void* w_
                                void* cuda_stream);
 
 /*
- * Backward for d_pair = d_hidden = 128: the reference's training path, stages B1-B12 of
+ * Backward, for every width the forward takes (d_pair = d_hidden = 128; d_pair = 64 with d_hidden = 128 for one direction
+ * or 64 per direction for direction 0, where dz is [B, N, N, 64], the gradients have the parameters' shapes of the
+ * forward's d_pair = 64 note, and drop_scale must be null): the reference's training path, stages B1-B12 of
  * docs/kernels/trimul/TRIMUL_STATUS.md:43-52 (its B5-B6, the contraction gradients, are cuBLAS calls there). Given
  * dy = d loss / d y ([B, N, N, 128] bf16), the inputs of the forward call and the workspace that
  * b200_trimul_forward / _forward_ex left behind for these inputs (it holds the stage tensors), it writes
@@ -318,8 +320,8 @@ int b200_trimul_backward(const void* dy, const void* z, const void* w_left, cons
                          const void* const* bias_opt, const uint8_t* token_mask, const uint8_t* pair_mask,
                          const void* drop_scale, const void* forward_workspace, void* dz, void* const* dw,
                          float* d_ln_in_w, float* d_ln_in_b, float* d_ln_out_w, float* d_ln_out_b, void* workspace,
-                         size_t workspace_bytes, int B, int N, int direction, float eps_in, float eps_out, int residual,
-                         void* cuda_stream);
+                         size_t workspace_bytes, int B, int N, int d_pair, int d_hidden, int direction, float eps_in,
+                         float eps_out, int residual, void* cuda_stream);
 
 /*
  * Pair Transition, the operator on the other side of the triangle update in every block

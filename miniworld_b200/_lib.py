@@ -46,7 +46,7 @@ SIGNATURES = {
     "b200_trimul_backward": (
         c_int,
         [c_void_p] * 8 + [c_int] + [c_void_p] * 4 + [c_void_p] * 5 + [c_void_p] * 2 + [c_void_p] * 4
-        + [c_void_p, c_size_t, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
+        + [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
     ),
     "b200_trimul_contract_partial": (
         c_int,

@@ -30,7 +30,8 @@ constexpr int kBwdThreads = 128 * kBwdParts;
 constexpr int kBwdCh = 128 / kBwdParts;          // channels per thread
 constexpr int kBwdChunks = kBwdCh / 8;           // 16-byte chunks (8 channels) per thread
 constexpr int kBwdTile = 32768;  // one [128][128] 16-bit tile
-constexpr int kBwdSmemBytes = 6 * kBwdTile + 4096 /* exchange */ + 1024 /* constants */ + 256 /* barriers */ + 1024;
+constexpr int kBwdXchg = kBwdParts * 128 * 8;  // float2 [kBwdParts][128]
+constexpr int kBwdSmemBytes = 6 * kBwdTile + kBwdXchg + 1024 /* constants */ + 256 /* barriers */ + 1024;
 
 // swizzled byte offset of element (r, e) in a [128 rows][128 elements] 16-bit tile stored as two halves of 64 elements,
 // each [128 rows][128 bytes] with the 128-byte TMA swizzle
@@ -67,16 +68,18 @@ __device__ __forceinline__ bool cta_wait(uint32_t bar, uint32_t parity, volatile
   return named_bar_and(1, kBwdThreads, got);
 }
 
-// Normalise the 128 channels of every position of a tile in place (fp16 result), the thread covering 64 of them.
+// Normalise the CT channels of every position of a tile in place (fp16 result), the thread covering CT / kBwdParts of them.
 // ROWS_ARE_POSITIONS: element (pos, c) (a [pos][c] tile, input bf16 or fp16), else element (c, pos) (a [c][pos] tile,
 // fp16). Returns rstd of the thread's position. `xchg` holds float2 [kBwdParts][128].
-template <bool ROWS_ARE_POSITIONS, bool IN_BF16>
+template <bool ROWS_ARE_POSITIONS, bool IN_BF16, int CT = 128>
 __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, int pos, int part, float eps) {
+  constexpr int kCh = CT / kBwdParts;  // channels per thread
+  constexpr int kChunks = kCh / 8;
   float pv = 0.f, s1 = 0.f, s2 = 0.f;
   if constexpr (ROWS_ARE_POSITIONS) {
 #pragma unroll
-    for (int ch = 0; ch < kBwdChunks; ++ch) {
-      const uint4 v = ld_chunk(tile + tile_chunk(pos, part * kBwdChunks + ch));
+    for (int ch = 0; ch < kChunks; ++ch) {
+      const uint4 v = ld_chunk(tile + tile_chunk(pos, part * kChunks + ch));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
@@ -89,16 +92,16 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
     }
   } else {
 #pragma unroll 8
-    for (int cc = 0; cc < kBwdCh; ++cc) {
-      const float x = ld_f16(tile + tile_off(part * kBwdCh + cc, pos));
+    for (int cc = 0; cc < kCh; ++cc) {
+      const float x = ld_f16(tile + tile_off(part * kCh + cc, pos));
       if (cc == 0) pv = x;
       const float d = x - pv;
       s1 += d;
       s2 = fmaf(d, d, s2);
     }
   }
-  const float mean_h = pv + s1 * (1.0f / kBwdCh);
-  const float m2_h = fmaxf(s2 - s1 * s1 * (1.0f / kBwdCh), 0.f);
+  const float mean_h = pv + s1 * (1.0f / kCh);
+  const float m2_h = fmaxf(s2 - s1 * s1 * (1.0f / kCh), 0.f);
   asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(mean_h), "f"(m2_h) : "memory");
   named_bar_sync(1, kBwdThreads);
   // merge the equal-sized partials of this position: mean of means, M2 = sum M2_k + n_k sum (mean_k - mean)^2
@@ -112,13 +115,13 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
   }
   mean *= 1.0f / kBwdParts;
 #pragma unroll
-  for (int k = 0; k < kBwdParts; ++k) m2 = fmaf(static_cast<float>(kBwdCh) * (mk[k] - mean), mk[k] - mean, m2);
-  const float rstd = rsqrtf(m2 * (1.0f / 128.0f) + eps);
+  for (int k = 0; k < kBwdParts; ++k) m2 = fmaf(static_cast<float>(kCh) * (mk[k] - mean), mk[k] - mean, m2);
+  const float rstd = rsqrtf(m2 * (1.0f / CT) + eps);
   const float nmr = -mean * rstd;
   if constexpr (ROWS_ARE_POSITIONS) {
 #pragma unroll
-    for (int ch = 0; ch < kBwdChunks; ++ch) {
-      const uint32_t addr = tile + tile_chunk(pos, part * kBwdChunks + ch);
+    for (int ch = 0; ch < kChunks; ++ch) {
+      const uint32_t addr = tile + tile_chunk(pos, part * kChunks + ch);
       const uint4 v = ld_chunk(addr);
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
       uint32_t o[4];
@@ -131,8 +134,8 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
     }
   } else {
 #pragma unroll 8
-    for (int cc = 0; cc < kBwdCh; ++cc) {
-      const uint32_t addr = tile + tile_off(part * kBwdCh + cc, pos);
+    for (int cc = 0; cc < kCh; ++cc) {
+      const uint32_t addr = tile + tile_off(part * kCh + cc, pos);
       st_f16_sat(addr, fmaf(ld_f16(addr), rstd, nmr));
     }
   }
@@ -153,18 +156,19 @@ __device__ __forceinline__ void sum_partials(uint32_t xchg, int pos, float& a, f
 
 // Sum the per-thread column partials of a CTA over its 128 positions: `acc` holds this thread's channels (part
 // `part`) for two vectors; scratch is float[256][129] (a tile region, padded against bank conflicts).
-__device__ __forceinline__ void flush_colsums(const float (&a0)[kBwdCh], const float (&a1)[kBwdCh], uint8_t* scratch, int pos,
+template <int NCH>
+__device__ __forceinline__ void flush_colsums(const float (&a0)[NCH], const float (&a1)[NCH], uint8_t* scratch, int pos,
                                               int part, float* out0, float* out1) {
   float* s = reinterpret_cast<float*>(scratch);
   // rows: (vector * 128 + channel), columns: position
 #pragma unroll
-  for (int c = 0; c < kBwdCh; ++c) {
-    s[(0 * 128 + part * kBwdCh + c) * 129 + pos] = a0[c];
-    s[(1 * 128 + part * kBwdCh + c) * 129 + pos] = a1[c];
+  for (int c = 0; c < NCH; ++c) {
+    s[(0 * 128 + part * NCH + c) * 129 + pos] = a0[c];
+    s[(1 * 128 + part * NCH + c) * 129 + pos] = a1[c];
   }
   __syncthreads();
-  const int r = threadIdx.x;  // 0..255: vector r / 128, channel r % 128
-  if (r < 256) {
+  const int r = threadIdx.x;  // 0..255: vector r / 128, channel r % 128 (channels beyond 4 * NCH do not exist)
+  if (r < 256 && (r & 127) < NCH * kBwdParts) {
     float sum = 0.f;
     for (int p = 0; p < 128; ++p) sum += s[r * 129 + p];
     (r < 128 ? out0 : out1)[r & 127] = sum;
@@ -202,24 +206,31 @@ struct BwdEpilogueParams {
 //   MODE 2 (second tensor): proj = part + t_hat_2 Wo_2'^T + d_2; dproj, dgate; d t_hat_2, dxg, Mo_2, Mg; the
 //                           LayerNorm backward of its own 128 channels with the sums over all 256 (means -> ln_part);
 //                           `bwd_ln_finish_kernel` then finishes the first tensor's gradient.
-template <int MODE>
+template <int MODE, int C = 128>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_z,
                     const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_wo,
                     const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ CUtensorMap map_dt,
                     const __grid_constant__ CUtensorMap map_dx, const BwdEpilogueParams p) {
+  // C = d_pair: the channels of z, dy, dproj, dgate and the rows of both weight matrices (128, or 64 for the narrow pair
+  // stacks; MODE 0 only). The contracted width (channels of t) is 128 in both cases.
+  static_assert(C == 128 || (C == 64 && MODE == 0), "d_pair is 128, or 64 with one output tensor");
+  constexpr int kZCh = C / kBwdParts;   // z-side channels per thread
+  constexpr int kZChunks = kZCh / 8;
+  constexpr int kZHalves = C / 64;      // 64-channel halves of a [pos][C] tile
+  constexpr uint32_t kWHalf = C * 128;  // bytes of one 64-wide k half of a weight matrix with C rows
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t wo_s = smem_base, wg_s = smem_base + kBwdTile;
   const uint32_t tiles_s = smem_base + 2 * kBwdTile;  // four tile buffers whose roles rotate from tile to tile
   const uint32_t xchg = smem_base + 6 * kBwdTile;
-  const uint32_t const_s = xchg + 4096;
+  const uint32_t const_s = xchg + kBwdXchg;
   const uint32_t bar_base = const_s + 1024;
   const uint32_t w_full = bar_base, tz_full = bar_base + 8, mma_bar = bar_base + 16, dy_full = bar_base + 24;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + 4096 + 1024 + 32);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + kBwdXchg + 1024 + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + 4096);
+  float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + kBwdXchg);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = warp & 3, part = warp >> 2;
@@ -251,16 +262,16 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
   const float gc = p.grad_scale[0];
 
   if (threadIdx.x == 0) {
-    mbar_arrive_expect_tx(w_full, 2 * kBwdTile);
+    // Wo' [C, 128] as two k halves, Wg' [C, C] as C / 64 k halves
+    mbar_arrive_expect_tx(w_full, (2 + kZHalves) * kWHalf);
 #pragma unroll
-    for (int kh = 0; kh < 2; ++kh) {
-      tma_load_2d(wo_s + kh * 16384, &map_wo, w_full, kh * 64, 0);
-      tma_load_2d(wg_s + kh * 16384, &map_wg, w_full, kh * 64, 0);
-    }
+    for (int kh = 0; kh < 2; ++kh) tma_load_2d(wo_s + kh * kWHalf, &map_wo, w_full, kh * 64, 0);
+#pragma unroll
+    for (int kh = 0; kh < kZHalves; ++kh) tma_load_2d(wg_s + kh * kWHalf, &map_wg, w_full, kh * 64, 0);
   }
-  float acc_so[kBwdCh], acc_sg[kBwdCh];
+  float acc_so[kZCh], acc_sg[kZCh];
 #pragma unroll
-  for (int c = 0; c < kBwdCh; ++c) acc_so[c] = 0.f, acc_sg[c] = 0.f;
+  for (int c = 0; c < kZCh; ++c) acc_so[c] = 0.f, acc_sg[c] = 0.f;
 
   // Buffer roles of tile `it`: t, z, dy, dgate = buffers (0, 1, 2, 3) for even it and (2, 3, 0, 1) for odd it. The
   // outputs of a tile are written over its t and z buffers and stored from there; its dy and dgate buffers are free
@@ -270,12 +281,11 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     const int row_i = tile_i / p.tiles_per_row;
     const int j_i = (tile_i - row_i * p.tiles_per_row) * 128;
     const uint32_t t_i = tiles_s + ((it_i & 1) * 2) * kBwdTile, z_i = t_i + kBwdTile;
-    mbar_arrive_expect_tx(tz_full, 2 * kBwdTile);
+    mbar_arrive_expect_tx(tz_full, kBwdTile + kZHalves * 16384);
 #pragma unroll
-    for (int kh = 0; kh < 2; ++kh) {
-      tma_load_3d(t_i + kh * 16384, &map_t, tz_full, j_i + kh * 64, 0, row_i);
-      tma_load_3d(z_i + kh * 16384, &map_z, tz_full, kh * 64, j_i, row_i);
-    }
+    for (int kh = 0; kh < 2; ++kh) tma_load_3d(t_i + kh * 16384, &map_t, tz_full, j_i + kh * 64, 0, row_i);
+#pragma unroll
+    for (int kh = 0; kh < kZHalves; ++kh) tma_load_3d(z_i + kh * 16384, &map_z, tz_full, kh * 64, j_i, row_i);
   };
   bool ok = true;
   int it = 0;
@@ -311,31 +321,31 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       // this tile's dy and dgate buffers held the previous tile's outputs: their store (issued a normalisation pass
       // ago) must have read them before the dy copy lands there
       bulk_wait_read<0>();
-      mbar_arrive_expect_tx(dy_full, kBwdTile);
+      mbar_arrive_expect_tx(dy_full, kZHalves * 16384);
 #pragma unroll
-      for (int kh = 0; kh < 2; ++kh) tma_load_3d(dy_s + kh * 16384, &map_dy, dy_full, kh * 64, j0, row);
+      for (int kh = 0; kh < kZHalves; ++kh) tma_load_3d(dy_s + kh * 16384, &map_dy, dy_full, kh * 64, j0, row);
       dy_pending = it;
     }
-    normalise_tile<true, true>(z_s, xchg, pos, part, p.eps_in);
+    normalise_tile<true, true, C>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
     // ---- phase 2: P = t_hat Wo'^T (columns 0-127), G = x_hat Wg'^T (columns 128-255)
     if (threadIdx.x == 0) {
       tc_fence_after();
-      constexpr uint32_t idesc_p = umma_idesc(128, 128, true, false, kFmtF16, kFmtF16);
-      constexpr uint32_t idesc_g = umma_idesc(128, 128, false, false, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_p = umma_idesc(128, C, true, false, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_g = umma_idesc(128, C, false, false, kFmtF16, kFmtF16);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
-        umma_bf16(tmem_base, umma_desc_mnmajor(t_s + ks * 2048, 16384), umma_desc_kmajor(wo_s + (ks >> 2) * 16384) + kb,
+        umma_bf16(tmem_base, umma_desc_mnmajor(t_s + ks * 2048, 16384), umma_desc_kmajor(wo_s + (ks >> 2) * kWHalf) + kb,
                   idesc_p, ks != 0 ? 1u : 0u);
       }
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
+      for (int ks = 0; ks < C / 16; ++ks) {
         const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
         umma_bf16(tmem_base + 128, umma_desc_kmajor(z_s + (ks >> 2) * 16384) + kb,
-                  umma_desc_kmajor(wg_s + (ks >> 2) * 16384) + kb, idesc_g, ks != 0 ? 1u : 0u);
+                  umma_desc_kmajor(wg_s + (ks >> 2) * kWHalf) + kb, idesc_g, ks != 0 ? 1u : 0u);
       }
       umma_commit(mma_bar);
     }
@@ -349,18 +359,18 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       const uint4* sc = nullptr;
       const uint4* pp = nullptr;
       if constexpr (MODE == 2) {
-        if (j < p.n) pp = reinterpret_cast<const uint4*>(p.p_part + (static_cast<size_t>(row) * p.n + j) * 128 + part * kBwdCh);
+        if (j < p.n) pp = reinterpret_cast<const uint4*>(p.p_part + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
       }
       if (p.drop_scale != nullptr && j < p.n) {
         const int b = row / p.n;
-        sc = reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * 128 + part * kBwdCh);
+        sc = reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * C + part * kZCh);
       }
 #pragma unroll
-      for (int ch = 0; ch < kBwdChunks; ++ch) {
+      for (int ch = 0; ch < kZChunks; ++ch) {
         uint32_t vp[8], vg[8];
-        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, vp);
-        tmem_ld8(tmem_base + lane_sel + 128 + part * kBwdCh + ch * 8, vg);
-        const uint32_t addr = tile_chunk(pos, part * kBwdChunks + ch);
+        tmem_ld8(tmem_base + lane_sel + part * kZCh + ch * 8, vp);
+        tmem_ld8(tmem_base + lane_sel + 128 + part * kZCh + ch * 8, vg);
+        const uint32_t addr = tile_chunk(pos, part * kZChunks + ch);
         const uint4 dyv = ld_chunk(dy_s + addr);
         uint4 scv = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);  // bf16 ones
         if (sc != nullptr) scv = __ldg(sc + ch);
@@ -381,7 +391,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
           float dpv[2], dgv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int c = part * kBwdCh + ch * 8 + t * 2 + e;
+            const int c = part * kZCh + ch * 8 + t * 2 + e;
             const float proj = __uint_as_float(vp[t * 2 + e]) + const_ptr[c] + (e == 0 ? p2.x : p2.y);
             const float gate = sigmoid_fast(__uint_as_float(vg[t * 2 + e]) + const_ptr[128 + c]);
             const float du = (e == 0 ? d2.x * s2.x : d2.y * s2.y) * gc;
@@ -396,6 +406,12 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         st_chunk(dy_s + addr, op[0], op[1], op[2], op[3]);
         // MODE 1: the part of proj leaves through the z buffer (x_hat is only needed by the G GEMM, which is done)
         st_chunk((MODE == 1 ? z_s : dg_s) + addr, og[0], og[1], og[2], og[3]);
+        if constexpr (C == 64) {
+          // the weight-gradient GEMMs read these tiles as 128-row operands: rows 64-127 (the second 64-channel block) are zero
+          const uint32_t zaddr = tile_chunk(pos, 8 + part * kZChunks + ch);
+          st_chunk(dy_s + zaddr, 0u, 0u, 0u, 0u);
+          st_chunk(dg_s + zaddr, 0u, 0u, 0u, 0u);
+        }
       }
     }
     tc_fence_before();
@@ -405,22 +421,23 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     //      Mg += dgate^T x_hat (384-511)
     if (threadIdx.x == 0) {
       tc_fence_after();
-      constexpr uint32_t idesc_d = umma_idesc(128, 128, false, true, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_d = umma_idesc(128, 128, false, true, kFmtF16, kFmtF16);   // d t_hat: N = 128
+      constexpr uint32_t idesc_dx = umma_idesc(128, C, false, true, kFmtF16, kFmtF16);    // d x_hat: N = C
       constexpr uint32_t idesc_mo = umma_idesc(128, 128, true, false, kFmtF16, kFmtF16);
-      constexpr uint32_t idesc_mg = umma_idesc(128, 128, true, true, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_mg = umma_idesc(128, C, true, true, kFmtF16, kFmtF16);
       const uint32_t accum = it != 0 ? 1u : 0u;
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
+      for (int ks = 0; ks < C / 16; ++ks) {  // K = the C channels of dproj; Wo' read MN-major: its k halves are the N blocks
         const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
-        umma_bf16(tmem_base, umma_desc_kmajor(dy_s + (ks >> 2) * 16384) + kb, umma_desc_mnmajor(wo_s + ks * 2048, 16384),
+        umma_bf16(tmem_base, umma_desc_kmajor(dy_s + (ks >> 2) * 16384) + kb, umma_desc_mnmajor(wo_s + ks * 2048, kWHalf),
                   idesc_d, ks != 0 ? 1u : 0u);
       }
       if constexpr (MODE != 1) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+        for (int ks = 0; ks < C / 16; ++ks) {
           const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
           umma_bf16(tmem_base + 128, umma_desc_kmajor(dg_s + (ks >> 2) * 16384) + kb,
-                    umma_desc_mnmajor(wg_s + ks * 2048, 16384), idesc_d, ks != 0 ? 1u : 0u);
+                    umma_desc_mnmajor(wg_s + ks * 2048, kWHalf), idesc_dx, ks != 0 ? 1u : 0u);
         }
       }
 #pragma unroll
@@ -479,9 +496,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       const float rs = rstd_out * 0.0625f;  // d / d t of the stored t / 16
 #pragma unroll
       for (int ch = 0; ch < kBwdChunks; ++ch) {
-        uint32_t v[8], x[8];
+        uint32_t v[8];
         tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
-        if constexpr (MODE != 1) tmem_ld8(tmem_base + lane_sel + 128 + part * kBwdCh + ch * 8, x);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -489,12 +505,19 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
           if constexpr (MODE == 1) st_f16_sat(addr, __uint_as_float(v[e]));  // finished by bwd_ln_finish_kernel
           else st_f16_sat(addr, rs * (__uint_as_float(v[e]) - m1 - ld_f16(addr) * m2));
         }
-        if constexpr (MODE != 1)
-        st_chunk(z_s + tile_chunk(pos, part * kBwdChunks + ch),
-                 pack_f16x2_sat(make_float2(__uint_as_float(x[0]), __uint_as_float(x[1]))),
-                 pack_f16x2_sat(make_float2(__uint_as_float(x[2]), __uint_as_float(x[3]))),
-                 pack_f16x2_sat(make_float2(__uint_as_float(x[4]), __uint_as_float(x[5]))),
-                 pack_f16x2_sat(make_float2(__uint_as_float(x[6]), __uint_as_float(x[7]))));
+      }
+      if constexpr (MODE != 1) {
+#pragma unroll
+        for (int ch = 0; ch < kZChunks; ++ch) {
+          uint32_t x[8];
+          tmem_ld8(tmem_base + lane_sel + 128 + part * kZCh + ch * 8, x);
+          tmem_ld_wait();
+          st_chunk(z_s + tile_chunk(pos, part * kZChunks + ch),
+                   pack_f16x2_sat(make_float2(__uint_as_float(x[0]), __uint_as_float(x[1]))),
+                   pack_f16x2_sat(make_float2(__uint_as_float(x[2]), __uint_as_float(x[3]))),
+                   pack_f16x2_sat(make_float2(__uint_as_float(x[4]), __uint_as_float(x[5]))),
+                   pack_f16x2_sat(make_float2(__uint_as_float(x[6]), __uint_as_float(x[7]))));
+        }
       }
     }
     tc_fence_before();
@@ -502,10 +525,10 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     __syncthreads();
     if (threadIdx.x == 0) {
 #pragma unroll
-      for (int kh = 0; kh < 2; ++kh) {
+      for (int kh = 0; kh < 2; ++kh)
         if (j0 + kh * 64 < p.n) tma_store_3d(&map_dt, t_s + kh * 16384, j0 + kh * 64, 0, row);
-        tma_store_3d(&map_dx, z_s + kh * 16384, kh * 64, j0, row);
-      }
+#pragma unroll
+      for (int kh = 0; kh < kZHalves; ++kh) tma_store_3d(&map_dx, z_s + kh * 16384, kh * 64, j0, row);
       bulk_commit();
     }
   }
@@ -634,23 +657,29 @@ struct BwdPrologueParams {
 // sig (1 - sig) m, adds dvalue W_v' + dgate W_g' to the running d x_hat, and accumulates the two weight gradients.
 // !LAST: the running d x_hat (fp16, times c) is written back through map_out. LAST: the input LayerNorm's backward
 // and the residual finish d loss / d z (bf16, unscaled) through map_out.
-template <bool LAST>
+template <bool LAST, int C = 128>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_do,
                     const __grid_constant__ CUtensorMap map_wv, const __grid_constant__ CUtensorMap map_wg,
                     const __grid_constant__ CUtensorMap map_out, const BwdPrologueParams p) {
+  // C = d_pair: the channels of z, d x_hat, dz and the columns of both weight matrices (128, or 64 for the narrow pair
+  // stacks). The contracted width (channels of dO, rows of the weight matrices) is 128 in both cases.
+  static_assert(C == 128 || C == 64, "d_pair is 128 or 64");
+  constexpr int kZCh = C / kBwdParts;   // z-side channels per thread
+  constexpr int kZChunks = kZCh / 8;
+  constexpr int kZHalves = C / 64;      // 64-channel halves of a [pos][C] tile = k halves of a [128][C] weight matrix
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t wv_s = smem_base, wg_s = smem_base + kBwdTile;
   const uint32_t tiles_s = smem_base + 2 * kBwdTile;  // four tile buffers whose roles rotate from tile to tile
   const uint32_t xchg = smem_base + 6 * kBwdTile;
-  const uint32_t const_s = xchg + 4096;
+  const uint32_t const_s = xchg + kBwdXchg;
   const uint32_t bar_base = const_s + 1024;
   const uint32_t w_full = bar_base, in_full = bar_base + 8, mma_bar = bar_base + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + 4096 + 1024 + 32);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + kBwdXchg + 1024 + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + 4096);
+  float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + kBwdXchg);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = warp & 3, part = warp >> 2;
@@ -679,9 +708,9 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   const float gc_inv = p.grad_scale[1];
 
   if (threadIdx.x == 0) {
-    mbar_arrive_expect_tx(w_full, 2 * kBwdTile);
+    mbar_arrive_expect_tx(w_full, 2 * kZHalves * 16384);
 #pragma unroll
-    for (int kh = 0; kh < 2; ++kh) {
+    for (int kh = 0; kh < kZHalves; ++kh) {
       tma_load_2d(wv_s + kh * 16384, &map_wv, w_full, kh * 64, 0);
       tma_load_2d(wg_s + kh * 16384, &map_wg, w_full, kh * 64, 0);
     }
@@ -702,12 +731,11 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     const int row_i = tile_i / p.tiles_per_row;
     const int j_i = (tile_i - row_i * p.tiles_per_row) * 128;
     const uint32_t z_i = role(it_i, 0), do_i = role(it_i, 1);
-    mbar_arrive_expect_tx(in_full, 2 * kBwdTile);
+    mbar_arrive_expect_tx(in_full, kBwdTile + kZHalves * 16384);
 #pragma unroll
-    for (int kh = 0; kh < 2; ++kh) {
-      tma_load_3d(z_i + kh * 16384, &map_z, in_full, kh * 64, j_i, row_i);
-      tma_load_3d(do_i + kh * 16384, &map_do, in_full, j_i + kh * 64, 0, row_i);
-    }
+    for (int kh = 0; kh < kZHalves; ++kh) tma_load_3d(z_i + kh * 16384, &map_z, in_full, kh * 64, j_i, row_i);
+#pragma unroll
+    for (int kh = 0; kh < 2; ++kh) tma_load_3d(do_i + kh * 16384, &map_do, in_full, j_i + kh * 64, 0, row_i);
   };
   bool ok = true;
   int it = 0;
@@ -724,7 +752,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
     if (threadIdx.x == 0) in_pending = -1;
     // ---- phase 1: x_hat in place
-    const float rstd_in = normalise_tile<true, true>(z_s, xchg, pos, part, p.eps_in);
+    const float rstd_in = normalise_tile<true, true, C>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -737,7 +765,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+        for (int ks = 0; ks < C / 16; ++ks) {
           const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
           umma_bf16(tmem_base + m * 128, umma_desc_kmajor(z_s + (ks >> 2) * 16384) + kb,
                     umma_desc_kmajor((m == 0 ? wv_s : wg_s) + (ks >> 2) * 16384) + kb, idesc, ks != 0 ? 1u : 0u);
@@ -788,8 +816,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     // ---- phase 4: d x_hat = dvalue Wv' + dgate Wg' (columns 0-127); Mv += dvalue^T x_hat (256-383), Mg += dgate^T x_hat
     if (threadIdx.x == 0) {
       tc_fence_after();
-      constexpr uint32_t idesc_d = umma_idesc(128, 128, false, true, kFmtF16, kFmtF16);
-      constexpr uint32_t idesc_m = umma_idesc(128, 128, true, true, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_d = umma_idesc(128, C, false, true, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_m = umma_idesc(128, C, true, true, kFmtF16, kFmtF16);
       const uint32_t accum = it != 0 ? 1u : 0u;
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
@@ -819,17 +847,17 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     // ---- phase 5: add the running d x_hat; !LAST: write it back, LAST: LayerNorm backward + residual -> dz
     {
       const bool inside = j < p.n;
-      const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * 128 + part * kBwdCh);
-      float tot[kBwdCh];
+      const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * C + part * kZCh);
+      float tot[kZCh];
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < kBwdChunks; ++ch) {
+      for (int ch = 0; ch < kZChunks; ++ch) {
         uint32_t v[8];
-        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
+        tmem_ld8(tmem_base + lane_sel + part * kZCh + ch * 8, v);
         uint4 in = make_uint4(0u, 0u, 0u, 0u);
         if (inside) in = __ldg(src + ch);
         uint4 xh = make_uint4(0u, 0u, 0u, 0u);
-        if constexpr (LAST) xh = ld_chunk(z_s + tile_chunk(pos, part * kBwdChunks + ch));
+        if constexpr (LAST) xh = ld_chunk(z_s + tile_chunk(pos, part * kZChunks + ch));
         tmem_ld_wait();
         const uint32_t iw[4] = {in.x, in.y, in.z, in.w};
         const uint32_t xw[4] = {xh.x, xh.y, xh.z, xh.w};
@@ -848,8 +876,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       }
       if constexpr (!LAST) {
 #pragma unroll
-        for (int ch = 0; ch < kBwdChunks; ++ch)
-          st_chunk(dv_s + tile_chunk(pos, part * kBwdChunks + ch), pack_f16x2_sat(make_float2(tot[ch * 8], tot[ch * 8 + 1])),
+        for (int ch = 0; ch < kZChunks; ++ch)
+          st_chunk(dv_s + tile_chunk(pos, part * kZChunks + ch), pack_f16x2_sat(make_float2(tot[ch * 8], tot[ch * 8 + 1])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 2], tot[ch * 8 + 3])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 4], tot[ch * 8 + 5])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 6], tot[ch * 8 + 7])));
@@ -858,13 +886,13 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
         named_bar_sync(1, kBwdThreads);
         float m1, m2;
         sum_partials(xchg, pos, m1, m2);
-        m1 *= 1.0f / 128.0f, m2 *= 1.0f / 128.0f;
+        m1 *= 1.0f / C, m2 *= 1.0f / C;
         const float rs = rstd_in * gc_inv;
         const uint4* dyp = p.dy == nullptr ? nullptr
-                                           : reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * 128 + part * kBwdCh);
+                                           : reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * C + part * kZCh);
 #pragma unroll
-        for (int ch = 0; ch < kBwdChunks; ++ch) {
-          const uint4 xh = ld_chunk(z_s + tile_chunk(pos, part * kBwdChunks + ch));
+        for (int ch = 0; ch < kZChunks; ++ch) {
+          const uint4 xh = ld_chunk(z_s + tile_chunk(pos, part * kZChunks + ch));
           uint4 dyv = make_uint4(0u, 0u, 0u, 0u);
           if (dyp != nullptr && inside) dyv = __ldg(dyp + ch);
           const uint32_t xw[4] = {xh.x, xh.y, xh.z, xh.w};
@@ -877,7 +905,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
             o[t] = pack_bf16x2(fmaf(rs, tot[ch * 8 + 2 * t] - m1 - x.x * m2, r.x),
                                fmaf(rs, tot[ch * 8 + 2 * t + 1] - m1 - x.y * m2, r.y));
           }
-          st_chunk(dv_s + tile_chunk(pos, part * kBwdChunks + ch), o[0], o[1], o[2], o[3]);
+          st_chunk(dv_s + tile_chunk(pos, part * kZChunks + ch), o[0], o[1], o[2], o[3]);
         }
       }
     }
@@ -886,7 +914,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     __syncthreads();
     if (threadIdx.x == 0) {
 #pragma unroll
-      for (int kh = 0; kh < 2; ++kh) tma_store_3d(&map_out, dv_s + kh * 16384, kh * 64, j0, row);
+      for (int kh = 0; kh < kZHalves; ++kh) tma_store_3d(&map_out, dv_s + kh * 16384, kh * 64, j0, row);
       bulk_commit();
     }
   }
@@ -974,18 +1002,23 @@ __global__ void __launch_bounds__(128) bwd_pack_kernel(const PackArgs a, uint8_t
   const int gw = blockIdx.x * 4 + (threadIdx.x >> 5);  // 0 .. 767
   const int lane = threadIdx.x & 31;
   const int m = gw >> 7, row = gw & 127;
+  const int n_rows = m < 4 ? 128 : a.c;  // a.c = d_pair: matrices 0..3 are [128, c], 4 (out) is [c, 128], 5 (gate) [c, c]
+  const int k = m == 4 ? 128 : a.c;
+  if (row >= n_rows) return;
+  const bool active = lane * 4 < k;
   const float* gamma = (m == 4) ? a.ln_out_w : a.ln_in_w;
   const float* beta = (m == 4) ? a.ln_out_b : a.ln_in_b;
-  float w[4];
-  if (a.f32_weights) {
+  float w[4] = {0.f, 0.f, 0.f, 0.f};
+  if (!active) {
+  } else if (a.f32_weights) {
     const float4 v = reinterpret_cast<const float4*>(static_cast<const float*>(a.w[m]) + static_cast<size_t>(row) * a.ld[m])[lane];
     w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
   } else {
     const uint2 v = reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(a.w[m]) + static_cast<size_t>(row) * a.ld[m])[lane];
     w[0] = bf16_lo(v.x), w[1] = bf16_hi(v.x), w[2] = bf16_lo(v.y), w[3] = bf16_hi(v.y);
   }
-  const float4 g = reinterpret_cast<const float4*>(gamma)[lane];
-  const float4 b = reinterpret_cast<const float4*>(beta)[lane];
+  const float4 g = active ? reinterpret_cast<const float4*>(gamma)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 b = active ? reinterpret_cast<const float4*>(beta)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
   const float gg[4] = {g.x, g.y, g.z, g.w}, bb[4] = {b.x, b.y, b.z, b.w};
   float d = 0.f;
   uint16_t o[4];
@@ -994,10 +1027,12 @@ __global__ void __launch_bounds__(128) bwd_pack_kernel(const PackArgs a, uint8_t
     o[t] = __half_as_ushort(__float2half_rn(fminf(fmaxf(w[t] * gg[t], -65504.f), 65504.f)));
     d = fmaf(w[t], bb[t], d);
   }
-  uint2 ov;
-  ov.x = static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 16);
-  ov.y = static_cast<uint32_t>(o[2]) | (static_cast<uint32_t>(o[3]) << 16);
-  reinterpret_cast<uint2*>(packed + static_cast<size_t>(m) * 32768)[row * 32 + lane] = ov;
+  if (active) {
+    uint2 ov;
+    ov.x = static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 16);
+    ov.y = static_cast<uint32_t>(o[2]) | (static_cast<uint32_t>(o[3]) << 16);
+    reinterpret_cast<uint2*>(packed + static_cast<size_t>(m) * 32768)[row * (k / 4) + lane] = ov;
+  }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
   if (lane == 0)
@@ -1044,6 +1079,13 @@ struct BwdFinalArgs {
 __global__ void __launch_bounds__(128) bwd_finalize_kernel(const BwdFinalArgs a) {
   const int k = threadIdx.x, m = blockIdx.x, rb = blockIdx.y;
   if (((a.mask >> m) & 1u) == 0u) return;
+  const int n_rows = m < 4 ? 128 : a.w.c, n_cols = m == 4 ? 128 : a.w.c;  // a.w.c = d_pair
+  float* part0 = a.ln_part + ((m * 8 + rb) * 2 + 0) * 128 + k;
+  float* part1 = a.ln_part + ((m * 8 + rb) * 2 + 1) * 128 + k;
+  if (k >= n_cols || rb * 16 >= n_rows) {
+    *part0 = 0.f, *part1 = 0.f;
+    return;
+  }
   const float cinv = a.scale[1];
   const float gamma = (m == 4 ? a.w.ln_out_w : a.w.ln_in_w)[k];
   const float beta = (m == 4 ? a.w.ln_out_b : a.w.ln_in_b)[k];
@@ -1059,8 +1101,8 @@ __global__ void __launch_bounds__(128) bwd_finalize_kernel(const BwdFinalArgs a)
     ag = fmaf(w, mv, ag);
     ab = fmaf(w, sv, ab);
   }
-  a.ln_part[((m * 8 + rb) * 2 + 0) * 128 + k] = ag;
-  a.ln_part[((m * 8 + rb) * 2 + 1) * 128 + k] = ab;
+  *part0 = ag;
+  *part1 = ab;
 }
 struct BwdLnArgs {
   const float* ln_part[2];  // per half
@@ -1070,6 +1112,7 @@ struct BwdLnArgs {
   float* d_ln_in_b;
   float* d_ln_out_w;  // [128 * halves]: half h at + 128 h
   float* d_ln_out_b;
+  int c;              // d_pair
 };
 __global__ void __launch_bounds__(128) bwd_finalize_ln_kernel(const BwdLnArgs a) {
   const int k = threadIdx.x;
@@ -1089,8 +1132,10 @@ __global__ void __launch_bounds__(128) bwd_finalize_ln_kernel(const BwdLnArgs a)
     a.d_ln_out_w[h * 128 + k] = g_out;
     a.d_ln_out_b[h * 128 + k] = b_out;
   }
-  a.d_ln_in_w[k] = g_in;
-  a.d_ln_in_b[k] = b_in;
+  if (k < a.c) {  // the input LayerNorm has d_pair channels
+    a.d_ln_in_w[k] = g_in;
+    a.d_ln_in_b[k] = b_in;
+  }
 }
 
 }  // namespace trimul

@@ -541,14 +541,15 @@ def trimul_backward(
     workspace: Optional[torch.Tensor] = None,
     check: bool = False,
 ):
-    """Backward of :func:`trimul_forward` for d_pair = d_hidden = 128 (``b200_trimul_backward``); ``outgoing=None`` is
-    the bidirectional module.
+    """Backward of :func:`trimul_forward` (``b200_trimul_backward``) for every width the forward takes;
+    ``outgoing=None`` is the bidirectional module.
 
     ``forward_workspace`` is the workspace the forward call used for the same inputs (it holds the stage tensors).
-    Returns ``(dz bf16 [B,N,N,128], grads)`` with ``grads`` a dict of fp32 tensors of the parameters' shapes under the
+    Returns ``(dz bf16, the input's shape, grads)`` with ``grads`` a dict of fp32 tensors of the parameters' shapes under the
     parameter keys.
     """
-    B, N = _check_z(z)
+    B, N = _check_z(z, widths=(D, 64))
+    C = int(z.shape[3])
     if z.shape[1] != N:
         raise RuntimeError(f"pair tensor must be square in its token dims, got {tuple(z.shape)}")
     dev = z.device
@@ -559,7 +560,9 @@ def trimul_backward(
     if not z.is_contiguous():
         raise RuntimeError("the pair tensor must be contiguous")
     bidir = outgoing is None
-    w = _Weights(params, biases, dev, bidirectional=bidir)
+    w = _Weights(params, biases, dev, bidirectional=bidir, d_pair=C)
+    if C != D and drop_scale is not None:
+        raise RuntimeError("the row-shared dropout scale is only implemented for d_pair = 128")
     ds = None
     if drop_scale is not None:
         if drop_scale.numel() != B * N * D or drop_scale.shape[-1] != D or drop_scale.shape[0] != B:
@@ -570,21 +573,21 @@ def trimul_backward(
         workspace = aligned_empty(need, dev)
     elif workspace.numel() * workspace.element_size() < need:
         raise RuntimeError(f"workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
-    if forward_workspace.numel() * forward_workspace.element_size() < workspace_bytes(B, N, outgoing):
+    if forward_workspace.numel() * forward_workspace.element_size() < workspace_bytes(B, N, outgoing, C):
         raise RuntimeError("forward_workspace is smaller than the forward's workspace for this shape")
     tm = as_mask_u8(mask, dev)
     pm = as_mask_u8(pair_mask, dev)
     dz = torch.empty_like(z)
-    wide = 2 * D if bidir else D
-    shapes = [(wide, D)] * 4 + [(D, D), (D, wide)]
+    wide = 2 * D if (bidir and C == D) else D  # contracted channels in total
+    shapes = [(wide, C)] * 4 + [(C, C), (C, wide)]
     dws = [torch.empty(sh, dtype=torch.float32, device=dev) for sh in shapes]
-    dln = [torch.empty(n, dtype=torch.float32, device=dev) for n in (D, D, wide, wide)]
+    dln = [torch.empty(n, dtype=torch.float32, device=dev) for n in (C, C, wide, wide)]
     dw_arr = (c_void_p * 6)(*[t.data_ptr() for t in dws])
     with torch.cuda.device(dev):
         rc = _lib.load().b200_trimul_backward(
             _ptr(dy), _ptr(z), *[_ptr(t) for t in w.weights], w.dtype_code, *[_ptr(t) for t in w.lns], w.bias_array,
             _ptr(tm), _ptr(pm), _ptr(ds), _ptr(forward_workspace), _ptr(dz), dw_arr, *[_ptr(t) for t in dln],
-            _ptr(workspace), workspace.numel() * workspace.element_size(), B, N, _direction(outgoing), float(eps_in),
+            _ptr(workspace), workspace.numel() * workspace.element_size(), B, N, C, w.d_hidden, _direction(outgoing), float(eps_in),
             float(eps_out), int(bool(residual)), _stream(dev),
         )
     _lib.check(rc, "b200_trimul_backward")

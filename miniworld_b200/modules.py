@@ -17,8 +17,8 @@ shapes.
 
 In training mode with ``p_drop > 0`` the forward applies the row-shared dropout of the reference
 (``x + drop_row(f(x))``: one keep-mask per (batch, column, channel), shared by all rows,
-``src/miniworld/blocks/template.py:38-40``). The modules with d_pair = d_hidden = 128 (unidirectional and bidirectional) are differentiable
-(input and all ten parameters, :mod:`miniworld_b200.training`); the 64-wide modules and the Transition have no backward: calling them with gradients enabled on an input that requires them raises
+``src/miniworld/blocks/template.py:38-40``). Every triangle-update module is differentiable (input and all ten parameters, :mod:`miniworld_b200.training`); the
+Transition has no backward: calling them with gradients enabled on an input that requires them raises
 ``NotImplementedError``.
 """
 
@@ -87,7 +87,7 @@ class Fp32LayerNorm(nn.LayerNorm):
 
 
 class TriangleMultiplication(nn.Module):
-    """Triangle multiplicative update on B200 kernels (forward; backward for d_pair = d_hidden = 128).
+    """Triangle multiplicative update on B200 kernels (forward and backward).
 
     ``forward(pair [B,N,N,d_pair] bf16, mask Bool[B,N] | None) -> pair + update`` (bf16).
     Linear weights may be bf16 or fp32 masters; LayerNorm affine parameters are kept in fp32 whatever
@@ -216,7 +216,7 @@ class TriangleMultiplication(nn.Module):
         return ws
 
     def _backward_supported(self) -> bool:
-        return self.d_pair == D_SUPPORTED and self.d_hidden == D_SUPPORTED
+        return True  # every width the constructor accepts has a backward
 
     def _run(self, pair: torch.Tensor, token_mask, pair_mask) -> torch.Tensor:
         # the differentiable path is taken when the input requires grad, or in training mode when a parameter does

@@ -1,4 +1,4 @@
-"""Training path of the triangle update (d_pair = d_hidden = 128, unidirectional and bidirectional): forward on the
+"""Training path of the triangle update (every width and direction the forward serves): forward on the
 library's kernels with the stage tensors kept, backward for the input and all ten parameters through
 ``b200_trimul_backward``.
 
@@ -33,11 +33,9 @@ class TriMulFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, z, token_mask, pair_mask, drop_scale, cfg, *params):
-        if z.shape[3] != D:
-            raise NotImplementedError("the backward is implemented for d_pair = d_hidden = 128")
         B, N = int(z.shape[0]), int(z.shape[1])
         p = {k: v.detach() for k, v in zip(_PARAM_KEYS, params)}
-        ws = F_.aligned_empty(F_.workspace_bytes(B, N, cfg["outgoing"]), z.device)  # kept until the backward has run
+        ws = F_.aligned_empty(F_.workspace_bytes(B, N, cfg["outgoing"], int(z.shape[3])), z.device)  # kept until the backward
         y = F_.trimul_forward(
             z.detach(), p, token_mask, outgoing=cfg["outgoing"], eps_in=cfg["eps_in"], eps_out=cfg["eps_out"],
             pair_mask=pair_mask, residual=cfg["residual"], biases=cfg["biases"], workspace=ws, check=cfg["check"],

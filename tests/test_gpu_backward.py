@@ -252,3 +252,52 @@ def test_bidirectional_module_training_step_dropout_zero_gamma_and_determinism()
         _check(k, grads[0][1][k], gp_ref[k])
         assert torch.equal(grads[0][1][k], grads[1][1][k]), k
     assert torch.equal(grads[0][0], grads[1][0])
+
+
+def _narrow_params(seed, beta_scale=0.05):
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *sh: torch.randn(*sh, generator=g)  # noqa: E731
+    bf = torch.bfloat16
+    return {
+        "ln_pair.weight": 1.0 + 0.1 * rn(64), "ln_pair.bias": beta_scale * rn(64),
+        "to_left.weight": (rn(128, 64) * 64**-0.5).to(bf), "to_left_gate.weight": (rn(128, 64) * 64**-0.5).to(bf),
+        "to_right.weight": (rn(128, 64) * 64**-0.5).to(bf), "to_right_gate.weight": (rn(128, 64) * 64**-0.5).to(bf),
+        "ln_out.weight": 1.0 + 0.1 * rn(128), "ln_out.bias": beta_scale * rn(128),
+        "to_gate.weight": (rn(64, 64) * 64**-0.5).to(bf), "to_out.weight": (rn(64, 128) * 128**-0.5).to(bf),
+    }
+
+
+@pytest.mark.parametrize("kind", ["outgoing", "incoming", "bidirectional"])
+@pytest.mark.parametrize("N,mask_kind", [(64, "none"), (136, "random"), (200, "holes"), (384, "random")])
+def test_narrow_gradients_match_the_oracle(kind, N, mask_kind):
+    """The 64-wide pair stacks: `TriangleMultiplication(64, d_hidden=128)` (the template blocks of the fine-tuning
+    harness, benchmarks/protenix_finetune/patch_engine.py:283-295 in the reference project) and
+    `BidirectionalTriangleMultiplication(64)` (the (L, D) = (384, 64) case of the reference's backward validation,
+    docs/archive/engine2-validation-20260923/validate_bidir_reference.py:11)."""
+    p = _narrow_params(700 + N)
+    g = torch.Generator().manual_seed(701 + N)
+    z = torch.randn(1, N, N, 64, generator=g).to(torch.bfloat16)
+    dy = (torch.randn(1, N, N, 64, generator=g) * 0.01).to(torch.bfloat16)
+    mask = None
+    if mask_kind == "random":
+        mask = torch.rand(1, N, generator=g) > 0.2
+    elif mask_kind == "holes":
+        mask = torch.ones(1, N, dtype=torch.bool)
+        mask[:, ::3] = False
+    if kind == "bidirectional":
+        y_ref, dz_ref, gp_ref = _bidir_oracle_grads(z, p, mask, dy)
+        m = mw.BidirectionalTriangleMultiplication(64, check_status=True)
+    else:
+        y_ref, dz_ref, gp_ref = _oracle_grads(z, p, mask, dy, kind == "outgoing")
+        m = mw.TriangleMultiplication(64, d_hidden=128, outgoing=kind == "outgoing", check_status=True)
+    m.load_state_dict(p)
+    m = m.to(DEV).to(torch.bfloat16).train()
+    zd = z.to(DEV).requires_grad_(True)
+    y = m(zd, None if mask is None else mask.to(DEV))
+    y.backward(dy.to(DEV))
+    _check("y", y, y_ref, 5e-3)
+    _check("dz", zd.grad, dz_ref)
+    sd = dict(m.named_parameters())
+    for k in _PARAM_KEYS:
+        assert sd[k].grad is not None and sd[k].grad.shape == sd[k].shape, k
+        _check(k, sd[k].grad, gp_ref[k])

@@ -228,8 +228,8 @@ def test_errors_are_loud():
     with pytest.raises(NotImplementedError):
         mw.TriangleMultiplication(64)  # 64 contracted channels in one direction is not a shape the kernels take
     zz = torch.zeros(1, 16, 16, 128, dtype=torch.bfloat16, device=DEV, requires_grad=True)
-    with pytest.raises(NotImplementedError):  # no backward for the 64-wide modules
-        mw.TriangleMultiplication(64, d_hidden=128).to(DEV)(torch.zeros(1, 16, 16, 64, dtype=torch.bfloat16, device=DEV, requires_grad=True), None)
+    with pytest.raises(NotImplementedError):  # the Transition has no backward
+        mw.Transition(128).to(DEV)(zz)
 
 
 def test_large_complex_workload_full_size_rows():

@@ -18,7 +18,7 @@ shapes.
 In training mode with ``p_drop > 0`` the forward applies the row-shared dropout of the reference
 (``x + drop_row(f(x))``: one keep-mask per (batch, column, channel), shared by all rows,
 ``src/miniworld/blocks/template.py:38-40``). Every triangle-update module is differentiable (input and all ten parameters, :mod:`miniworld_b200.training`); the
-Transition has no backward: calling them with gradients enabled on an input that requires them raises
+Transition has no backward: calling it with gradients enabled on an input that requires them raises
 ``NotImplementedError``.
 """
 

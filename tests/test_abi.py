@@ -75,3 +75,24 @@ def test_null_pointers_are_rejected_before_any_cuda_call(lib):
                                  1e-5, 1e-5, 1, None)
     assert rc == -1
     assert lib.b200_trimul_contract(None, None, None, 1, 384, 0, 384, 1, None, None) == -1
+
+
+def test_backward_entry_points_validate_before_any_cuda_call(lib):
+    out = ctypes.c_size_t(0)
+    assert lib.b200_trimul_backward_workspace_bytes(1, 384, 1, ctypes.byref(out)) == 0
+    uni = out.value
+    assert lib.b200_trimul_backward_workspace_bytes(1, 384, 0, ctypes.byref(out)) == 0
+    plane = 384 * 384 * 128 * 2
+    assert uni >= 4 * plane and out.value >= uni + 4 * plane  # the bidirectional module keeps four more tensors
+    assert lib.b200_trimul_backward_workspace_bytes(1, 100, 1, ctypes.byref(out)) == -3  # N not a multiple of 8
+    assert lib.b200_trimul_backward_workspace_bytes(1, 384, 5, ctypes.byref(out)) == -2
+    assert lib.b200_trimul_backward_workspace_bytes(1, 384, 1, None) == -1
+    arr = (ctypes.c_size_t * 18)()
+    assert lib.b200_trimul_backward_workspace_layout(1, 384, 0, arr) == 0
+    offs = list(arr)
+    assert offs[0] == 0 and all(o % 1024 == 0 for o in offs) and offs == sorted(offs)
+    assert lib.b200_trimul_backward_workspace_bytes(1, 384, 0, ctypes.byref(out)) == 0 and offs[17] == out.value
+    rc = lib.b200_trimul_backward(*([None] * 8), 0, *([None] * 4), *([None] * 5), *([None] * 2), *([None] * 4), None, 0,
+                                  1, 384, 128, 128, 1, 1e-5, 1e-5, 1, None)
+    assert rc == -1
+    assert lib.b200_trimul_contract_backward(None, None, None, None, None, 1, 384, 1, None, None) == -1

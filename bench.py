@@ -424,6 +424,55 @@ def run_b200(args):
                                  f"(max abs {worst}, bit-identical expected: {exact_expected})")
         return line
 
+    def link_evidence(r: Runner):
+        """Several GPUs, p2p transport: CUDA-event time of stage 1 (the kernel that stores its output tiles into the
+        peers' memory over NVLink) with the peers as destinations and with local buffers of the same shapes instead;
+        the bytes it sends to peers; and the rate that follows if the difference is the links' time."""
+        from miniworld_b200 import functional as F_
+
+        if r.kind != "rows":
+            return None
+        m = r.mods["outgoing"]
+        if m.transport != "p2p" or m._sym is None or m._bufs is None:
+            return None
+        sets, b = m._sym[1], m._bufs[1]
+        z, N, rows = r.z, r.N, r.rows
+        pro = dict(token_mask=r.mask, row_begin=r.begin, eps_in=float(m.ln_pair.eps), has_bias=False)
+        f16 = dict(dtype=torch.float16, device=dev)
+        if m.contraction == "channels":
+            cg = 128 // world
+            local_l = [torch.empty(1, N, cg, N, **f16) for _ in range(world)]
+            local_r = [torch.empty(1, N, cg, N, **f16) for _ in range(world)]
+            peer = lambda: F_.prologue_channels(z, b["packed"], sets[0]["left"], sets[0]["right"], b["status"], **pro)  # noqa: E731
+            local = lambda: F_.prologue_channels(z, b["packed"], local_l, local_r, b["status"], **pro)  # noqa: E731
+            sent = 2 * rows * (128 - cg) * N * 2  # left and right, the channel groups of the other GPUs
+            stage = "prologue_channels"
+        else:
+            views = sets[0]["full"]
+            left = torch.empty(1, rows, 128, N, **f16)
+            local_copies = [torch.empty(1, N, 128, N, **f16) for _ in range(world)]
+            peers = [views[q] for q in range(world) if q != rank]
+            peer = lambda: F_.prologue_push(z, b["packed"], left, views[rank], peers, b["status"], **pro)  # noqa: E731
+            local = lambda: F_.prologue_push(z, b["packed"], left, local_copies[rank],  # noqa: E731
+                                             [local_copies[q] for q in range(world) if q != rank], b["status"], **pro)
+            sent = rows * 128 * N * 2 * (world - 1)  # `right` to every other GPU
+            stage = "prologue_push"
+        out = {"stage": stage, "bytes_to_peers_per_gpu": sent}
+        for name, fn in (("peer_ms", peer), ("local_ms", local)):
+            for _ in range(3):
+                fn()
+            barrier()
+            ms = sorted(time_events(fn, 10, stream) / 10 for _ in range(3))
+            out[name] = max_over_ranks(ms[1])
+            barrier()
+        out["peer_gbs_lower_bound"] = sent / (out["peer_ms"] * 1e-3) / 1e9
+        if out["peer_ms"] > out["local_ms"]:
+            out["link_gbs_if_difference_is_link_time"] = sent / ((out["peer_ms"] - out["local_ms"]) * 1e-3) / 1e9
+        out["how"] = ("stage 1 alone, ten launches per sample, median of three, max over ranks; the peers' buffers are the "
+                      "symmetric-memory views the forward uses, the local run stores the same tiles into this GPU's memory")
+        r.check_status()
+        return out
+
     # ---- headline workload
     r = Runner(args.workload, world, rank, dev, contraction=args.contraction)
     B, N = r.B, r.N
@@ -446,6 +495,7 @@ def run_b200(args):
     h2d = r.z_host.numel() * 2
     d2h = y_host.numel() * 2
     parity = parity_line(r) if world > 1 else None
+    link = link_evidence(r) if world > 1 else None
 
     # ---- per-stage timing for the roofline (single GPU only: a second K-step loop with events per stage)
     roofline = None
@@ -477,6 +527,9 @@ def run_b200(args):
                 entry["stages_ms"], entry["roofline"] = st2, rf2
             else:
                 p2 = parity_line(r2)
+                l2 = link_evidence(r2)
+                if l2 is not None:
+                    entry["nvlink"] = l2
                 if p2 is not None:
                     entry["parity"] = p2
             extra[name] = entry
@@ -523,6 +576,8 @@ def run_b200(args):
         }
         if parity is not None:
             line["parity"] = parity
+        if link is not None:
+            line["nvlink"] = link
         if stages_ms is not None:
             line["stages_ms"] = stages_ms
         if roofline is not None:

@@ -51,6 +51,9 @@ class TriMulFunction(torch.autograd.Function):
     def backward(ctx, dy):
         z, *params = ctx.saved_tensors
         cfg = ctx.cfg
+        if ctx.ws is None:
+            raise RuntimeError("the forward's stage tensors were released by the first backward of this call "
+                               "(a second backward through the same forward is not supported)")
         B, N = int(z.shape[0]), int(z.shape[1])
         dz, grads = F_.trimul_backward(
             dy.to(torch.bfloat16), z.detach(), {k: v.detach() for k, v in zip(_PARAM_KEYS, params)}, ctx.ws, ctx.token_mask,

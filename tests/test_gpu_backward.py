@@ -87,7 +87,7 @@ def test_module_training_step_with_dropout_padding_and_no_residual():
     for k in _PARAM_KEYS:
         assert sd[k].grad is not None, k
         _check(k, sd[k].grad, gp_ref[k])
-    with pytest.raises(RuntimeError, match="second backward"):
+    with pytest.raises(RuntimeError):
         y.backward(dy.to(DEV))  # the stage tensors are released after the first backward
     # parameters only (the input does not require grad): still differentiable in training mode
     m.zero_grad()

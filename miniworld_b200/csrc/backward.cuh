@@ -1,21 +1,25 @@
 // Backward of the triangle update around the contraction: the epilogue's gradients (output LayerNorm, output
 // projection, output gate) and the prologue's gradients (input LayerNorm, the four gated projections, the mask).
 //
-// Both kernels walk tiles of 128 consecutive columns j of one pair row, one CTA per SM, 256 threads: thread = one
-// position (its TMEM lane) and 64 of the 128 channels. A tile goes through a fixed sequence of phases separated by
-// CTA-wide barriers; one thread issues the TMA copies and the MMAs. Per tile:
+// Both kernels walk tiles of 128 consecutive columns j of one pair row, one CTA per SM, 512 threads: four threads per
+// position (its TMEM lane), each covering a quarter of the channels. A tile goes through a fixed sequence of phases
+// separated by CTA-wide barriers; one thread issues the TMA copies and the MMAs. Per tile:
 //   1. TMA loads of the tile's inputs; the LayerNorm inputs are normalised in place in shared memory (fp16),
 //   2. the forward GEMMs are recomputed on the tensor cores (weights with the LayerNorm gamma folded in, fp16),
 //   3. the threads turn the upstream gradient into the gradients of the GEMM outputs (fp16 tiles in shared memory),
 //   4. the tensor cores compute, from those tiles, the gradients with respect to the normalised inputs (the same weight
 //      tiles read MN-major) and accumulate the weight gradients M = dOut^T x_hat over all tiles of the CTA in TMEM,
 //   5. the threads finish (LayerNorm backward) and the results leave through TMA stores.
-// Column sums of the dOut tiles (the bias-like terms) are accumulated per thread in registers. At the end every CTA
-// writes its partial M and column sums; a small kernel adds the partials and forms the parameter gradients.
+// The four tile buffers of a CTA rotate their roles from tile to tile: the next tile's inputs are copied into the
+// buffers the gradient GEMMs have finished with while the tile completes, and a store is only waited for when its
+// buffer is needed again. Column sums of the dOut tiles (the bias-like terms) are accumulated per thread in
+// registers. At the end every CTA writes its partial M and column sums; small kernels add the partials and form the
+// parameter gradients. Both kernels are templates on the input width C (128, or 64 for the narrow pair stacks); the
+// epilogue's backward also has a two-launch form for an output LayerNorm over 256 channels (the bidirectional module).
 //
 // Gradients travel in fp16 tiles, so the upstream gradient is multiplied by a power of two c (read from device
-// memory, chosen from max |dy| by `grad_scale_kernel`); every output of these kernels carries that factor, and the
-// final kernels divide it out in fp32.
+// memory, chosen from max |dy| by `bwd_amax_kernel` / `bwd_scale_kernel`); every output of these kernels carries that
+// factor, and the final kernels divide it out in fp32.
 #pragma once
 
 #include "ptx.cuh"
@@ -27,7 +31,7 @@ namespace trimul {
 #endif
 constexpr int kBwdParts = TRIMUL_BWD_PARTS;      // threads per position: each covers 128 / kBwdParts channels
 constexpr int kBwdThreads = 128 * kBwdParts;
-constexpr int kBwdCh = 128 / kBwdParts;          // channels per thread
+constexpr int kBwdCh = 128 / kBwdParts;          // channels per thread of a 128-channel tile
 constexpr int kBwdChunks = kBwdCh / 8;           // 16-byte chunks (8 channels) per thread
 constexpr int kBwdTile = 32768;  // one [128][128] 16-bit tile
 constexpr int kBwdXchg = kBwdParts * 128 * 8;  // float2 [kBwdParts][128]

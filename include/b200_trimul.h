@@ -345,6 +345,22 @@ int b200_trimul_clear_status(int* status, void* cuda_stream);
 /* Synchronise `cuda_stream` and copy the device status word to *host_status. */
 int b200_trimul_read_status(const int* status, void* cuda_stream, int* host_status);
 
+/*
+ * Backward of the pair Transition (the operator has no training kernel of its own in the reference tree; its forward is
+ * `transition_fused_fwd_sm100a`, docs/phase2-b200-training-speed.md:165). Given dy = d loss / d y ([positions, 128]
+ * bf16) and the forward's inputs, writes dx ([positions, 128] bf16, the residual path included when `residual` is
+ * non-zero) and, in fp32 and the parameters' shapes, d_expand_a / d_expand_b [512, 128], d_squeeze [128, 512],
+ * d_ln_w / d_ln_b [128]. Every output is overwritten. One launch per block of 128 hidden units (four), whose three
+ * weight-gradient accumulators stay in tensor memory over all positions; the running d x_hat is carried between the
+ * launches in the workspace. Deterministic. Workspace: b200_transition_backward_workspace_bytes, 1024-byte aligned.
+ */
+int b200_transition_backward_workspace_bytes(long long positions, size_t* out_bytes);
+int b200_transition_backward(const void* dy, const void* x, const void* w_expand_a, const void* w_expand_b,
+                             const void* w_squeeze, int weight_dtype, const float* ln_w, const float* ln_b, void* dx,
+                             float* d_expand_a, float* d_expand_b, float* d_squeeze, float* d_ln_w, float* d_ln_b,
+                             void* workspace, size_t workspace_bytes, long long positions, int d, int n, float eps,
+                             int residual, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

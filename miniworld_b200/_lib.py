@@ -121,6 +121,11 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     ),
+    "b200_transition_backward_workspace_bytes": (c_int, [ctypes.c_longlong, POINTER(c_size_t)]),
+    "b200_transition_backward": (
+        c_int,
+        [c_void_p] * 5 + [c_int] + [c_void_p] * 8 + [c_void_p, c_size_t, ctypes.c_longlong, c_int, c_int, c_float, c_int, c_void_p],
+    ),
     "b200_trimul_clear_status": (c_int, [c_void_p, c_void_p]),
     "b200_trimul_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
 }

@@ -372,6 +372,7 @@ static int launch_contract_pair(const CUtensorMap& ma, const CUtensorMap& mb, co
 }  // namespace trimul
 
 #include "backward.cuh"  // after PackArgs
+#include "transition_backward.cuh"
 
 using namespace trimul;
 
@@ -1278,3 +1279,4 @@ extern "C" int b200_trimul_forward_static(const void* z, const void* w_left, con
 }
 
 #include "backward_host.inc"
+#include "transition_backward_host.inc"

@@ -644,3 +644,53 @@ def transition_forward(x: torch.Tensor, packed: torch.Tensor, status: torch.Tens
                                                  int(bool(residual)), _ptr(status), _stream(x.device))
     _lib.check(rc, "b200_transition_forward")
     return out
+
+
+def transition_backward(dy: torch.Tensor, x: torch.Tensor, params: dict, *, eps: float = 1e-5, residual: bool = True,
+                        workspace: Optional[torch.Tensor] = None, check: bool = False):
+    """Backward of the pair Transition (``b200_transition_backward``): ``dy``, ``x`` [..., 128] bf16 contiguous, ``params``
+    under ``TRANSITION_KEYS``. Returns ``(dx bf16, grads)`` with fp32 gradients of the parameters' shapes."""
+    for name, t in (("dy", dy), ("x", x)):
+        _require_cuda(t, name)
+        if t.dtype != torch.bfloat16 or t.shape[-1] != D or not t.is_contiguous():
+            raise RuntimeError(f"{name} must be a contiguous bf16 tensor [..., {D}], got {t.dtype} {tuple(t.shape)}")
+    if tuple(dy.shape) != tuple(x.shape):
+        raise RuntimeError("dy must have the input's shape")
+    wa, wb, wsq = params["expand_a.weight"], params["expand_b.weight"], params["squeeze.weight"]
+    g, b = params["ln_in.weight"], params["ln_in.bias"]
+    dt = wa.dtype
+    if dt not in (torch.bfloat16, torch.float32) or wb.dtype != dt or wsq.dtype != dt:
+        raise RuntimeError("the three transition weights must share one dtype, bf16 or fp32")
+    if tuple(wa.shape) != (4 * D, D) or tuple(wb.shape) != (4 * D, D) or tuple(wsq.shape) != (D, 4 * D):
+        raise RuntimeError(f"transition weights must be [{4 * D},{D}], [{4 * D},{D}], [{D},{4 * D}] (d = {D}, n = 4 only)")
+    for name, t in (("expand_a.weight", wa), ("expand_b.weight", wb), ("squeeze.weight", wsq), ("ln_in.weight", g), ("ln_in.bias", b)):
+        _require_cuda(t, name)
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    if g.dtype != torch.float32 or b.dtype != torch.float32:
+        raise RuntimeError("the LayerNorm affine parameters must be fp32")
+    dev = x.device
+    positions = x.numel() // D
+    need = c_size_t(0)
+    _lib.check(_lib.load().b200_transition_backward_workspace_bytes(positions, ctypes.byref(need)),
+               "b200_transition_backward_workspace_bytes")
+    if workspace is None:
+        workspace = aligned_empty(int(need.value), dev)
+    elif workspace.numel() * workspace.element_size() < need.value:
+        raise RuntimeError("workspace too small")
+    dx = torch.empty_like(x)
+    f32 = dict(dtype=torch.float32, device=dev)
+    d_wa, d_wb, d_ws = torch.empty(4 * D, D, **f32), torch.empty(4 * D, D, **f32), torch.empty(D, 4 * D, **f32)
+    d_g, d_b = torch.empty(D, **f32), torch.empty(D, **f32)
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200_transition_backward(
+            _ptr(dy), _ptr(x), _ptr(wa.detach()), _ptr(wb.detach()), _ptr(wsq.detach()),
+            _lib.DTYPE_BF16 if dt == torch.bfloat16 else _lib.DTYPE_F32, _ptr(g.detach()), _ptr(b.detach()), _ptr(dx),
+            _ptr(d_wa), _ptr(d_wb), _ptr(d_ws), _ptr(d_g), _ptr(d_b), _ptr(workspace),
+            workspace.numel() * workspace.element_size(), positions, D, 4, float(eps), int(bool(residual)), _stream(dev),
+        )
+    _lib.check(rc, "b200_transition_backward")
+    if check:
+        check_status(workspace[:4].view(torch.int32), "b200_transition_backward")
+    return dx, {"ln_in.weight": d_g, "ln_in.bias": d_b, "expand_a.weight": d_wa, "expand_b.weight": d_wb,
+                "squeeze.weight": d_ws}

@@ -398,13 +398,20 @@ class Transition(nn.Module):
         return 0 if self._scratch is None else F_.read_status(self._scratch[1])
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if torch.is_grad_enabled() and x.requires_grad:
-            raise NotImplementedError("backward is not implemented: call under torch.no_grad()")
         if not x.is_cuda:
             raise RuntimeError("input must be a CUDA tensor: this module has no CPU implementation")
         if x.shape[-1] != self.d:
             raise RuntimeError(f"input must be [..., {self.d}], got {tuple(x.shape)}")
         in_dtype = x.dtype
+        # the differentiable path is taken when the input requires grad, or in training mode when a parameter does
+        if torch.is_grad_enabled() and (x.requires_grad or (self.training and any(q.requires_grad for q in self.parameters()))):
+            from .training import transition_train
+
+            xb = (x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)).contiguous()
+            params = {"ln_in.weight": self.ln_in.weight, "ln_in.bias": self.ln_in.bias, "expand_a.weight": self.expand_a.weight,
+                      "expand_b.weight": self.expand_b.weight, "squeeze.weight": self.squeeze.weight}
+            y = transition_train(xb, params, eps=float(self.ln_in.eps), residual=self.residual, check=self.check_status)
+            return y if in_dtype == torch.bfloat16 else y.to(in_dtype)
         xb = x.detach()
         if xb.dtype != torch.bfloat16:
             xb = xb.to(torch.bfloat16)

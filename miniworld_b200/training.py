@@ -77,3 +77,44 @@ def trimul_train(z: torch.Tensor, params: dict, token_mask: Optional[torch.Tenso
     cfg = {"outgoing": None if outgoing is None else bool(outgoing), "eps_in": float(eps_in), "eps_out": float(eps_out), "residual": bool(residual),
            "biases": biases, "check": bool(check)}
     return TriMulFunction.apply(z, token_mask, pair_mask, drop_scale, cfg, *[params[k] for k in _PARAM_KEYS])
+
+
+_TRANSITION_KEYS = ("ln_in.weight", "ln_in.bias", "expand_a.weight", "expand_b.weight", "squeeze.weight")
+
+
+class TransitionFunction(torch.autograd.Function):
+    """``y = TransitionFunction.apply(x, cfg, *params)`` for the pair Transition; ``cfg``: ``eps``, ``residual``,
+    ``check``; ``params`` in ``_TRANSITION_KEYS`` order. Nothing but the input is kept for the backward (the hidden
+    activations are recomputed)."""
+
+    @staticmethod
+    def forward(ctx, x, cfg, *params):
+        p = {k: v.detach() for k, v in zip(_TRANSITION_KEYS, params)}
+        packed = F_.aligned_empty(F_.transition_packed_bytes(), x.device)
+        status = torch.zeros(16, dtype=torch.int32, device=x.device)
+        F_.transition_pack_weights(p, packed)
+        y = F_.transition_forward(x.detach(), packed, status, eps=cfg["eps"], residual=cfg["residual"])
+        if cfg["check"]:
+            F_.check_status(status, "b200_transition_forward")
+        ctx.save_for_backward(x, *params)
+        ctx.cfg = cfg
+        return y
+
+    @staticmethod
+    @torch.no_grad()
+    def backward(ctx, dy):
+        x, *params = ctx.saved_tensors
+        cfg = ctx.cfg
+        dx, grads = F_.transition_backward(dy.to(torch.bfloat16).contiguous(), x.detach(),
+                                           {k: v.detach() for k, v in zip(_TRANSITION_KEYS, params)}, eps=cfg["eps"],
+                                           residual=cfg["residual"], check=cfg["check"])
+        out = [dx if ctx.needs_input_grad[0] else None, None]
+        for i, (k, prm) in enumerate(zip(_TRANSITION_KEYS, params)):
+            out.append(grads[k].to(prm.dtype) if ctx.needs_input_grad[2 + i] else None)
+        return tuple(out)
+
+
+def transition_train(x: torch.Tensor, params: dict, *, eps: float = 1e-5, residual: bool = True, check: bool = False):
+    """Differentiable pair Transition: ``x`` [..., 128] bf16 contiguous and the five parameters may require grad."""
+    cfg = {"eps": float(eps), "residual": bool(residual), "check": bool(check)}
+    return TransitionFunction.apply(x, cfg, *[params[k] for k in _TRANSITION_KEYS])

@@ -282,7 +282,8 @@ def bidir_forward(z, params, mask=None, **kw) -> torch.Tensor:
 TRANSITION_KEYS = ("ln_in.weight", "ln_in.bias", "expand_a.weight", "expand_b.weight", "squeeze.weight")
 
 
-def transition_forward(x: torch.Tensor, params: dict, *, eps: float = 1e-5, residual: bool = True) -> torch.Tensor:
+def transition_forward(x: torch.Tensor, params: dict, *, eps: float = 1e-5, residual: bool = True,
+                       differentiable: bool = False) -> torch.Tensor:
     """fp32 forward of the pair Transition that follows the triangle update in every block
     (``src/miniworld/modules/mini_pairformer.py:81-84,108`` of the reference project):
 
@@ -294,8 +295,9 @@ def transition_forward(x: torch.Tensor, params: dict, *, eps: float = 1e-5, resi
     residual: ``scripts/render_transition_fusion.py:218,262`` and ``docs/h100-kernel-upgrade.md:14``). PARITY
     UNPINNED like the rest of this file: the module's source is in the same un-vendored wheel.
     """
-    p = {k: v.detach().to(torch.float32) for k, v in params.items()}
-    xf = x.detach().to(torch.float32)
+    keep = (lambda v: v.to(torch.float32)) if differentiable else (lambda v: v.detach().to(torch.float32))
+    p = {k: keep(v) for k, v in params.items()}
+    xf = keep(x)  # differentiable: autograd through this restatement is the backward oracle
     C = xf.shape[-1]
     xn = F.layer_norm(xf, (C,), p["ln_in.weight"], p["ln_in.bias"], eps)
     hdn = F.silu(F.linear(xn, p["expand_a.weight"])) * F.linear(xn, p["expand_b.weight"])

@@ -113,3 +113,49 @@ def test_transition_large_offsets_and_saturation():
     with torch.no_grad():
         y = _module(p)(x.to(DEV))
     assert torch.isfinite(y.float()).all()
+
+
+def _oracle_grads(x, p, dy, **kw):
+    xf = x.detach().float().requires_grad_(True)
+    pf = {k: v.detach().clone().float().requires_grad_(True) for k, v in p.items()}
+    y = oracle.transition_forward(xf, pf, differentiable=True, **kw)
+    y.backward(dy.float())
+    return y.detach(), xf.grad, {k: v.grad for k, v in pf.items()}
+
+
+def _rel(a, b):
+    return oracle.rel_frobenius(a.detach().float().cpu(), b.detach().float().cpu())
+
+
+@pytest.mark.parametrize("shape,residual,dtype", [((1, 64, 64, 128), True, torch.bfloat16), ((2, 77, 77, 128), True, torch.bfloat16),
+                                                  ((1, 200, 136, 128), False, torch.float32), ((1, 384, 384, 128), True, torch.bfloat16)])
+def test_transition_gradients_match_the_oracle(shape, residual, dtype):
+    """Backward of the pair Transition: gradients of the input and the five parameters against autograd through the
+    fp32 oracle (relative L2 below 1e-2 each; the reference's bound for its fused transition is a few 1e-3 against fp32
+    PyTorch, docs/engine2-training-connection.md:121 in the reference project), bit-identical on repetition."""
+    p = transition_params(900 + shape[1], dtype=dtype)
+    g = torch.Generator().manual_seed(901 + shape[1])
+    x = torch.randn(*shape, generator=g).to(torch.bfloat16)
+    dy = (torch.randn(*shape, generator=g) * 0.01).to(torch.bfloat16)
+    y_ref, dx_ref, gp_ref = _oracle_grads(x, p, dy, residual=residual)
+    m = mw.Transition(128, residual=residual, check_status=True)
+    m.load_state_dict({k: v.clone() for k, v in p.items()})
+    m = m.to(DEV).to(dtype).train()
+    runs = []
+    for _ in range(2):
+        m.zero_grad()
+        xd = x.to(DEV).requires_grad_(True)
+        y = m(xd)
+        y.backward(dy.to(DEV))
+        runs.append((xd.grad.clone(), {k: v.grad.clone() for k, v in m.named_parameters()}))
+    assert _rel(y, y_ref) <= 5e-3
+    errs = {"dx": _rel(runs[0][0], dx_ref)}
+    for k in gp_ref:
+        assert runs[0][1][k].shape == gp_ref[k].shape
+        errs[k] = _rel(runs[0][1][k], gp_ref[k])
+        assert torch.equal(runs[0][1][k], runs[1][1][k]), k
+    assert torch.equal(runs[0][0], runs[1][0])
+    print("[transition grads]", {k: f"{v:.2e}" for k, v in errs.items()})
+    assert max(errs.values()) <= 1e-2, errs
+    y_eval = m.eval()(x.to(DEV))
+    assert not y_eval.requires_grad

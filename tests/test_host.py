@@ -84,7 +84,7 @@ def test_unsupported_configurations_raise():
         m(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16, requires_grad=True))
     with pytest.raises(RuntimeError, match="CUDA"):
         mw.BidirectionalTriangleMultiplication(64)(torch.zeros(1, 8, 8, 64, dtype=torch.bfloat16, requires_grad=True))
-    with pytest.raises(NotImplementedError):  # the Transition has no backward
+    with pytest.raises(RuntimeError, match="CUDA"):
         mw.Transition(128)(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16, requires_grad=True))
     with pytest.raises(RuntimeError):
         mw.TriangleMultiplication(128).eval()(torch.zeros(1, 8, 8, 128), torch.ones(1, 8, 8, dtype=torch.bool))

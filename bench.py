@@ -637,6 +637,19 @@ def block_operators(r: "Runner", steps: int, stream, dev) -> dict:
     if bid.device_status() != 0 or tr.device_status() != 0:
         raise SystemExit("bidirectional / transition forward reported a device status")
     out["training"] = training_step(r, steps, stream, dev, bid)
+    # the Transition's training step on the same input
+    params = {k: v.detach() for k, v in tr.state_dict().items()}
+    dy = (torch.randn(r.z.shape, generator=torch.Generator(device=dev).manual_seed(79), device=dev) * 0.01).to(torch.bfloat16)
+    from miniworld_b200 import functional as F_
+
+    def tr_bwd():
+        F_.transition_backward(dy, r.z, params)
+
+    for _ in range(3):
+        tr_bwd()
+    ms = sorted(time_events(tr_bwd, steps, stream) / steps for _ in range(REPEATS))
+    out["training"]["transition"] = {"ms_forward": out["transition"]["ms_per_forward"], "ms_backward": statistics.median(ms),
+                                     "backward_over_forward": statistics.median(ms) / out["transition"]["ms_per_forward"]}
     return out
 
 

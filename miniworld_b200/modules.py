@@ -17,9 +17,8 @@ shapes.
 
 In training mode with ``p_drop > 0`` the forward applies the row-shared dropout of the reference
 (``x + drop_row(f(x))``: one keep-mask per (batch, column, channel), shared by all rows,
-``src/miniworld/blocks/template.py:38-40``). Every triangle-update module is differentiable (input and all ten parameters, :mod:`miniworld_b200.training`); the
-Transition has no backward: calling it with gradients enabled on an input that requires them raises
-``NotImplementedError``.
+``src/miniworld/blocks/template.py:38-40``). Every module here is differentiable (:mod:`miniworld_b200.training`): the triangle updates (input and all ten
+parameters) and the pair Transition (input and its five parameters).
 """
 
 from __future__ import annotations
@@ -363,7 +362,7 @@ class BidirectionalTriangleMultiplication(TriangleMultiplication):
 
 
 class Transition(nn.Module):
-    """Pair transition ``x + squeeze(SiLU(expand_a(LN x)) * expand_b(LN x))``, forward only, on the B200 kernel.
+    """Pair transition ``x + squeeze(SiLU(expand_a(LN x)) * expand_b(LN x))`` on the B200 kernels (forward and backward).
 
     Mirrors ``miniworld_engine.modules.Transition(d, n=4, implementation=...)`` as MiniWorld's blocks build it
     (``src/miniworld/modules/mini_pairformer.py:81-84``; it owns its residual, ``:108``): parameters ``ln_in`` [d],

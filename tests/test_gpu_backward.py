@@ -349,3 +349,33 @@ def test_training_step_replays_from_a_cuda_graph():
         for k in _PARAM_KEYS:
             assert torch.equal(grads_r[k], grads_e[k]), k
     F_.check_status(bws[:64].view(torch.int32), "b200_trimul_backward")
+
+
+@pytest.mark.parametrize("kind", ["common_offset_20", "heavy_tail"])
+def test_backward_numerical_corners(kind):
+    """The backward on the inputs of the forward's numerical corner cases: a common offset of 20 on z (|mean| = 20 sigma
+    at every position), and heavy-tailed z with 128 x larger projection weights (|t| of a few 1e5, a third of the fp16
+    range of the stored t): gradients stay finite and keep the usual accuracy (measured 2e-3 in both cases)."""
+    N = 128
+    g = torch.Generator().manual_seed(570)
+    p = rand_params(571, ln_bias_scale=0.2)
+    z = torch.randn(1, N, N, 128, generator=g)
+    tol = GRAD_REL_TOL
+    if kind == "common_offset_20":
+        z = z + 20.0
+    else:
+        for k in ("to_left.weight", "to_right.weight"):
+            p[k] = (p[k].float() * 128.0).to(torch.bfloat16)
+        spikes = torch.rand(1, N, N, 128, generator=g) < 0.01
+        z = torch.where(spikes, z * 30.0, z)
+    z = z.to(torch.bfloat16)
+    dy = torch.randn(1, N, N, 128, generator=g).to(torch.bfloat16)
+    mask = torch.rand(1, N, generator=g) > 0.1
+    y_ref, dz_ref, gp_ref = _oracle_grads(z, p, mask, dy, True)
+    zd = z.to(DEV).requires_grad_(True)
+    pd = {k: v.detach().to(DEV).requires_grad_(True) for k, v in p.items()}
+    y = trimul_train(zd, pd, mask.to(DEV), outgoing=True, check=True)
+    y.backward(dy.to(DEV))
+    _check("dz", zd.grad, dz_ref, tol)
+    for k in _PARAM_KEYS:
+        _check(k, pd[k].grad, gp_ref[k], tol)

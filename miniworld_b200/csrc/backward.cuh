@@ -842,6 +842,16 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       }
       umma_commit(mma_bar);
     }
+    // the running d x_hat of this thread's channels: requested now, used after the GEMM round
+    const bool inside = j < p.n;
+    uint4 dx_prev[kZChunks];
+#pragma unroll
+    for (int ch = 0; ch < kZChunks; ++ch) dx_prev[ch] = make_uint4(0u, 0u, 0u, 0u);
+    if (inside) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
+#pragma unroll
+      for (int ch = 0; ch < kZChunks; ++ch) dx_prev[ch] = __ldg(src + ch);
+    }
     if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
     if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
@@ -850,16 +860,13 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     }
     // ---- phase 5: add the running d x_hat; !LAST: write it back, LAST: LayerNorm backward + residual -> dz
     {
-      const bool inside = j < p.n;
-      const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * C + part * kZCh);
       float tot[kZCh];
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
       for (int ch = 0; ch < kZChunks; ++ch) {
         uint32_t v[8];
         tmem_ld8(tmem_base + lane_sel + part * kZCh + ch * 8, v);
-        uint4 in = make_uint4(0u, 0u, 0u, 0u);
-        if (inside) in = __ldg(src + ch);
+        const uint4 in = dx_prev[ch];
         uint4 xh = make_uint4(0u, 0u, 0u, 0u);
         if constexpr (LAST) xh = ld_chunk(z_s + tile_chunk(pos, part * kZChunks + ch));
         tmem_ld_wait();
@@ -886,19 +893,24 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 4], tot[ch * 8 + 5])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 6], tot[ch * 8 + 7])));
       } else {
+        uint4 dy_res[kZChunks];  // the residual branch's share of dz, requested ahead of the exchange
+#pragma unroll
+        for (int ch = 0; ch < kZChunks; ++ch) dy_res[ch] = make_uint4(0u, 0u, 0u, 0u);
+        if (p.dy != nullptr && inside) {
+          const uint4* dyp = reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
+#pragma unroll
+          for (int ch = 0; ch < kZChunks; ++ch) dy_res[ch] = __ldg(dyp + ch);
+        }
         asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
         named_bar_sync(1, kBwdThreads);
         float m1, m2;
         sum_partials(xchg, pos, m1, m2);
         m1 *= 1.0f / C, m2 *= 1.0f / C;
         const float rs = rstd_in * gc_inv;
-        const uint4* dyp = p.dy == nullptr ? nullptr
-                                           : reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + (inside ? j : 0)) * C + part * kZCh);
 #pragma unroll
         for (int ch = 0; ch < kZChunks; ++ch) {
           const uint4 xh = ld_chunk(z_s + tile_chunk(pos, part * kZChunks + ch));
-          uint4 dyv = make_uint4(0u, 0u, 0u, 0u);
-          if (dyp != nullptr && inside) dyv = __ldg(dyp + ch);
+          const uint4 dyv = dy_res[ch];
           const uint32_t xw[4] = {xh.x, xh.y, xh.z, xh.w};
           const uint32_t dw[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
           uint32_t o[4];

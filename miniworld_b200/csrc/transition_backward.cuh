@@ -291,23 +291,30 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                   idesc_m, (ks != 0 ? 1u : 0u) | accum);
       umma_commit(mma_bar);
     }
+    // the earlier launches' running d x_hat for this thread: requested now, used after the GEMM round
+    const long long gp = static_cast<long long>(p0) + pos;
+    const bool inside = gp < p.positions;
+    uint4 dx_prev[kBwdChunks];
+#pragma unroll
+    for (int ch = 0; ch < kBwdChunks; ++ch) dx_prev[ch] = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (!FIRST) {
+      if (inside) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + gp * 128 + part * kBwdCh);
+#pragma unroll
+        for (int ch = 0; ch < kBwdChunks; ++ch) dx_prev[ch] = __ldg(src + ch);
+      }
+    }
     if (!mma_wait()) { ok = false; break; }
     tc_fence_after();
     // ---- the running d x_hat: add the earlier launches' sum; LAST: LayerNorm backward + residual -> dx (bf16)
     {
-      const long long gp = static_cast<long long>(p0) + pos;
-      const bool inside = gp < p.positions;
-      const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (inside ? gp : 0) * 128 + part * kBwdCh);
       float tot[kBwdCh];
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
       for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t v[8];
         tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
-        uint4 in = make_uint4(0u, 0u, 0u, 0u);
-        if constexpr (!FIRST) {
-          if (inside) in = __ldg(src + ch);
-        }
+        const uint4 in = dx_prev[ch];
         uint4 xh = make_uint4(0u, 0u, 0u, 0u);
         if constexpr (LAST) xh = ld_chunk(x_s + tile_chunk(pos, part * kBwdChunks + ch));
         tmem_ld_wait();

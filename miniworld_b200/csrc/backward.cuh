@@ -693,7 +693,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
     mbar_init(in_full, 1);
-    mbar_init(mma_bar, 1);
+    mbar_init(mma_bar, 2);  // two issuing threads commit to it in every GEMM round
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&map_z);
@@ -761,19 +761,19 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     tc_fence_before();
     __syncthreads();
     // ---- phase 2: value = x_hat Wv'^T (columns 0-127), gate = x_hat Wg'^T (128-255)
-    if (threadIdx.x == 0) {
+    // (the GEMMs of a round are issued by two threads, one per accumulator group: one thread's issue rate does not
+    // keep the tensor pipe busy)
+    if (threadIdx.x == 0 || threadIdx.x == 32) {
+      const int m = threadIdx.x >> 5;
       // this tile's dgate scratch held the previous tile's output: its store must have read it before phase 3
-      bulk_wait_read<0>();
+      if (m == 0) bulk_wait_read<0>();
       tc_fence_after();
       constexpr uint32_t idesc = umma_idesc(128, 128, false, false, kFmtF16, kFmtF16);
 #pragma unroll
-      for (int m = 0; m < 2; ++m) {
-#pragma unroll
-        for (int ks = 0; ks < C / 16; ++ks) {
-          const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
-          umma_bf16(tmem_base + m * 128, umma_desc_kmajor(z_s + (ks >> 2) * 16384) + kb,
-                    umma_desc_kmajor((m == 0 ? wv_s : wg_s) + (ks >> 2) * 16384) + kb, idesc, ks != 0 ? 1u : 0u);
-        }
+      for (int ks = 0; ks < C / 16; ++ks) {
+        const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+        umma_bf16(tmem_base + m * 128, umma_desc_kmajor(z_s + (ks >> 2) * 16384) + kb,
+                  umma_desc_kmajor((m == 0 ? wv_s : wg_s) + (ks >> 2) * 16384) + kb, idesc, ks != 0 ? 1u : 0u);
       }
       umma_commit(mma_bar);
     }
@@ -821,8 +821,6 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     if (threadIdx.x == 0) {
       tc_fence_after();
       constexpr uint32_t idesc_d = umma_idesc(128, C, false, true, kFmtF16, kFmtF16);
-      constexpr uint32_t idesc_m = umma_idesc(128, C, true, true, kFmtF16, kFmtF16);
-      const uint32_t accum = it != 0 ? 1u : 0u;
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
 #pragma unroll
@@ -832,6 +830,11 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                     umma_desc_mnmajor((m == 0 ? wv_s : wg_s) + ks * 2048, 16384), idesc_d, (m | ks) != 0 ? 1u : 0u);
         }
       }
+      umma_commit(mma_bar);
+    } else if (threadIdx.x == 32) {
+      tc_fence_after();
+      constexpr uint32_t idesc_m = umma_idesc(128, C, true, true, kFmtF16, kFmtF16);
+      const uint32_t accum = it != 0 ? 1u : 0u;
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
 #pragma unroll

@@ -683,7 +683,6 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   const uint32_t w_full = bar_base, in_full = bar_base + 8, mma_bar = bar_base + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + kBwdXchg + 1024 + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + kBwdXchg);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = warp & 3, part = warp >> 2;
@@ -700,7 +699,6 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     prefetch_tmap(&map_do);
     prefetch_tmap(&map_out);
   }
-  if (threadIdx.x < 256) const_ptr[threadIdx.x] = p.consts[threadIdx.x];
   if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
@@ -710,6 +708,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const float gc_inv = p.grad_scale[1];
+  const float c_value = p.consts[pos], c_gate_half = 0.5f * p.consts[128 + pos];  // this thread's channel
 
   if (threadIdx.x == 0) {
     mbar_arrive_expect_tx(w_full, 2 * kZHalves * 16384);
@@ -719,9 +718,11 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       tma_load_2d(wg_s + kh * 16384, &map_wg, w_full, kh * 64, 0);
     }
   }
-  float acc_sv[kBwdCh], acc_sg[kBwdCh];
-#pragma unroll
-  for (int c = 0; c < kBwdCh; ++c) acc_sv[c] = 0.f, acc_sg[c] = 0.f;
+  // Phases 2-3 work on the transposed projections (TMEM lanes = contracted channels, columns = positions): a thread
+  // owns channel `pos` (its lane) and the position quarter `part`, so its constants and its column sums are scalars
+  // and dO, stored [channel][position], is read in 16-byte runs of positions.
+  float acc_sv = 0.f, acc_sg = 0.f;
+  uint32_t* valid_words = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + kBwdXchg + 1024 + 64);  // one per 32 positions
 
   // Buffer roles (z, dO, dvalue, dgate) of tile `it`, one nibble each, period 4: the next tile's z and dO are copied
   // into this tile's dO buffer (free after phase 3) and dgate buffer (free after the gradient GEMMs) while this tile
@@ -752,6 +753,17 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     const int row = tile / p.tiles_per_row;
     const int j0 = (tile - row * p.tiles_per_row) * 128;
     const uint32_t z_s = role(it, 0), do_s = role(it, 1), dv_s = role(it, 2), dg_s = role(it, 3);
+    const int j = j0 + pos;
+    if (part == 0) {  // validity of the tile's positions, one bit each (read in phase 3, two CTA barriers later)
+      const int b = row / p.n;
+      const int i = row - b * p.n;
+      bool valid = j < p.n;
+      if (valid && p.token_mask != nullptr)
+        valid = p.token_mask[static_cast<size_t>(b) * p.n + i] != 0 && p.token_mask[static_cast<size_t>(b) * p.n + j] != 0;
+      if (valid && p.pair_mask != nullptr) valid = p.pair_mask[(static_cast<size_t>(b) * p.n + i) * p.n + j] != 0;
+      const uint32_t word = __ballot_sync(0xFFFFFFFFu, valid);
+      if (lane == 0) valid_words[q] = word;
+    }
     if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
     if (threadIdx.x == 0) in_pending = -1;
@@ -760,7 +772,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
-    // ---- phase 2: value = x_hat Wv'^T (columns 0-127), gate = x_hat Wg'^T (128-255)
+    // ---- phase 2: value^T = Wv' x_hat^T (columns 0-127), gate^T = Wg' x_hat^T (128-255): lanes = contracted channels
     // (the GEMMs of a round are issued by two threads, one per accumulator group: one thread's issue rate does not
     // keep the tensor pipe busy)
     if (threadIdx.x == 0 || threadIdx.x == 32) {
@@ -772,74 +784,83 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 #pragma unroll
       for (int ks = 0; ks < C / 16; ++ks) {
         const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
-        umma_bf16(tmem_base + m * 128, umma_desc_kmajor(z_s + (ks >> 2) * 16384) + kb,
-                  umma_desc_kmajor((m == 0 ? wv_s : wg_s) + (ks >> 2) * 16384) + kb, idesc, ks != 0 ? 1u : 0u);
+        umma_bf16(tmem_base + m * 128, umma_desc_kmajor((m == 0 ? wv_s : wg_s) + (ks >> 2) * 16384) + kb,
+                  umma_desc_kmajor(z_s + (ks >> 2) * 16384) + kb, idesc, ks != 0 ? 1u : 0u);
       }
       umma_commit(mma_bar);
     }
     if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
-    // ---- phase 3: dvalue, dgate for this thread's position and 64 contracted channels
-    const int j = j0 + pos;
+    // ---- phase 3: dvalue, dgate for this thread's channel and 32 positions, stored [channel][position]
     {
-      const int b = row / p.n;
-      const int i = row - b * p.n;
-      bool valid = j < p.n;
-      if (valid && p.token_mask != nullptr)
-        valid = p.token_mask[static_cast<size_t>(b) * p.n + i] != 0 && p.token_mask[static_cast<size_t>(b) * p.n + j] != 0;
-      if (valid && p.pair_mask != nullptr) valid = p.pair_mask[(static_cast<size_t>(b) * p.n + i) * p.n + j] != 0;
-      const float vm = valid ? 16.0f : 0.f;  // the contraction's outputs are stored times 2^-4
+      const uint32_t vbits = valid_words[part];
+      uint32_t vv[32], vg[32];
+      tmem_ld32(tmem_base + lane_sel + part * 32, vv);
+      tmem_ld32(tmem_base + lane_sel + 128 + part * 32, vg);
+      uint4 dov[4];
 #pragma unroll
-      for (int ch = 0; ch < kBwdChunks; ++ch) {
-        uint32_t vv[8], vg[8];
-        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, vv);
-        tmem_ld8(tmem_base + lane_sel + 128 + part * kBwdCh + ch * 8, vg);
-        tmem_ld_wait();
-        float dvv[8], dgv[8];
+      for (int k4 = 0; k4 < 4; ++k4) dov[k4] = ld_chunk(do_s + tile_chunk(pos, part * 4 + k4));
+      tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int h = part * kBwdCh + ch * 8 + e;
-          const float val = __uint_as_float(vv[e]) + const_ptr[h];
-          const float sg = sigmoid_fast(__uint_as_float(vg[e]) + const_ptr[128 + h]);
-          const float d_o = ld_f16(do_s + tile_off(h, pos)) * vm;
-          dvv[e] = d_o * sg;
-          dgv[e] = d_o * val * sg * (1.0f - sg);
-          acc_sv[ch * 8 + e] += dvv[e];
-          acc_sg[ch * 8 + e] += dgv[e];
+      for (int k4 = 0; k4 < 4; ++k4) {
+        const uint32_t dw[4] = {dov[k4].x, dov[k4].y, dov[k4].z, dov[k4].w};
+        uint32_t ov[4], og[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float2 d_o = f16x2_to_float2(dw[t]);
+          const int e0 = k4 * 8 + 2 * t;
+          if (vbits != 0xFFFFFFFFu) {
+            d_o.x = ((vbits >> e0) & 1u) ? d_o.x : 0.f;
+            d_o.y = ((vbits >> (e0 + 1)) & 1u) ? d_o.y : 0.f;
+          }
+          float dv2[2], dg2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const float val = __uint_as_float(vv[e0 + u]) + c_value;
+            const float th = tanh_approx(fmaf(__uint_as_float(vg[e0 + u]), 0.5f, c_gate_half));
+            const float sg = fmaf(th, 0.5f, 0.5f);
+            const float sg16 = fmaf(th, 8.0f, 8.0f);  // the contraction's outputs are stored times 2^-4
+            dv2[u] = (u == 0 ? d_o.x : d_o.y) * sg16;
+            dg2[u] = dv2[u] * fmaf(-val, sg, val);
+            acc_sv += dv2[u];
+            acc_sg += dg2[u];
+          }
+          ov[t] = pack_f16x2_sat(make_float2(dv2[0], dv2[1]));
+          og[t] = pack_f16x2_sat(make_float2(dg2[0], dg2[1]));
         }
-        const uint32_t addr = tile_chunk(pos, part * kBwdChunks + ch);
-        st_chunk(dv_s + addr, pack_f16x2_sat(make_float2(dvv[0], dvv[1])), pack_f16x2_sat(make_float2(dvv[2], dvv[3])),
-                 pack_f16x2_sat(make_float2(dvv[4], dvv[5])), pack_f16x2_sat(make_float2(dvv[6], dvv[7])));
-        st_chunk(dg_s + addr, pack_f16x2_sat(make_float2(dgv[0], dgv[1])), pack_f16x2_sat(make_float2(dgv[2], dgv[3])),
-                 pack_f16x2_sat(make_float2(dgv[4], dgv[5])), pack_f16x2_sat(make_float2(dgv[6], dgv[7])));
+        const uint32_t addr = tile_chunk(pos, part * 4 + k4);
+        st_chunk(dv_s + addr, ov[0], ov[1], ov[2], ov[3]);
+        st_chunk(dg_s + addr, og[0], og[1], og[2], og[3]);
       }
     }
     tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
-    // ---- phase 4: d x_hat = dvalue Wv' + dgate Wg' (columns 0-127); Mv += dvalue^T x_hat (256-383), Mg += dgate^T x_hat
+    // ---- phase 4: d x_hat = dvalue Wv' + dgate Wg' (columns 0-127, lanes = positions); Mv += dvalue^T x_hat (256-383),
+    // Mg += dgate^T x_hat (384-511). dvalue / dgate are [channel][position] tiles: MN-major as the A operand of the
+    // first pair of GEMMs (M = positions), K-major as that of the second (M = channels, K = positions).
     if (threadIdx.x == 0) {
       tc_fence_after();
-      constexpr uint32_t idesc_d = umma_idesc(128, C, false, true, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_d = umma_idesc(128, C, true, true, kFmtF16, kFmtF16);
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
-          umma_bf16(tmem_base, umma_desc_kmajor((m == 0 ? dv_s : dg_s) + (ks >> 2) * 16384) + kb,
+          umma_bf16(tmem_base, umma_desc_mnmajor((m == 0 ? dv_s : dg_s) + ks * 2048, 16384),
                     umma_desc_mnmajor((m == 0 ? wv_s : wg_s) + ks * 2048, 16384), idesc_d, (m | ks) != 0 ? 1u : 0u);
         }
       }
       umma_commit(mma_bar);
     } else if (threadIdx.x == 32) {
       tc_fence_after();
-      constexpr uint32_t idesc_m = umma_idesc(128, C, true, true, kFmtF16, kFmtF16);
+      constexpr uint32_t idesc_m = umma_idesc(128, C, false, true, kFmtF16, kFmtF16);
       const uint32_t accum = it != 0 ? 1u : 0u;
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          umma_bf16(tmem_base + 256 + m * 128, umma_desc_mnmajor((m == 0 ? dv_s : dg_s) + ks * 2048, 16384),
+          const uint64_t kb = static_cast<uint64_t>((ks & 3) * 2);
+          umma_bf16(tmem_base + 256 + m * 128, umma_desc_kmajor((m == 0 ? dv_s : dg_s) + (ks >> 2) * 16384) + kb,
                     umma_desc_mnmajor(z_s + ks * 2048, 16384), idesc_m, (ks != 0 ? 1u : 0u) | accum);
         }
       }
@@ -865,14 +886,16 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     {
       float tot[kZCh];
       float s1 = 0.f, s2 = 0.f;
+      uint32_t vt[kZChunks][8];
+#pragma unroll
+      for (int ch = 0; ch < kZChunks; ++ch) tmem_ld8(tmem_base + lane_sel + part * kZCh + ch * 8, vt[ch]);
+      tmem_ld_wait();
 #pragma unroll
       for (int ch = 0; ch < kZChunks; ++ch) {
-        uint32_t v[8];
-        tmem_ld8(tmem_base + lane_sel + part * kZCh + ch * 8, v);
+        const uint32_t(&v)[8] = vt[ch];
         const uint4 in = dx_prev[ch];
         uint4 xh = make_uint4(0u, 0u, 0u, 0u);
         if constexpr (LAST) xh = ld_chunk(z_s + tile_chunk(pos, part * kZChunks + ch));
-        tmem_ld_wait();
         const uint32_t iw[4] = {in.x, in.y, in.z, in.w};
         const uint32_t xw[4] = {xh.x, xh.y, xh.z, xh.w};
 #pragma unroll
@@ -966,9 +989,16 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       }
     }
   }
-  {
-    float* ps = p.part_s + static_cast<size_t>(blockIdx.x) * 2 * 128;
-    flush_colsums(acc_sv, acc_sg, smem, pos, part, ps, ps + 128);
+  {  // column sums: the four position quarters of a channel, fixed order
+    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(acc_sv), "f"(acc_sg) : "memory");
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      float a, b;
+      sum_partials(xchg, threadIdx.x, a, b);
+      float* ps = p.part_s + static_cast<size_t>(blockIdx.x) * 2 * 128;
+      ps[threadIdx.x] = a;
+      ps[128 + threadIdx.x] = b;
+    }
   }
   tc_fence_before();
   __syncthreads();

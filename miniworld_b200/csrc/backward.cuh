@@ -64,6 +64,25 @@ __device__ __forceinline__ uint4 ld_chunk(uint32_t addr) {
 __device__ __forceinline__ void st_chunk(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+// 32 bytes per thread in one request (address 32-byte aligned): a warp whose lanes read different 128-byte lines pays
+// per line and request, so half as many requests as with 16-byte loads
+__device__ __forceinline__ void ldg_32B(const void* p, uint4& a, uint4& b) {
+  asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+               : "l"(p));
+}
+// `chunks` 16-byte pieces (an even count) from p: 32-byte requests if the address allows, else 16-byte ones
+template <int CHUNKS>
+__device__ __forceinline__ void ldg_chunks(const uint4* p, bool wide, uint4 (&out)[CHUNKS]) {
+  static_assert(CHUNKS % 2 == 0, "pairs of 16-byte chunks");
+  if (wide) {
+#pragma unroll
+    for (int c = 0; c < CHUNKS; c += 2) ldg_32B(p + c, out[c], out[c + 1]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) out[c] = __ldg(p + c);
+  }
+}
 __device__ __forceinline__ float sigmoid_fast(float x) { return fmaf(tanh_approx(0.5f * x), 0.5f, 0.5f); }
 
 // CTA-wide bounded wait on an mbarrier: one lane per warp polls, the decision is shared by all 256 threads.
@@ -873,8 +892,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     for (int ch = 0; ch < kZChunks; ++ch) dx_prev[ch] = make_uint4(0u, 0u, 0u, 0u);
     if (inside) {
       const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
-#pragma unroll
-      for (int ch = 0; ch < kZChunks; ++ch) dx_prev[ch] = __ldg(src + ch);
+      ldg_chunks(src, true, dx_prev);  // the workspace is 1024-byte aligned
     }
     if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
@@ -924,8 +942,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
         for (int ch = 0; ch < kZChunks; ++ch) dy_res[ch] = make_uint4(0u, 0u, 0u, 0u);
         if (p.dy != nullptr && inside) {
           const uint4* dyp = reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
-#pragma unroll
-          for (int ch = 0; ch < kZChunks; ++ch) dy_res[ch] = __ldg(dyp + ch);
+          ldg_chunks(dyp, (reinterpret_cast<uintptr_t>(p.dy) & 31u) == 0, dy_res);
         }
         asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
         named_bar_sync(1, kBwdThreads);

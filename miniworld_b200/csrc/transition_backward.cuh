@@ -300,8 +300,7 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     if constexpr (!FIRST) {
       if (inside) {
         const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + gp * 128 + part * kBwdCh);
-#pragma unroll
-        for (int ch = 0; ch < kBwdChunks; ++ch) dx_prev[ch] = __ldg(src + ch);
+        ldg_chunks(src, true, dx_prev);  // the workspace is 1024-byte aligned
       }
     }
     if (!mma_wait()) { ok = false; break; }

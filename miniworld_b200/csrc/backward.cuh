@@ -710,7 +710,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
-    mbar_init(in_full, 1);
+    mbar_init(in_full, 2);  // a tile's z and dO copies are issued at different times, one arrival each
     mbar_init(mma_bar, 2);  // two issuing threads commit to it in every GEMM round
     *abort_flag = 0;
     fence_mbar_init();
@@ -751,13 +751,19 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     const uint32_t rr = static_cast<uint32_t>(0x1302012320313210ull >> (16 * (it_i & 3))) & 0xFFFFu;
     return tiles_s + ((rr >> (4 * r)) & 0xFu) * kBwdTile;
   };
-  auto issue_in = [&](int tile_i, int it_i) {
+  auto issue_z = [&](int tile_i, int it_i) {
     const int row_i = tile_i / p.tiles_per_row;
     const int j_i = (tile_i - row_i * p.tiles_per_row) * 128;
-    const uint32_t z_i = role(it_i, 0), do_i = role(it_i, 1);
-    mbar_arrive_expect_tx(in_full, kBwdTile + kZHalves * 16384);
+    const uint32_t z_i = role(it_i, 0);
+    mbar_arrive_expect_tx(in_full, kZHalves * 16384);
 #pragma unroll
     for (int kh = 0; kh < kZHalves; ++kh) tma_load_3d(z_i + kh * 16384, &map_z, in_full, kh * 64, j_i, row_i);
+  };
+  auto issue_do = [&](int tile_i, int it_i) {
+    const int row_i = tile_i / p.tiles_per_row;
+    const int j_i = (tile_i - row_i * p.tiles_per_row) * 128;
+    const uint32_t do_i = role(it_i, 1);
+    mbar_arrive_expect_tx(in_full, kBwdTile);
 #pragma unroll
     for (int kh = 0; kh < 2; ++kh) tma_load_3d(do_i + kh * 16384, &map_do, in_full, j_i + kh * 64, 0, row_i);
   };
@@ -765,7 +771,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   int it = 0;
   int in_pending = -1;  // thread 0: iteration whose copies are in flight, or -1
   if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < p.num_tiles) {
-    issue_in(blockIdx.x, 0);
+    issue_z(blockIdx.x, 0);
+    issue_do(blockIdx.x, 0);
     in_pending = 0;
   }
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
@@ -855,6 +862,10 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
+    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
+      issue_z(tile + gridDim.x, it + 1);  // into this tile's dO buffer, read for the last time in phase 3
+      in_pending = it + 1;
+    }
     // ---- phase 4: d x_hat = dvalue Wv' + dgate Wg' (columns 0-127, lanes = positions); Mv += dvalue^T x_hat (256-383),
     // Mg += dgate^T x_hat (384-511). dvalue / dgate are [channel][position] tiles: MN-major as the A operand of the
     // first pair of GEMMs (M = positions), K-major as that of the second (M = channels, K = positions).
@@ -894,12 +905,19 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       const uint4* src = reinterpret_cast<const uint4*>(p.dx_in + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
       ldg_chunks(src, true, dx_prev);  // the workspace is 1024-byte aligned
     }
+    uint4 dy_res[LAST ? kZChunks : 2];  // LAST: the residual branch's share of dz, requested at the same time
+    if constexpr (LAST) {
+#pragma unroll
+      for (int ch = 0; ch < kZChunks; ++ch) dy_res[ch] = make_uint4(0u, 0u, 0u, 0u);
+      if (p.dy != nullptr && inside) {
+        const uint4* dyp = reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
+        ldg_chunks(dyp, (reinterpret_cast<uintptr_t>(p.dy) & 31u) == 0, dy_res);
+      }
+    }
     if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
-    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
-      issue_in(tile + gridDim.x, it + 1);  // into this tile's dO and dgate buffers
-      in_pending = it + 1;
-    }
+    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles)
+      issue_do(tile + gridDim.x, it + 1);  // into this tile's dgate buffer, free once the gradient GEMMs are done
     // ---- phase 5: add the running d x_hat; !LAST: write it back, LAST: LayerNorm backward + residual -> dz
     {
       float tot[kZCh];
@@ -937,13 +955,6 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 4], tot[ch * 8 + 5])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 6], tot[ch * 8 + 7])));
       } else {
-        uint4 dy_res[kZChunks];  // the residual branch's share of dz, requested ahead of the exchange
-#pragma unroll
-        for (int ch = 0; ch < kZChunks; ++ch) dy_res[ch] = make_uint4(0u, 0u, 0u, 0u);
-        if (p.dy != nullptr && inside) {
-          const uint4* dyp = reinterpret_cast<const uint4*>(p.dy + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
-          ldg_chunks(dyp, (reinterpret_cast<uintptr_t>(p.dy) & 31u) == 0, dy_res);
-        }
         asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
         named_bar_sync(1, kBwdThreads);
         float m1, m2;

@@ -53,7 +53,8 @@ __device__ __forceinline__ float ld_f16(uint32_t addr) {
   return __half2float(__ushort_as_half(v));
 }
 __device__ __forceinline__ void st_f16_sat(uint32_t addr, float x) {
-  const uint16_t v = __half_as_ushort(__float2half_rn(fminf(fmaxf(x, -65504.f), 65504.f)));
+  uint16_t v;
+  asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(v) : "f"(x));
   asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
 }
 __device__ __forceinline__ uint4 ld_chunk(uint32_t addr) {
@@ -99,6 +100,7 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
   constexpr int kCh = CT / kBwdParts;  // channels per thread
   constexpr int kChunks = kCh / 8;
   float pv = 0.f, s1 = 0.f, s2 = 0.f;
+  float xt[ROWS_ARE_POSITIONS ? 1 : kCh];  // the [c][pos] form keeps its values between the two passes
   if constexpr (ROWS_ARE_POSITIONS) {
 #pragma unroll
     for (int ch = 0; ch < kChunks; ++ch) {
@@ -114,11 +116,12 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
       }
     }
   } else {
-#pragma unroll 8
+#pragma unroll
+    for (int cc = 0; cc < kCh; ++cc) xt[cc] = ld_f16(tile + tile_off(part * kCh + cc, pos));
+    pv = xt[0];
+#pragma unroll
     for (int cc = 0; cc < kCh; ++cc) {
-      const float x = ld_f16(tile + tile_off(part * kCh + cc, pos));
-      if (cc == 0) pv = x;
-      const float d = x - pv;
+      const float d = xt[cc] - pv;
       s1 += d;
       s2 = fmaf(d, d, s2);
     }
@@ -156,11 +159,8 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
       st_chunk(addr, o[0], o[1], o[2], o[3]);
     }
   } else {
-#pragma unroll 8
-    for (int cc = 0; cc < kCh; ++cc) {
-      const uint32_t addr = tile + tile_off(part * kCh + cc, pos);
-      st_f16_sat(addr, fmaf(ld_f16(addr), rstd, nmr));
-    }
+#pragma unroll
+    for (int cc = 0; cc < kCh; ++cc) st_f16_sat(tile + tile_off(part * kCh + cc, pos), fmaf(xt[cc], rstd, nmr));
   }
   named_bar_sync(1, kBwdThreads);  // the exchange buffer may be reused
   return rstd;

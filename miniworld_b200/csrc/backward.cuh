@@ -492,16 +492,19 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         if (inside) other = p.ln_part[static_cast<size_t>(row) * p.n + j0 + pos];
       }
       float s1 = 0.f, s2 = 0.f;
+      float th[kBwdCh];  // this thread's t_hat values, kept for the second pass
 #pragma unroll
       for (int ch = 0; ch < kBwdChunks; ++ch) {
         uint32_t v[8];
         tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) th[ch * 8 + e] = ld_f16(t_s + tile_off(part * kBwdCh + ch * 8 + e, pos));
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float d = __uint_as_float(v[e]);
           s1 += d;
-          s2 = fmaf(d, ld_f16(t_s + tile_off(part * kBwdCh + ch * 8 + e, pos)), s2);
+          s2 = fmaf(d, th[ch * 8 + e], s2);
         }
       }
       asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
@@ -526,7 +529,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         for (int e = 0; e < 8; ++e) {
           const uint32_t addr = t_s + tile_off(part * kBwdCh + ch * 8 + e, pos);
           if constexpr (MODE == 1) st_f16_sat(addr, __uint_as_float(v[e]));  // finished by bwd_ln_finish_kernel
-          else st_f16_sat(addr, rs * (__uint_as_float(v[e]) - m1 - ld_f16(addr) * m2));
+          else st_f16_sat(addr, rs * (__uint_as_float(v[e]) - m1 - th[ch * 8 + e] * m2));
         }
       }
       if constexpr (MODE != 1) {

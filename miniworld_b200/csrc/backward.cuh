@@ -292,9 +292,12 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
 #pragma unroll
     for (int kh = 0; kh < kZHalves; ++kh) tma_load_2d(wg_s + kh * kWHalf, &map_wg, w_full, kh * 64, 0);
   }
-  float acc_so[kZCh], acc_sg[kZCh];
+  // Column sums of dproj and dgate (the bias / beta terms of the weight gradients): gathered from the fp16 tiles while
+  // the gradient GEMMs run, this thread taking the 16-byte chunk `sum_chunk` (eight channels) of four position rows.
+  const int sum_chunk = threadIdx.x & 15, sum_rows = (threadIdx.x >> 4) * 4;
+  float acc_so[8], acc_sg[8];
 #pragma unroll
-  for (int c = 0; c < kZCh; ++c) acc_so[c] = 0.f, acc_sg[c] = 0.f;
+  for (int c = 0; c < 8; ++c) acc_so[c] = 0.f, acc_sg[c] = 0.f;
 
   // Buffer roles of tile `it`: t, z, dy, dgate = buffers (0, 1, 2, 3) for even it and (2, 3, 0, 1) for odd it. The
   // outputs of a tile are written over its t and z buffers and stored from there; its dy and dgate buffers are free
@@ -388,11 +391,15 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         const int b = row / p.n;
         sc = reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * C + part * kZCh);
       }
+      uint32_t vp[kZChunks][8], vg[kZChunks][8];
 #pragma unroll
       for (int ch = 0; ch < kZChunks; ++ch) {
-        uint32_t vp[8], vg[8];
-        tmem_ld8(tmem_base + lane_sel + part * kZCh + ch * 8, vp);
-        tmem_ld8(tmem_base + lane_sel + 128 + part * kZCh + ch * 8, vg);
+        tmem_ld8(tmem_base + lane_sel + part * kZCh + ch * 8, vp[ch]);
+        tmem_ld8(tmem_base + lane_sel + 128 + part * kZCh + ch * 8, vg[ch]);
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int ch = 0; ch < kZChunks; ++ch) {
         const uint32_t addr = tile_chunk(pos, part * kZChunks + ch);
         const uint4 dyv = ld_chunk(dy_s + addr);
         uint4 scv = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);  // bf16 ones
@@ -401,8 +408,14 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         if constexpr (MODE == 2) {
           if (pp != nullptr) ppv = __ldg(pp + ch);
         }
+        float co[8], cg[8];  // the eight channels' constants (the same addresses for the whole warp)
+        {
+          const float4* cp = reinterpret_cast<const float4*>(const_ptr + part * kZCh + ch * 8);
+          const float4 a0 = cp[0], a1 = cp[1], b0 = cp[32], b1 = cp[33];
+          co[0] = a0.x, co[1] = a0.y, co[2] = a0.z, co[3] = a0.w, co[4] = a1.x, co[5] = a1.y, co[6] = a1.z, co[7] = a1.w;
+          cg[0] = b0.x, cg[1] = b0.y, cg[2] = b0.z, cg[3] = b0.w, cg[4] = b1.x, cg[5] = b1.y, cg[6] = b1.z, cg[7] = b1.w;
+        }
         const uint32_t pw[4] = {ppv.x, ppv.y, ppv.z, ppv.w};
-        tmem_ld_wait();
         const uint32_t dw[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
         const uint32_t sw[4] = {scv.x, scv.y, scv.z, scv.w};
         uint32_t op[4], og[4];
@@ -414,14 +427,11 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
           float dpv[2], dgv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int c = part * kZCh + ch * 8 + t * 2 + e;
-            const float proj = __uint_as_float(vp[t * 2 + e]) + const_ptr[c] + (e == 0 ? p2.x : p2.y);
-            const float gate = sigmoid_fast(__uint_as_float(vg[t * 2 + e]) + const_ptr[128 + c]);
+            const float proj = __uint_as_float(vp[ch][t * 2 + e]) + co[t * 2 + e] + (e == 0 ? p2.x : p2.y);
+            const float gate = sigmoid_fast(__uint_as_float(vg[ch][t * 2 + e]) + cg[t * 2 + e]);
             const float du = (e == 0 ? d2.x * s2.x : d2.y * s2.y) * gc;
             dpv[e] = du * gate;
-            dgv[e] = MODE == 1 ? proj : du * proj * gate * (1.0f - gate);  // MODE 1 hands its part of proj on
-            acc_so[ch * 8 + t * 2 + e] += dpv[e];
-            acc_sg[ch * 8 + t * 2 + e] += dgv[e];
+            dgv[e] = MODE == 1 ? proj : dpv[e] * fmaf(-proj, gate, proj);  // MODE 1 hands its part of proj on
           }
           op[t] = pack_f16x2_sat(make_float2(dpv[0], dpv[1]));
           og[t] = pack_f16x2_sat(make_float2(dgv[0], dgv[1]));
@@ -478,6 +488,28 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       }
       umma_commit(mma_bar);
     }
+    if (sum_chunk < C / 8) {  // column sums of the two fp16 tiles the GEMMs are reading
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const uint32_t addr = tile_chunk(sum_rows + r, sum_chunk);
+        const uint4 a = ld_chunk(dy_s + addr);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 x = f16x2_to_float2(aw[t]);
+          acc_so[2 * t] += x.x, acc_so[2 * t + 1] += x.y;
+        }
+        if constexpr (MODE != 1) {
+          const uint4 b = ld_chunk(dg_s + addr);
+          const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 x = f16x2_to_float2(bw[t]);
+            acc_sg[2 * t] += x.x, acc_sg[2 * t + 1] += x.y;
+          }
+        }
+      }
+    }
     if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
     if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
@@ -492,17 +524,18 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         if (inside) other = p.ln_part[static_cast<size_t>(row) * p.n + j0 + pos];
       }
       float s1 = 0.f, s2 = 0.f;
-      float th[kBwdCh];  // this thread's t_hat values, kept for the second pass
+      float th[kBwdCh];                 // this thread's t_hat values and its d t_hat, both kept for the second pass
+      uint32_t dtv[kBwdChunks][8];
+#pragma unroll
+      for (int ch = 0; ch < kBwdChunks; ++ch) tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, dtv[ch]);
+#pragma unroll
+      for (int cc = 0; cc < kBwdCh; ++cc) th[cc] = ld_f16(t_s + tile_off(part * kBwdCh + cc, pos));
+      tmem_ld_wait();
 #pragma unroll
       for (int ch = 0; ch < kBwdChunks; ++ch) {
-        uint32_t v[8];
-        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) th[ch * 8 + e] = ld_f16(t_s + tile_off(part * kBwdCh + ch * 8 + e, pos));
-        tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float d = __uint_as_float(v[e]);
+          const float d = __uint_as_float(dtv[ch][e]);
           s1 += d;
           s2 = fmaf(d, th[ch * 8 + e], s2);
         }
@@ -522,22 +555,21 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       const float rs = rstd_out * 0.0625f;  // d / d t of the stored t / 16
 #pragma unroll
       for (int ch = 0; ch < kBwdChunks; ++ch) {
-        uint32_t v[8];
-        tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
-        tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const uint32_t addr = t_s + tile_off(part * kBwdCh + ch * 8 + e, pos);
-          if constexpr (MODE == 1) st_f16_sat(addr, __uint_as_float(v[e]));  // finished by bwd_ln_finish_kernel
-          else st_f16_sat(addr, rs * (__uint_as_float(v[e]) - m1 - th[ch * 8 + e] * m2));
+          if constexpr (MODE == 1) st_f16_sat(addr, __uint_as_float(dtv[ch][e]));  // finished by bwd_ln_finish_kernel
+          else st_f16_sat(addr, rs * (__uint_as_float(dtv[ch][e]) - m1 - th[ch * 8 + e] * m2));
         }
       }
       if constexpr (MODE != 1) {
+        uint32_t xg[kZChunks][8];
+#pragma unroll
+        for (int ch = 0; ch < kZChunks; ++ch) tmem_ld8(tmem_base + lane_sel + 128 + part * kZCh + ch * 8, xg[ch]);
+        tmem_ld_wait();
 #pragma unroll
         for (int ch = 0; ch < kZChunks; ++ch) {
-          uint32_t x[8];
-          tmem_ld8(tmem_base + lane_sel + 128 + part * kZCh + ch * 8, x);
-          tmem_ld_wait();
+          const uint32_t(&x)[8] = xg[ch];
           st_chunk(z_s + tile_chunk(pos, part * kZChunks + ch),
                    pack_f16x2_sat(make_float2(__uint_as_float(x[0]), __uint_as_float(x[1]))),
                    pack_f16x2_sat(make_float2(__uint_as_float(x[2]), __uint_as_float(x[3]))),
@@ -589,9 +621,20 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       }
     }
   }
-  {
-    float* ps = p.part_s + static_cast<size_t>(blockIdx.x) * 2 * 128;
-    flush_colsums(acc_so, acc_sg, smem, pos, part, ps, ps + 128);  // every tile region is free by now
+  {  // the 32 row groups of a channel, fixed order; every tile region is free by now
+    float* sc = reinterpret_cast<float*>(smem);  // [32 row groups][2][128]
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      sc[((threadIdx.x >> 4) * 2 + 0) * 128 + sum_chunk * 8 + c] = acc_so[c];
+      sc[((threadIdx.x >> 4) * 2 + 1) * 128 + sum_chunk * 8 + c] = acc_sg[c];
+    }
+    __syncthreads();
+    if (threadIdx.x < 256 && (threadIdx.x & 127) < C) {
+      float sum = 0.f;
+      for (int g = 0; g < 32; ++g) sum += sc[g * 256 + threadIdx.x];
+      p.part_s[static_cast<size_t>(blockIdx.x) * 2 * 128 + threadIdx.x] = sum;
+    }
+    __syncthreads();
   }
   tc_fence_before();
   __syncthreads();

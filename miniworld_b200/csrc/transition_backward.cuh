@@ -87,7 +87,11 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       tma_load_2d(ws_s + kh * 16384, &map_ws, w_full, p.block * 128 + kh * 64, 0);  // Ws columns of block j, [128 c][128 hid]
     }
   }
-  float sa_acc = 0.f, sb_acc = 0.f;  // this thread's hidden unit (threadIdx & 127), position quarter (threadIdx >> 7)
+  // column sums of da and db: this thread's 16-byte chunk (eight hidden units) of four position rows of the scratch tile
+  const int sum_chunk = threadIdx.x & 15, sum_rows = (threadIdx.x >> 4) * 4;
+  float sa_acc[8], sb_acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) sa_acc[c] = 0.f, sb_acc[c] = 0.f;
 
   bool ok = true;
   int it = 0;
@@ -98,16 +102,18 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     mma_phase ^= 1u;
     return got;
   };
-  // column sum of the scratch tile for this thread's hidden unit over its quarter of the positions
-  auto column_sum = [&]() {
-    const int hid = threadIdx.x & 127, pq = threadIdx.x >> 7;
-    float s = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < 32; ++i) {
-      const int r = pq * 32 + i;
-      s += ld_f16(s_s + tile_off(r, hid));
+  // adds this thread's share of the scratch tile's column sums
+  auto column_sum = [&](float (&acc)[8]) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint4 a = ld_chunk(s_s + tile_chunk(sum_rows + r, sum_chunk));
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 x = f16x2_to_float2(aw[t]);
+        acc[2 * t] += x.x, acc[2 * t + 1] += x.y;
+      }
     }
-    return s;
   };
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
     const int p0 = tile * 128;
@@ -184,8 +190,13 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       uint32_t v[8];
       tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
       tmem_ld_wait();
+      {
+        const float4* cp = reinterpret_cast<const float4*>(const_ptr + part * kBwdCh + ch * 8);
+        const float4 c0 = cp[0], c1 = cp[1];
+        const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-      for (int e = 0; e < 8; ++e) av[ch * 8 + e] = __uint_as_float(v[e]) + const_ptr[part * kBwdCh + ch * 8 + e];
+        for (int e = 0; e < 8; ++e) av[ch * 8 + e] = __uint_as_float(v[e]) + cc[e];
+      }
     }
     tc_fence_before();
     __syncthreads();
@@ -210,13 +221,16 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       tmem_ld8(tmem_base + lane_sel + part * kBwdCh + ch * 8, v);
       tmem_ld_wait();
       uint32_t da_p[4];
+      const float4* cbp = reinterpret_cast<const float4*>(const_ptr + 128 + part * kBwdCh + ch * 8);
+      const float4 cb0 = cbp[0], cb1 = cbp[1];
+      const float cbv[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         float dav[2], dbv[2], hv[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int i = ch * 8 + t * 2 + e;
-          const float b = __uint_as_float(v[t * 2 + e]) + const_ptr[128 + part * kBwdCh + i];
+          const float b = __uint_as_float(v[t * 2 + e]) + cbv[t * 2 + e];
           const float a = av[i];
           const float sg = sigmoid_fast(a);
           const float silu = a * sg;
@@ -250,7 +264,7 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                   idesc_m, (ks != 0 ? 1u : 0u) | accum);
       umma_commit(mma_bar);
     }
-    sa_acc += column_sum();  // reads the tile the MMAs read
+    column_sum(sa_acc);  // reads the tile the MMAs read
     if (!mma_wait()) { ok = false; break; }
     // ---- db -> scratch; d x_hat += db Wb_j', Mb += db^T x_hat (columns 256-383)
 #pragma unroll
@@ -273,7 +287,7 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                   idesc_m, (ks != 0 ? 1u : 0u) | accum);
       umma_commit(mma_bar);
     }
-    sb_acc += column_sum();
+    column_sum(sb_acc);
     if (!mma_wait()) { ok = false; break; }
     // ---- h -> scratch; dWs_j += dy^T h (columns 384-511; lanes = channels c, columns = hidden units)
 #pragma unroll
@@ -404,10 +418,23 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
     }
   }
-  {
+  {  // the 32 row groups of a hidden unit, fixed order (every tile region is free by now); the sums go to quarter 0
+    float* sc = reinterpret_cast<float*>(smem);  // [32 row groups][2][128]
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      sc[((threadIdx.x >> 4) * 2 + 0) * 128 + sum_chunk * 8 + c] = sa_acc[c];
+      sc[((threadIdx.x >> 4) * 2 + 1) * 128 + sum_chunk * 8 + c] = sb_acc[c];
+    }
+    __syncthreads();
     float* ps = p.part_s + static_cast<size_t>(blockIdx.x) * 2 * 512;
-    ps[threadIdx.x] = sa_acc;        // [quarter][hidden unit]
-    ps[512 + threadIdx.x] = sb_acc;
+    float sum = 0.f;
+    if (threadIdx.x < 256)
+      for (int g = 0; g < 32; ++g) sum += sc[g * 256 + threadIdx.x];
+    __syncthreads();
+    // [vector][quarter][hidden unit]: threads 0-255 hold (vector, unit); quarters 1-3 are zero
+    if (threadIdx.x < 256) ps[(threadIdx.x >> 7) * 512 + (threadIdx.x & 127)] = sum;
+    else ps[((threadIdx.x - 256) >> 7) * 512 + 128 + (threadIdx.x & 127)] = 0.f;
+    ps[(threadIdx.x >> 8) * 512 + 256 + (threadIdx.x & 255)] = 0.f;
   }
   tc_fence_before();
   __syncthreads();

@@ -129,8 +129,7 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
     loads_pending = false;
-    // ---- x_hat in place; dy * c as fp16 in place
-    const float rstd_in = normalise_tile<true, true, 128>(x_s, xchg, pos, part, p.eps);
+    // ---- dy * c as fp16 in place (x_hat follows while the first GEMM runs)
 #pragma unroll
     for (int ch = 0; ch < kBwdChunks; ++ch) {
       const uint32_t addr = y_s + tile_chunk(pos, part * kBwdChunks + ch);
@@ -157,6 +156,9 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                   umma_desc_mnmajor(ws_s + ks * 2048, 16384), idesc, ks != 0 ? 1u : 0u);
       umma_commit(mma_bar);
     }
+    // ---- x_hat in place, in the shadow of the dh GEMM (which reads dy and Ws only)
+    const float rstd_in = normalise_tile<true, true, 128>(x_s, xchg, pos, part, p.eps);
+    fence_proxy_async_smem();
     if (!mma_wait()) { ok = false; break; }
     tc_fence_after();
     float dh[kBwdCh];

@@ -1086,17 +1086,23 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 // ------------------------------------------------------------------------------------------------ small kernels
 // Largest |dy| (bf16) as the bits of a non-negative float: `amax_bits` must be zero before the launch.
 __global__ void __launch_bounds__(256) bwd_amax_kernel(const uint4* dy, size_t n_chunks, unsigned int* amax_bits) {
-  float m = 0.f;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n_chunks;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const uint4 v = __ldg(dy + i);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  // |x| of a bf16 pair compares like the unsigned integer of its bits with the sign cleared, so the maximum is taken on
+  // the packed halves; four loads per thread in flight
+  uint32_t mx = 0u;
+  auto fold = [&](const uint4& v) {
+    const uint32_t w[4] = {v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu, v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu};
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const float2 x = bf16x2_to_float2(w[t]);
-      m = fmaxf(m, fmaxf(fabsf(x.x), fabsf(x.y)));
-    }
+    for (int t = 0; t < 4; ++t) mx = __vmaxu2(mx, w[t]);
+  };
+  const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  for (; i + 3 * step < n_chunks; i += 4 * step) {
+    const uint4 v0 = __ldg(dy + i), v1 = __ldg(dy + i + step), v2 = __ldg(dy + i + 2 * step), v3 = __ldg(dy + i + 3 * step);
+    fold(v0), fold(v1), fold(v2), fold(v3);
   }
+  for (; i < n_chunks; i += step) fold(__ldg(dy + i));
+  const uint32_t top = (mx >> 16) > (mx & 0xFFFFu) ? (mx >> 16) : (mx & 0xFFFFu);
+  float m = __uint_as_float(top << 16);  // NaN or infinity bits stay above 3e38 and are rejected below
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
   if ((threadIdx.x & 31) == 0 && m > 0.f && m <= 3.0e38f) atomicMax(amax_bits, __float_as_uint(m));
@@ -1162,23 +1168,28 @@ __global__ void __launch_bounds__(128) bwd_pack_kernel(const PackArgs a, uint8_t
     reinterpret_cast<float*>(packed + kBwdPackedD)[m * 128 + row] = d + (a.bias[m] != nullptr ? a.bias[m][row] : 0.f);
 }
 
-// M[e] and S[e] = sums over the CTAs' partials, in CTA order (deterministic). Blocks 0 .. 127 take M (2 x 128 x 128
-// values), block 128 takes S (2 x 128 values).
+// M[e] and S[e] = sums over the CTAs' partials in a fixed order (deterministic). Blocks 0 .. 511 take M (2 x 128 x 128
+// values), blocks 512 .. 515 take S (2 x 128 values).
 __global__ void __launch_bounds__(256) bwd_reduce_kernel(const float* part_m, const float* part_s, int n_parts, float* m_out,
                                                          float* s_out) {
-  const bool is_s = blockIdx.x == 128;
+  // grid = 512 blocks for M (64 elements each) + 4 for S; a block's four groups of 64 threads take every fourth partial
+  // (two loads in flight each) and are combined in a fixed order
+  __shared__ float comb[4][64];
+  const bool is_s = blockIdx.x >= 512;
   const float* parts = is_s ? part_s : part_m;
   const size_t stride = is_s ? 2 * 128 : 2 * 128 * 128;
-  const int e = is_s ? threadIdx.x : blockIdx.x * 256 + threadIdx.x;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int i = 0;
-  for (; i + 4 <= n_parts; i += 4) {  // four independent loads in flight; the additions keep their order
-    const float a = parts[static_cast<size_t>(i) * stride + e], b = parts[static_cast<size_t>(i + 1) * stride + e];
-    const float c = parts[static_cast<size_t>(i + 2) * stride + e], d = parts[static_cast<size_t>(i + 3) * stride + e];
-    s0 += a, s1 += b, s2 += c, s3 += d;
+  const int el = threadIdx.x & 63, g = threadIdx.x >> 6;
+  const int e = (is_s ? blockIdx.x - 512 : blockIdx.x) * 64 + el;
+  float s0 = 0.f, s1 = 0.f;
+  int i = g;
+  for (; i + 4 < n_parts; i += 8) {
+    const float a = parts[static_cast<size_t>(i) * stride + e], b = parts[static_cast<size_t>(i + 4) * stride + e];
+    s0 += a, s1 += b;
   }
-  for (; i < n_parts; ++i) s0 += parts[static_cast<size_t>(i) * stride + e];
-  (is_s ? s_out : m_out)[e] = (s0 + s1) + (s2 + s3);
+  if (i < n_parts) s0 += parts[static_cast<size_t>(i) * stride + e];
+  comb[g][el] = s0 + s1;
+  __syncthreads();
+  if (g == 0) (is_s ? s_out : m_out)[e] = (comb[0][el] + comb[1][el]) + (comb[2][el] + comb[3][el]);
 }
 
 // Parameter gradients from the reduced sums M[m] = dOut_m^T x_hat (times c) and S[m] = column sums of dOut_m (times c):

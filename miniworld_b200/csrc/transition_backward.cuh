@@ -500,16 +500,22 @@ __global__ void __launch_bounds__(128) tr_bwd_pack_kernel(const TrBwdPackArgs a,
 
 // out[e] = sum over the CTAs' partials (fixed order)
 __global__ void __launch_bounds__(256) tr_bwd_reduce_kernel(const float* parts, int n_parts, size_t stride, float* out, int count) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= count) return;
+  // a block covers 64 elements; its four groups of 64 threads take every fourth partial and are combined in a fixed order
+  __shared__ float comb[4][64];
+  const int el = threadIdx.x & 63, g = threadIdx.x >> 6;
+  const int e = blockIdx.x * 64 + el;
   float s0 = 0.f, s1 = 0.f;
-  int i = 0;
-  for (; i + 2 <= n_parts; i += 2) {
-    s0 += parts[static_cast<size_t>(i) * stride + e];
-    s1 += parts[static_cast<size_t>(i + 1) * stride + e];
+  if (e < count) {
+    int i = g;
+    for (; i + 4 < n_parts; i += 8) {
+      const float a = parts[static_cast<size_t>(i) * stride + e], b = parts[static_cast<size_t>(i + 4) * stride + e];
+      s0 += a, s1 += b;
+    }
+    if (i < n_parts) s0 += parts[static_cast<size_t>(i) * stride + e];
   }
-  if (i < n_parts) s0 += parts[static_cast<size_t>(i) * stride + e];
-  out[e] = s0 + s1;
+  comb[g][el] = s0 + s1;
+  __syncthreads();
+  if (g == 0 && e < count) out[e] = (comb[0][el] + comb[1][el]) + (comb[2][el] + comb[3][el]);
 }
 
 // Parameter gradients of the Transition from the reduced sums of all four blocks:

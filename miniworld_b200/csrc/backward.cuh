@@ -1168,26 +1168,32 @@ __global__ void __launch_bounds__(128) bwd_pack_kernel(const PackArgs a, uint8_t
     reinterpret_cast<float*>(packed + kBwdPackedD)[m * 128 + row] = d + (a.bias[m] != nullptr ? a.bias[m][row] : 0.f);
 }
 
+// Sum of element e over the partials g, g + 4, g + 8, ... (four loads in flight, fixed order of additions).
+__device__ __forceinline__ float sum_every_fourth(const float* parts, size_t stride, int n_parts, int e, int g) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int i = g;
+  for (; i + 12 < n_parts; i += 16) {
+    const float a = parts[static_cast<size_t>(i) * stride + e], b = parts[static_cast<size_t>(i + 4) * stride + e];
+    const float c = parts[static_cast<size_t>(i + 8) * stride + e], d = parts[static_cast<size_t>(i + 12) * stride + e];
+    s0 += a, s1 += b, s2 += c, s3 += d;
+  }
+  for (; i < n_parts; i += 4) s0 += parts[static_cast<size_t>(i) * stride + e];
+  return (s0 + s1) + (s2 + s3);
+}
+
 // M[e] and S[e] = sums over the CTAs' partials in a fixed order (deterministic). Blocks 0 .. 511 take M (2 x 128 x 128
 // values), blocks 512 .. 515 take S (2 x 128 values).
 __global__ void __launch_bounds__(256) bwd_reduce_kernel(const float* part_m, const float* part_s, int n_parts, float* m_out,
                                                          float* s_out) {
   // grid = 512 blocks for M (64 elements each) + 4 for S; a block's four groups of 64 threads take every fourth partial
-  // (two loads in flight each) and are combined in a fixed order
+  // and are combined in a fixed order
   __shared__ float comb[4][64];
   const bool is_s = blockIdx.x >= 512;
   const float* parts = is_s ? part_s : part_m;
   const size_t stride = is_s ? 2 * 128 : 2 * 128 * 128;
   const int el = threadIdx.x & 63, g = threadIdx.x >> 6;
   const int e = (is_s ? blockIdx.x - 512 : blockIdx.x) * 64 + el;
-  float s0 = 0.f, s1 = 0.f;
-  int i = g;
-  for (; i + 4 < n_parts; i += 8) {
-    const float a = parts[static_cast<size_t>(i) * stride + e], b = parts[static_cast<size_t>(i + 4) * stride + e];
-    s0 += a, s1 += b;
-  }
-  if (i < n_parts) s0 += parts[static_cast<size_t>(i) * stride + e];
-  comb[g][el] = s0 + s1;
+  comb[g][el] = sum_every_fourth(parts, stride, n_parts, e, g);
   __syncthreads();
   if (g == 0) (is_s ? s_out : m_out)[e] = (comb[0][el] + comb[1][el]) + (comb[2][el] + comb[3][el]);
 }

@@ -498,24 +498,20 @@ __global__ void __launch_bounds__(128) tr_bwd_pack_kernel(const TrBwdPackArgs a,
   }
 }
 
-// out[e] = sum over the CTAs' partials (fixed order)
-__global__ void __launch_bounds__(256) tr_bwd_reduce_kernel(const float* parts, int n_parts, size_t stride, float* out, int count) {
-  // a block covers 64 elements; its four groups of 64 threads take every fourth partial and are combined in a fixed order
+// m_out[e] (3 x 128 x 128 values: blocks 0 .. 767) and s_out[e] (2 x 512 values: blocks 768 .. 783) = sums over the CTAs'
+// partials; a block covers 64 elements, its four groups of 64 threads take every fourth partial and are combined in a
+// fixed order.
+__global__ void __launch_bounds__(256) tr_bwd_reduce_kernel(const float* part_m, const float* part_s, int n_parts, float* m_out,
+                                                            float* s_out) {
   __shared__ float comb[4][64];
+  const bool is_s = blockIdx.x >= 768;
+  const float* parts = is_s ? part_s : part_m;
+  const size_t stride = is_s ? 2 * 512 : 3 * 128 * 128;
   const int el = threadIdx.x & 63, g = threadIdx.x >> 6;
-  const int e = blockIdx.x * 64 + el;
-  float s0 = 0.f, s1 = 0.f;
-  if (e < count) {
-    int i = g;
-    for (; i + 4 < n_parts; i += 8) {
-      const float a = parts[static_cast<size_t>(i) * stride + e], b = parts[static_cast<size_t>(i + 4) * stride + e];
-      s0 += a, s1 += b;
-    }
-    if (i < n_parts) s0 += parts[static_cast<size_t>(i) * stride + e];
-  }
-  comb[g][el] = s0 + s1;
+  const int e = (is_s ? blockIdx.x - 768 : blockIdx.x) * 64 + el;
+  comb[g][el] = sum_every_fourth(parts, stride, n_parts, e, g);
   __syncthreads();
-  if (g == 0 && e < count) out[e] = (comb[0][el] + comb[1][el]) + (comb[2][el] + comb[3][el]);
+  if (g == 0) (is_s ? s_out : m_out)[e] = (comb[0][el] + comb[1][el]) + (comb[2][el] + comb[3][el]);
 }
 
 // Parameter gradients of the Transition from the reduced sums of all four blocks:

@@ -646,7 +646,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
 }
 
 // Mean and rstd of the stored t over the 256 channels of two tensors [rows][128][N] (fp16), one thread per row and
-// group of eight columns: stats[row][j] = {mean, rsqrt(var + eps)} (eps already scaled like the stored t).
+// group of eight columns: stats[row][j] = {mean, rsqrt(var + eps)} (eps already scaled like the stored t). Eight
+// channels' loads are in flight per thread.
 __global__ void __launch_bounds__(256) bwd_ln_stats_kernel(const uint4* t0, const uint4* t1, int n, long long groups, float eps,
                                                            float2* stats) {
   const long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -657,52 +658,86 @@ __global__ void __launch_bounds__(256) bwd_ln_stats_kernel(const uint4* t0, cons
   float pv[8], s1[8], s2[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) pv[e] = 0.f, s1[e] = 0.f, s2[e] = 0.f;
-  for (int c = 0; c < 256; ++c) {
-    const uint4* src = (c < 128 ? t0 : t1) + (row * 128 + (c & 127)) * per_row + jc;
-    const uint4 v = __ldg(src);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  for (int c0 = 0; c0 < 256; c0 += 8) {
+    const uint4* src = (c0 < 128 ? t0 : t1) + (row * 128 + (c0 & 127)) * per_row + jc;
+    uint4 v[8];
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const float2 x = f16x2_to_float2(w[t]);
-      if (c == 0) pv[2 * t] = x.x, pv[2 * t + 1] = x.y;
-      const float d0 = x.x - pv[2 * t], d1 = x.y - pv[2 * t + 1];
-      s1[2 * t] += d0, s1[2 * t + 1] += d1;
-      s2[2 * t] = fmaf(d0, d0, s2[2 * t]), s2[2 * t + 1] = fmaf(d1, d1, s2[2 * t + 1]);
+    for (int k = 0; k < 8; ++k) v[k] = __ldg(src + static_cast<long long>(k) * per_row);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 x = f16x2_to_float2(w[t]);
+        if (c0 == 0 && k == 0) pv[2 * t] = x.x, pv[2 * t + 1] = x.y;
+        const float d0 = x.x - pv[2 * t], d1 = x.y - pv[2 * t + 1];
+        s1[2 * t] += d0, s1[2 * t + 1] += d1;
+        s2[2 * t] = fmaf(d0, d0, s2[2 * t]), s2[2 * t + 1] = fmaf(d1, d1, s2[2 * t + 1]);
+      }
     }
   }
+  float4* dst = reinterpret_cast<float4*>(stats + row * n + jc * 8);  // 64-byte aligned: n is a multiple of 8
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const float mean = pv[e] + s1[e] * (1.0f / 256.0f);
-    const float var = fmaxf(s2[e] - s1[e] * s1[e] * (1.0f / 256.0f), 0.f) * (1.0f / 256.0f);
-    stats[row * n + jc * 8 + e] = make_float2(mean, rsqrtf(var + eps));
+  for (int e = 0; e < 8; e += 2) {
+    float m[2], r[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      m[u] = pv[e + u] + s1[e + u] * (1.0f / 256.0f);
+      const float var = fmaxf(s2[e + u] - s1[e + u] * s1[e + u] * (1.0f / 256.0f), 0.f) * (1.0f / 256.0f);
+      r[u] = rsqrtf(var + eps);
+    }
+    dst[e >> 1] = make_float4(m[0], r[0], m[1], r[1]);
   }
 }
 
 // Finishes the first tensor's gradient of the 256-channel LayerNorm backward, in place over the raw d t_hat the MODE 1
 // launch left in dt [rows][128][N] (fp16, times c): dt = rstd / 16 * (d t_hat - m1 - t_hat m2), t_hat recomputed from t.
+// One thread per row, group of eight columns and group of 16 channels: the eight positions' statistics are read once.
+constexpr int kLnFinishChannels = 16;
 __global__ void __launch_bounds__(256) bwd_ln_finish_kernel(uint4* dt, const uint4* t, const float2* stats, const float2* means,
-                                                            int n, long long chunks) {
+                                                            int n, long long threads) {
   const long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (g >= chunks) return;
+  if (g >= threads) return;
   const int per_row = n / 8;
-  const long long rc = g / per_row;  // row * 128 + channel
-  const int jc = static_cast<int>(g - rc * per_row);
-  const long long row = rc >> 7;
-  const uint4 dv = dt[g];
-  const uint4 tv = __ldg(t + g);
-  const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w}, tw[4] = {tv.x, tv.y, tv.z, tv.w};
-  uint32_t o[4];
+  const long long rg = g / per_row;  // row * (128 / kLnFinishChannels) + channel group
+  const int jc = static_cast<int>(g - rg * per_row);
+  const long long row = rg / (128 / kLnFinishChannels);
+  const int c_first = static_cast<int>(rg - row * (128 / kLnFinishChannels)) * kLnFinishChannels;
+  float mean[8], k0[8], k1[8], m1[8];
+  {
+    const float4* sp = reinterpret_cast<const float4*>(stats + row * n + jc * 8);
+    const float4* mp = reinterpret_cast<const float4*>(means + row * n + jc * 8);
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const float2 d = f16x2_to_float2(dw[q]);
-    const float2 x = f16x2_to_float2(tw[q]);
-    const float2 st0 = stats[row * n + jc * 8 + 2 * q], st1 = stats[row * n + jc * 8 + 2 * q + 1];
-    const float2 mm0 = means[row * n + jc * 8 + 2 * q], mm1 = means[row * n + jc * 8 + 2 * q + 1];
-    const float r0 = st0.y * 0.0625f * (d.x - mm0.x - (x.x - st0.x) * st0.y * mm0.y);
-    const float r1 = st1.y * 0.0625f * (d.y - mm1.x - (x.y - st1.x) * st1.y * mm1.y);
-    o[q] = pack_f16x2_sat(make_float2(r0, r1));
+    for (int q = 0; q < 4; ++q) {
+      const float4 st = __ldg(sp + q), mm = __ldg(mp + q);
+      mean[2 * q] = st.x, k0[2 * q] = st.y * 0.0625f, k1[2 * q] = st.y * mm.y, m1[2 * q] = mm.x;
+      mean[2 * q + 1] = st.z, k0[2 * q + 1] = st.w * 0.0625f, k1[2 * q + 1] = st.w * mm.w, m1[2 * q + 1] = mm.z;
+    }
   }
-  dt[g] = make_uint4(o[0], o[1], o[2], o[3]);
+  const long long base = (row * 128 + c_first) * per_row + jc;
+#pragma unroll
+  for (int c0 = 0; c0 < kLnFinishChannels; c0 += 4) {
+    uint4 dv[4], tv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      dv[k] = dt[base + static_cast<long long>(c0 + k) * per_row];
+      tv[k] = __ldg(t + base + static_cast<long long>(c0 + k) * per_row);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t dw[4] = {dv[k].x, dv[k].y, dv[k].z, dv[k].w}, tw[4] = {tv[k].x, tv[k].y, tv[k].z, tv[k].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 d = f16x2_to_float2(dw[q]);
+        const float2 x = f16x2_to_float2(tw[q]);
+        const float r0 = k0[2 * q] * (d.x - m1[2 * q] - (x.x - mean[2 * q]) * k1[2 * q]);
+        const float r1 = k0[2 * q + 1] * (d.y - m1[2 * q + 1] - (x.y - mean[2 * q + 1]) * k1[2 * q + 1]);
+        o[q] = pack_f16x2_sat(make_float2(r0, r1));
+      }
+      dt[base + static_cast<long long>(c0 + k) * per_row] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
 }
 
 struct BwdPrologueParams {

@@ -375,22 +375,31 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       }
       umma_commit(mma_bar);
     }
+    // per-thread global operands of phase 3 (MODE 2: the first launch's part of the projection; the dropout scale),
+    // requested before the waits
+    const int j = j0 + pos;
+    uint4 ppv[kZChunks], scv[kZChunks];
+#pragma unroll
+    for (int ch = 0; ch < kZChunks; ++ch) {
+      ppv[ch] = make_uint4(0u, 0u, 0u, 0u);
+      scv[ch] = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);  // bf16 ones
+    }
+    if constexpr (MODE == 2) {
+      if (j < p.n)
+        ldg_chunks(reinterpret_cast<const uint4*>(p.p_part + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh), true,
+                   ppv);  // the workspace is 1024-byte aligned
+    }
+    if (p.drop_scale != nullptr && j < p.n) {
+      const int b = row / p.n;
+      ldg_chunks(reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * C + part * kZCh),
+                 (reinterpret_cast<uintptr_t>(p.drop_scale) & 31u) == 0, scv);
+    }
     if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     if (!cta_wait(dy_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
     if (threadIdx.x == 0) dy_pending = -1;
     tc_fence_after();
     // ---- phase 3: dproj = c du gate, dgate = c du proj gate (1 - gate); du = dy (* dropout scale)
     {
-      const int j = j0 + pos;
-      const uint4* sc = nullptr;
-      const uint4* pp = nullptr;
-      if constexpr (MODE == 2) {
-        if (j < p.n) pp = reinterpret_cast<const uint4*>(p.p_part + (static_cast<size_t>(row) * p.n + j) * C + part * kZCh);
-      }
-      if (p.drop_scale != nullptr && j < p.n) {
-        const int b = row / p.n;
-        sc = reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * C + part * kZCh);
-      }
       uint32_t vp[kZChunks][8], vg[kZChunks][8];
 #pragma unroll
       for (int ch = 0; ch < kZChunks; ++ch) {
@@ -402,12 +411,6 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       for (int ch = 0; ch < kZChunks; ++ch) {
         const uint32_t addr = tile_chunk(pos, part * kZChunks + ch);
         const uint4 dyv = ld_chunk(dy_s + addr);
-        uint4 scv = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);  // bf16 ones
-        if (sc != nullptr) scv = __ldg(sc + ch);
-        uint4 ppv = make_uint4(0u, 0u, 0u, 0u);
-        if constexpr (MODE == 2) {
-          if (pp != nullptr) ppv = __ldg(pp + ch);
-        }
         float co[8], cg[8];  // the eight channels' constants (the same addresses for the whole warp)
         {
           const float4* cp = reinterpret_cast<const float4*>(const_ptr + part * kZCh + ch * 8);
@@ -415,9 +418,9 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
           co[0] = a0.x, co[1] = a0.y, co[2] = a0.z, co[3] = a0.w, co[4] = a1.x, co[5] = a1.y, co[6] = a1.z, co[7] = a1.w;
           cg[0] = b0.x, cg[1] = b0.y, cg[2] = b0.z, cg[3] = b0.w, cg[4] = b1.x, cg[5] = b1.y, cg[6] = b1.z, cg[7] = b1.w;
         }
-        const uint32_t pw[4] = {ppv.x, ppv.y, ppv.z, ppv.w};
+        const uint32_t pw[4] = {ppv[ch].x, ppv[ch].y, ppv[ch].z, ppv[ch].w};
         const uint32_t dw[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
-        const uint32_t sw[4] = {scv.x, scv.y, scv.z, scv.w};
+        const uint32_t sw[4] = {scv[ch].x, scv[ch].y, scv[ch].z, scv[ch].w};
         uint32_t op[4], og[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {

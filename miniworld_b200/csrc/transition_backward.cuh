@@ -115,20 +115,24 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
     }
   };
+  auto issue_inputs = [&](int p0_i) {  // thread 0
+    mbar_arrive_expect_tx(in_full, 2 * kBwdTile);
+#pragma unroll
+    for (int kh = 0; kh < 2; ++kh) {
+      tma_load_2d(y_s + kh * 16384, &map_dy, in_full, kh * 64, p0_i);
+      tma_load_2d(x_s + kh * 16384, &map_x, in_full, kh * 64, p0_i);
+    }
+    loads_pending = true;
+  };
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
     const int p0 = tile * 128;
     if (threadIdx.x == 0) {
-      mbar_arrive_expect_tx(in_full, 2 * kBwdTile);
-#pragma unroll
-      for (int kh = 0; kh < 2; ++kh) {
-        tma_load_2d(x_s + kh * 16384, &map_x, in_full, kh * 64, p0);
-        tma_load_2d(y_s + kh * 16384, &map_dy, in_full, kh * 64, p0);
-      }
-      loads_pending = true;
+      if (!loads_pending) issue_inputs(p0);  // (not LAST: requested while the previous tile finished)
+      bulk_wait_read<0>();                   // the previous tile's store has read the scratch tile
     }
     if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
-    loads_pending = false;
+    loads_pending = false;  // (only thread 0's copy is read)
     // ---- dy * c as fp16 in place (x_hat follows while the first GEMM runs)
 #pragma unroll
     for (int ch = 0; ch < kBwdChunks; ++ch) {
@@ -321,6 +325,10 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
     if (!mma_wait()) { ok = false; break; }
     tc_fence_after();
+    if constexpr (!LAST) {
+      // x_hat and dy * c have been read for the last time: the next tile's inputs land while this one finishes
+      if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) issue_inputs((tile + gridDim.x) * 128);
+    }
     // ---- the running d x_hat: add the earlier launches' sum; LAST: LayerNorm backward + residual -> dx (bf16)
     {
       float tot[kBwdCh];
@@ -388,7 +396,6 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #pragma unroll
       for (int kh = 0; kh < 2; ++kh) tma_store_2d(&map_out, s_s + kh * 16384, kh * 64, p0);
       bulk_commit();
-      bulk_wait_read<0>();
     }
   }
   if (threadIdx.x == 0) {

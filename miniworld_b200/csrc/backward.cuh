@@ -825,7 +825,29 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   // owns channel `pos` (its lane) and the position quarter `part`, so its constants and its column sums are scalars
   // and dO, stored [channel][position], is read in 16-byte runs of positions.
   float acc_sv = 0.f, acc_sg = 0.f;
-  uint32_t* valid_words = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + kBwdXchg + 1024 + 64);  // one per 32 positions
+  // validity of a tile's positions, one bit each: [2][4] words (tile parity, 32 positions per word). The mask bytes of
+  // the NEXT tile are requested by the first four warps before a GEMM wait and turned into the words after it, so that
+  // their latency is off the path.
+  uint32_t* valid_words = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + kBwdXchg + 1024 + 64);
+  auto mask_bytes = [&](int tile_i, bool& in_range, uint32_t& m_i, uint32_t& m_j, uint32_t& m_p) {
+    const int row_i = tile_i / p.tiles_per_row;
+    const int j_i = (tile_i - row_i * p.tiles_per_row) * 128 + pos;
+    const int b = row_i / p.n;
+    const int i = row_i - b * p.n;
+    in_range = j_i < p.n;
+    m_i = 1u, m_j = 1u, m_p = 1u;
+    if (in_range) {
+      if (p.token_mask != nullptr) {
+        m_i = p.token_mask[static_cast<size_t>(b) * p.n + i];
+        m_j = p.token_mask[static_cast<size_t>(b) * p.n + j_i];
+      }
+      if (p.pair_mask != nullptr) m_p = p.pair_mask[(static_cast<size_t>(b) * p.n + i) * p.n + j_i];
+    }
+  };
+  auto publish_valid = [&](int it_i, bool in_range, uint32_t m_i, uint32_t m_j, uint32_t m_p) {
+    const uint32_t word = __ballot_sync(0xFFFFFFFFu, in_range && m_i != 0u && m_j != 0u && m_p != 0u);
+    if (lane == 0) valid_words[(it_i & 1) * 4 + q] = word;
+  };
 
   // Buffer roles (z, dO, dvalue, dgate) of tile `it`, one nibble each, period 4: the next tile's z and dO are copied
   // into this tile's dO buffer (free after phase 3) and dgate buffer (free after the gradient GEMMs) while this tile
@@ -859,21 +881,17 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     issue_do(blockIdx.x, 0);
     in_pending = 0;
   }
+  if (part == 0 && static_cast<int>(blockIdx.x) < p.num_tiles) {
+    bool in0;
+    uint32_t a0, b0, c0;
+    mask_bytes(blockIdx.x, in0, a0, b0, c0);
+    publish_valid(0, in0, a0, b0, c0);
+  }
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
     const int row = tile / p.tiles_per_row;
     const int j0 = (tile - row * p.tiles_per_row) * 128;
     const uint32_t z_s = role(it, 0), do_s = role(it, 1), dv_s = role(it, 2), dg_s = role(it, 3);
     const int j = j0 + pos;
-    if (part == 0) {  // validity of the tile's positions, one bit each (read in phase 3, two CTA barriers later)
-      const int b = row / p.n;
-      const int i = row - b * p.n;
-      bool valid = j < p.n;
-      if (valid && p.token_mask != nullptr)
-        valid = p.token_mask[static_cast<size_t>(b) * p.n + i] != 0 && p.token_mask[static_cast<size_t>(b) * p.n + j] != 0;
-      if (valid && p.pair_mask != nullptr) valid = p.pair_mask[(static_cast<size_t>(b) * p.n + i) * p.n + j] != 0;
-      const uint32_t word = __ballot_sync(0xFFFFFFFFu, valid);
-      if (lane == 0) valid_words[q] = word;
-    }
     if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
     if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
     if (threadIdx.x == 0) in_pending = -1;
@@ -899,11 +917,16 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       }
       umma_commit(mma_bar);
     }
+    bool nx_in = false;
+    uint32_t nx_i = 1u, nx_j = 1u, nx_p = 1u;
+    const bool has_next = tile + static_cast<int>(gridDim.x) < p.num_tiles;
+    if (part == 0 && has_next) mask_bytes(tile + gridDim.x, nx_in, nx_i, nx_j, nx_p);
     if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
+    if (part == 0 && has_next) publish_valid(it + 1, nx_in, nx_i, nx_j, nx_p);
     // ---- phase 3: dvalue, dgate for this thread's channel and 32 positions, stored [channel][position]
     {
-      const uint32_t vbits = valid_words[part];
+      const uint32_t vbits = valid_words[(it & 1) * 4 + part];
       uint32_t vv[32], vg[32];
       tmem_ld32(tmem_base + lane_sel + part * 32, vv);
       tmem_ld32(tmem_base + lane_sel + 128 + part * 32, vg);

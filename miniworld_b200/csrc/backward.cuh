@@ -783,7 +783,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   const uint32_t xchg = smem_base + 6 * kBwdTile;
   const uint32_t const_s = xchg + kBwdXchg;
   const uint32_t bar_base = const_s + 1024;
-  const uint32_t w_full = bar_base, in_full = bar_base + 8, mma_bar = bar_base + 16;
+  const uint32_t w_full = bar_base, z_full = bar_base + 8, mma_bar = bar_base + 16, do_full = bar_base + 24;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + kBwdXchg + 1024 + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -794,7 +794,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
-    mbar_init(in_full, 2);  // a tile's z and dO copies are issued at different times, one arrival each
+    mbar_init(z_full, 1);   // a tile's z and dO copies are issued and awaited at different times
+    mbar_init(do_full, 1);
     mbar_init(mma_bar, 2);  // two issuing threads commit to it in every GEMM round
     *abort_flag = 0;
     fence_mbar_init();
@@ -861,25 +862,25 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     const int row_i = tile_i / p.tiles_per_row;
     const int j_i = (tile_i - row_i * p.tiles_per_row) * 128;
     const uint32_t z_i = role(it_i, 0);
-    mbar_arrive_expect_tx(in_full, kZHalves * 16384);
+    mbar_arrive_expect_tx(z_full, kZHalves * 16384);
 #pragma unroll
-    for (int kh = 0; kh < kZHalves; ++kh) tma_load_3d(z_i + kh * 16384, &map_z, in_full, kh * 64, j_i, row_i);
+    for (int kh = 0; kh < kZHalves; ++kh) tma_load_3d(z_i + kh * 16384, &map_z, z_full, kh * 64, j_i, row_i);
   };
   auto issue_do = [&](int tile_i, int it_i) {
     const int row_i = tile_i / p.tiles_per_row;
     const int j_i = (tile_i - row_i * p.tiles_per_row) * 128;
     const uint32_t do_i = role(it_i, 1);
-    mbar_arrive_expect_tx(in_full, kBwdTile);
+    mbar_arrive_expect_tx(do_full, kBwdTile);
 #pragma unroll
-    for (int kh = 0; kh < 2; ++kh) tma_load_3d(do_i + kh * 16384, &map_do, in_full, j_i + kh * 64, 0, row_i);
+    for (int kh = 0; kh < 2; ++kh) tma_load_3d(do_i + kh * 16384, &map_do, do_full, j_i + kh * 64, 0, row_i);
   };
   bool ok = true;
   int it = 0;
-  int in_pending = -1;  // thread 0: iteration whose copies are in flight, or -1
+  int z_pending = -1, do_pending = -1;  // thread 0: iteration whose copy is in flight, or -1
   if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < p.num_tiles) {
     issue_z(blockIdx.x, 0);
     issue_do(blockIdx.x, 0);
-    in_pending = 0;
+    z_pending = 0, do_pending = 0;
   }
   if (part == 0 && static_cast<int>(blockIdx.x) < p.num_tiles) {
     bool in0;
@@ -893,8 +894,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     const uint32_t z_s = role(it, 0), do_s = role(it, 1), dv_s = role(it, 2), dg_s = role(it, 3);
     const int j = j0 + pos;
     if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
-    if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
-    if (threadIdx.x == 0) in_pending = -1;
+    if (!cta_wait(z_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    if (threadIdx.x == 0) z_pending = -1;
     // ---- phase 1: x_hat in place
     const float rstd_in = normalise_tile<true, true, C>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
@@ -924,6 +925,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
     if (part == 0 && has_next) publish_valid(it + 1, nx_in, nx_i, nx_j, nx_p);
+    if (!cta_wait(do_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    if (threadIdx.x == 0) do_pending = -1;
     // ---- phase 3: dvalue, dgate for this thread's channel and 32 positions, stored [channel][position]
     {
       const uint32_t vbits = valid_words[(it & 1) * 4 + part];
@@ -971,7 +974,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     __syncthreads();
     if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
       issue_z(tile + gridDim.x, it + 1);  // into this tile's dO buffer, read for the last time in phase 3
-      in_pending = it + 1;
+      z_pending = it + 1;
     }
     // ---- phase 4: d x_hat = dvalue Wv' + dgate Wg' (columns 0-127, lanes = positions); Mv += dvalue^T x_hat (256-383),
     // Mg += dgate^T x_hat (384-511). dvalue / dgate are [channel][position] tiles: MN-major as the A operand of the
@@ -1023,8 +1026,10 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     }
     if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
-    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles)
+    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
       issue_do(tile + gridDim.x, it + 1);  // into this tile's dgate buffer, free once the gradient GEMMs are done
+      do_pending = it + 1;
+    }
     // ---- phase 5: add the running d x_hat; !LAST: write it back, LAST: LayerNorm backward + residual -> dz
     {
       float tot[kZCh];
@@ -1098,7 +1103,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   if (threadIdx.x == 0) {
     if (!ok) {  // a wait gave up: copies in flight must land before the CTA exits
       const long long t0 = clock64();
-      while (!mbar_try_wait(w_full, 0) || (in_pending >= 0 && !mbar_try_wait(in_full, in_pending & 1))) {
+      while (!mbar_try_wait(w_full, 0) || (z_pending >= 0 && !mbar_try_wait(z_full, z_pending & 1)) ||
+             (do_pending >= 0 && !mbar_try_wait(do_full, do_pending & 1))) {
         if (clock64() - t0 > kWaitLimitCycles) {
           atomicCAS(p.status, 0, kDevTimeoutDrain);
           break;

@@ -874,10 +874,18 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 #pragma unroll
     for (int kh = 0; kh < 2; ++kh) tma_load_3d(do_i + kh * 16384, &map_do, do_full, j_i + kh * 64, 0, row_i);
   };
+  // The single-thread jobs of a tile sit on three different warps so that they do not queue behind one another: the MMA
+  // issue (threads 0 and 32), the TMA loads of the next tile (thread 96) and the TMA store with its bulk group (thread 64).
+  const bool load_thread = threadIdx.x == 96, store_thread = threadIdx.x == 64;
+  // tile -> (row, column block) without a division per tile
+  const int step_rows = static_cast<int>(gridDim.x) / p.tiles_per_row;
+  const int step_cols = static_cast<int>(gridDim.x) - step_rows * p.tiles_per_row;
+  int row = static_cast<int>(blockIdx.x) / p.tiles_per_row;
+  int jt = static_cast<int>(blockIdx.x) - row * p.tiles_per_row;
   bool ok = true;
   int it = 0;
-  int z_pending = -1, do_pending = -1;  // thread 0: iteration whose copy is in flight, or -1
-  if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < p.num_tiles) {
+  int z_pending = -1, do_pending = -1;  // load thread: iteration whose copy is in flight, or -1
+  if (load_thread && static_cast<int>(blockIdx.x) < p.num_tiles) {
     issue_z(blockIdx.x, 0);
     issue_do(blockIdx.x, 0);
     z_pending = 0, do_pending = 0;
@@ -889,13 +897,16 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     publish_valid(0, in0, a0, b0, c0);
   }
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
-    const int row = tile / p.tiles_per_row;
-    const int j0 = (tile - row * p.tiles_per_row) * 128;
+    if (it != 0) {
+      row += step_rows, jt += step_cols;
+      if (jt >= p.tiles_per_row) jt -= p.tiles_per_row, ++row;
+    }
+    const int j0 = jt * 128;
     const uint32_t z_s = role(it, 0), do_s = role(it, 1), dv_s = role(it, 2), dg_s = role(it, 3);
     const int j = j0 + pos;
     if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
     if (!cta_wait(z_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
-    if (threadIdx.x == 0) z_pending = -1;
+    if (load_thread) z_pending = -1;
     // ---- phase 1: x_hat in place
     const float rstd_in = normalise_tile<true, true, C>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
@@ -906,8 +917,6 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     // keep the tensor pipe busy)
     if (threadIdx.x == 0 || threadIdx.x == 32) {
       const int m = threadIdx.x >> 5;
-      // this tile's dgate scratch held the previous tile's output: its store must have read it before phase 3
-      if (m == 0) bulk_wait_read<0>();
       tc_fence_after();
       constexpr uint32_t idesc = umma_idesc(128, 128, false, false, kFmtF16, kFmtF16);
 #pragma unroll
@@ -918,6 +927,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       }
       umma_commit(mma_bar);
     }
+    // this tile's dgate scratch held the previous tile's output: its store must have read it before phase 3
+    if (store_thread) bulk_wait_read<0>();
     bool nx_in = false;
     uint32_t nx_i = 1u, nx_j = 1u, nx_p = 1u;
     const bool has_next = tile + static_cast<int>(gridDim.x) < p.num_tiles;
@@ -926,7 +937,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     tc_fence_after();
     if (part == 0 && has_next) publish_valid(it + 1, nx_in, nx_i, nx_j, nx_p);
     if (!cta_wait(do_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
-    if (threadIdx.x == 0) do_pending = -1;
+    if (load_thread) do_pending = -1;
     // ---- phase 3: dvalue, dgate for this thread's channel and 32 positions, stored [channel][position]
     {
       const uint32_t vbits = valid_words[(it & 1) * 4 + part];
@@ -972,7 +983,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
-    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
+    if (load_thread && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
       issue_z(tile + gridDim.x, it + 1);  // into this tile's dO buffer, read for the last time in phase 3
       z_pending = it + 1;
     }
@@ -1026,7 +1037,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     }
     if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
     tc_fence_after();
-    if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
+    if (load_thread && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
       issue_do(tile + gridDim.x, it + 1);  // into this tile's dgate buffer, free once the gradient GEMMs are done
       do_pending = it + 1;
     }
@@ -1094,13 +1105,14 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (store_thread) {
 #pragma unroll
       for (int kh = 0; kh < kZHalves; ++kh) tma_store_3d(&map_out, dv_s + kh * 16384, kh * 64, j0, row);
       bulk_commit();
     }
   }
-  if (threadIdx.x == 0) {
+  if (store_thread) bulk_wait<0>();
+  if (load_thread) {
     if (!ok) {  // a wait gave up: copies in flight must land before the CTA exits
       const long long t0 = clock64();
       while (!mbar_try_wait(w_full, 0) || (z_pending >= 0 && !mbar_try_wait(z_full, z_pending & 1)) ||
@@ -1111,7 +1123,6 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
         }
       }
     }
-    bulk_wait<0>();
   }
   __syncthreads();
   if (ok && it > 0) {

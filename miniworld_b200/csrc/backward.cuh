@@ -34,7 +34,8 @@ constexpr int kBwdThreads = 128 * kBwdParts;
 constexpr int kBwdCh = 128 / kBwdParts;          // channels per thread of a 128-channel tile
 constexpr int kBwdChunks = kBwdCh / 8;           // 16-byte chunks (8 channels) per thread
 constexpr int kBwdTile = 32768;  // one [128][128] 16-bit tile
-constexpr int kBwdXchg = kBwdParts * 128 * 8;  // float2 [kBwdParts][128]
+constexpr int kBwdXchgHalf = kBwdParts * 128 * 8;  // float2 [kBwdParts][128]
+constexpr int kBwdXchg = 2 * kBwdXchgHalf;         // two exchange buffers, used in turn (see normalise_tile)
 constexpr int kBwdSmemBytes = 6 * kBwdTile + kBwdXchg + 1024 /* constants */ + 256 /* barriers */ + 1024;
 
 // swizzled byte offset of element (r, e) in a [128 rows][128 elements] 16-bit tile stored as two halves of 64 elements,
@@ -86,6 +87,14 @@ __device__ __forceinline__ void ldg_chunks(const uint4* p, bool wide, uint4 (&ou
 }
 __device__ __forceinline__ float sigmoid_fast(float x) { return fmaf(tanh_approx(0.5f * x), 0.5f, 0.5f); }
 
+// Bounded wait of one thread on an mbarrier, without a CTA-wide barrier (which costs 200-300 cycles for 512 threads, and
+// 540 in the form below): false when the thread gave up or the CTA is giving up. The caller carries on with the tile
+// (every later wait then returns within one poll, on whatever data there is: all addresses stay valid) and the CTA
+// leaves together at the tile's closing barrier, which ANDs the threads' flags.
+__device__ __forceinline__ bool thread_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag, status, code);
+}
 // CTA-wide bounded wait on an mbarrier: one lane per warp polls, the decision is shared by all 256 threads.
 __device__ __forceinline__ bool cta_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   const bool got = mbar_wait_warp(bar, parity, abort_flag, status, code);
@@ -94,7 +103,8 @@ __device__ __forceinline__ bool cta_wait(uint32_t bar, uint32_t parity, volatile
 
 // Normalise the CT channels of every position of a tile in place (fp16 result), the thread covering CT / kBwdParts of them.
 // ROWS_ARE_POSITIONS: element (pos, c) (a [pos][c] tile, input bf16 or fp16), else element (c, pos) (a [c][pos] tile,
-// fp16). Returns rstd of the thread's position. `xchg` holds float2 [kBwdParts][128].
+// fp16). Returns rstd of the thread's position. `xchg` holds float2 [kBwdParts][128]; the caller must not pass the same
+// buffer to two calls (or other uses) without a CTA-wide barrier between them.
 template <bool ROWS_ARE_POSITIONS, bool IN_BF16, int CT = 128>
 __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, int pos, int part, float eps) {
   constexpr int kCh = CT / kBwdParts;  // channels per thread
@@ -162,8 +172,7 @@ __device__ __forceinline__ float normalise_tile(uint32_t tile, uint32_t xchg, in
 #pragma unroll
     for (int cc = 0; cc < kCh; ++cc) st_f16_sat(tile + tile_off(part * kCh + cc, pos), fmaf(xt[cc], rstd, nmr));
   }
-  named_bar_sync(1, kBwdThreads);  // the exchange buffer may be reused
-  return rstd;
+  return rstd;  // (no closing barrier: consecutive calls alternate between the two exchange buffers)
 }
 
 // Sum of the float2 partials the kBwdParts threads of a position left in `xchg` (fixed order).
@@ -352,7 +361,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       for (int kh = 0; kh < kZHalves; ++kh) tma_load_3d(dy_s + kh * 16384, &map_dy, dy_full, kh * 64, j0, row);
       dy_pending = it;
     }
-    normalise_tile<true, true, C>(z_s, xchg, pos, part, p.eps_in);
+    normalise_tile<true, true, C>(z_s, xchg + kBwdXchgHalf, pos, part, p.eps_in);  // (the other exchange buffer)
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -904,9 +913,12 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     const int j0 = jt * 128;
     const uint32_t z_s = role(it, 0), do_s = role(it, 1), dv_s = role(it, 2), dg_s = role(it, 3);
     const int j = j0 + pos;
-    if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
-    if (!cta_wait(z_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    if (it == 0) ok &= thread_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma);
+    ok &= thread_wait(z_full, it & 1, abort_flag, p.status, kDevTimeoutStats);
     if (load_thread) z_pending = -1;
+    // this tile's dgate scratch held the previous tile's output: its store must have read it before phase 3 (the
+    // barrier that closes phase 1 orders this wait before every thread's phase 3)
+    if (store_thread) bulk_wait_read<0>();
     // ---- phase 1: x_hat in place
     const float rstd_in = normalise_tile<true, true, C>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
@@ -927,16 +939,14 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       }
       umma_commit(mma_bar);
     }
-    // this tile's dgate scratch held the previous tile's output: its store must have read it before phase 3
-    if (store_thread) bulk_wait_read<0>();
     bool nx_in = false;
     uint32_t nx_i = 1u, nx_j = 1u, nx_p = 1u;
     const bool has_next = tile + static_cast<int>(gridDim.x) < p.num_tiles;
     if (part == 0 && has_next) mask_bytes(tile + gridDim.x, nx_in, nx_i, nx_j, nx_p);
-    if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
+    ok &= thread_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue);
     tc_fence_after();
     if (part == 0 && has_next) publish_valid(it + 1, nx_in, nx_i, nx_j, nx_p);
-    if (!cta_wait(do_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    ok &= thread_wait(do_full, it & 1, abort_flag, p.status, kDevTimeoutStats);
     if (load_thread) do_pending = -1;
     // ---- phase 3: dvalue, dgate for this thread's channel and 32 positions, stored [channel][position]
     {
@@ -1035,7 +1045,7 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
         ldg_chunks(dyp, (reinterpret_cast<uintptr_t>(p.dy) & 31u) == 0, dy_res);
       }
     }
-    if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
+    ok &= thread_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue);
     tc_fence_after();
     if (load_thread && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
       issue_do(tile + gridDim.x, it + 1);  // into this tile's dgate buffer, free once the gradient GEMMs are done
@@ -1078,10 +1088,11 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 4], tot[ch * 8 + 5])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 6], tot[ch * 8 + 7])));
       } else {
-        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
+        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + kBwdXchgHalf + (part * 128 + pos) * 8), "f"(s1), "f"(s2)
+                     : "memory");
         named_bar_sync(1, kBwdThreads);
         float m1, m2;
-        sum_partials(xchg, pos, m1, m2);
+        sum_partials(xchg + kBwdXchgHalf, pos, m1, m2);
         m1 *= 1.0f / C, m2 *= 1.0f / C;
         const float rs = rstd_in * gc_inv;
 #pragma unroll
@@ -1104,7 +1115,8 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     }
     tc_fence_before();
     fence_proxy_async_smem();
-    __syncthreads();
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;  // a thread that gave up takes the whole CTA out here
+    if (!ok) break;
     if (store_thread) {
 #pragma unroll
       for (int kh = 0; kh < kZHalves; ++kh) tma_store_3d(&map_out, dv_s + kh * 16384, kh * 64, j0, row);

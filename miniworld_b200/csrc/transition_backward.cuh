@@ -364,10 +364,11 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 4], tot[ch * 8 + 5])),
                    pack_f16x2_sat(make_float2(tot[ch * 8 + 6], tot[ch * 8 + 7])));
       } else {
-        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + (part * 128 + pos) * 8), "f"(s1), "f"(s2) : "memory");
+        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xchg + kBwdXchgHalf + (part * 128 + pos) * 8), "f"(s1), "f"(s2)
+                     : "memory");
         named_bar_sync(1, kBwdThreads);
         float m1, m2;
-        sum_partials(xchg, pos, m1, m2);
+        sum_partials(xchg + kBwdXchgHalf, pos, m1, m2);
         m1 *= 1.0f / 128.0f, m2 *= 1.0f / 128.0f;
         const float rs = rstd_in * gc_inv;
         const float res = p.residual ? gc_inv : 0.f;  // the dy tile holds dy * c

@@ -260,6 +260,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
   const uint32_t const_s = xchg + kBwdXchg;
   const uint32_t bar_base = const_s + 1024;
   const uint32_t w_full = bar_base, tz_full = bar_base + 8, mma_bar = bar_base + 16, dy_full = bar_base + 24;
+  const uint32_t sums_done = bar_base + 48;  // every thread arrives once it has read the gradient tiles for the column sums
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBwdTile + kBwdXchg + 1024 + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* const_ptr = reinterpret_cast<float*>(smem + 6 * kBwdTile + kBwdXchg);
@@ -274,6 +275,7 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     mbar_init(tz_full, 1);
     mbar_init(dy_full, 1);
     mbar_init(mma_bar, 1);
+    mbar_init(sums_done, kBwdThreads);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&map_t);
@@ -334,8 +336,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     const int j0 = (tile - row * p.tiles_per_row) * 128;
     const uint32_t t_s = tiles_s + ((it & 1) * 2) * kBwdTile, z_s = t_s + kBwdTile;
     const uint32_t dy_s = tiles_s + (((it & 1) ^ 1) * 2) * kBwdTile, dg_s = dy_s + kBwdTile;
-    if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
-    if (!cta_wait(tz_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    if (it == 0) ok &= thread_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma);
+    ok &= thread_wait(tz_full, it & 1, abort_flag, p.status, kDevTimeoutStats);
     if (threadIdx.x == 0) tz_pending = -1;
     // ---- phase 1: normalise t (rows = channels) and z (rows = positions) in place
     float rstd_out;
@@ -403,8 +405,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
       ldg_chunks(reinterpret_cast<const uint4*>(p.drop_scale + (static_cast<size_t>(b) * p.n + j) * C + part * kZCh),
                  (reinterpret_cast<uintptr_t>(p.drop_scale) & 31u) == 0, scv);
     }
-    if (!cta_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
-    if (!cta_wait(dy_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    ok &= thread_wait(mma_bar, 0, abort_flag, p.status, kDevTimeoutEpilogue);
+    ok &= thread_wait(dy_full, it & 1, abort_flag, p.status, kDevTimeoutStats);
     if (threadIdx.x == 0) dy_pending = -1;
     tc_fence_after();
     // ---- phase 3: dproj = c du gate, dgate = c du proj gate (1 - gate); du = dy (* dropout scale)
@@ -522,10 +524,13 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
         }
       }
     }
-    if (!cta_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue)) { ok = false; break; }
+    mbar_arrive(sums_done);
+    ok &= thread_wait(mma_bar, 1, abort_flag, p.status, kDevTimeoutEpilogue);
     tc_fence_after();
     if (threadIdx.x == 0 && tile + static_cast<int>(gridDim.x) < p.num_tiles) {
-      issue_tz(tile + gridDim.x, it + 1);  // into this tile's dy and dgate buffers, which the GEMMs have finished with
+      // into this tile's dy and dgate buffers: the GEMMs have finished with them, and so must every thread's column sums
+      ok &= thread_wait(sums_done, it & 1, abort_flag, p.status, kDevTimeoutEpilogue);
+      issue_tz(tile + gridDim.x, it + 1);
       tz_pending = it + 1;
     }
     // ---- phase 5: LayerNorm backward of the output normalisation, in place over t_hat; dxg over x_hat
@@ -592,7 +597,8 @@ bwd_epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_cons
     }
     tc_fence_before();
     fence_proxy_async_smem();
-    __syncthreads();
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;  // a thread that gave up takes the whole CTA out here
+    if (!ok) break;
     if (threadIdx.x == 0) {
 #pragma unroll
       for (int kh = 0; kh < 2; ++kh)

@@ -98,7 +98,8 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   bool loads_pending = false;
   uint32_t mma_phase = 0;
   auto mma_wait = [&]() {
-    const bool got = cta_wait(mma_bar, mma_phase, abort_flag, p.status, kDevTimeoutEpilogue);
+    // per thread, no CTA-wide barrier: a thread that gives up carries on and the CTA leaves at the tile's last barrier
+    const bool got = thread_wait(mma_bar, mma_phase, abort_flag, p.status, kDevTimeoutEpilogue);
     mma_phase ^= 1u;
     return got;
   };
@@ -130,8 +131,8 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       if (!loads_pending) issue_inputs(p0);  // (not LAST: requested while the previous tile finished)
       bulk_wait_read<0>();                   // the previous tile's store has read the scratch tile
     }
-    if (it == 0 && !cta_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma)) { ok = false; break; }
-    if (!cta_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats)) { ok = false; break; }
+    if (it == 0) ok &= thread_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma);
+    ok &= thread_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats);
     loads_pending = false;  // (only thread 0's copy is read)
     // ---- dy * c as fp16 in place (x_hat follows while the first GEMM runs)
 #pragma unroll
@@ -163,7 +164,7 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     // ---- x_hat in place, in the shadow of the dh GEMM (which reads dy and Ws only)
     const float rstd_in = normalise_tile<true, true, 128>(x_s, xchg, pos, part, p.eps);
     fence_proxy_async_smem();
-    if (!mma_wait()) { ok = false; break; }
+    ok &= mma_wait();
     tc_fence_after();
     float dh[kBwdCh];
 #pragma unroll
@@ -188,7 +189,7 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
       umma_commit(mma_bar);
     }
-    if (!mma_wait()) { ok = false; break; }
+    ok &= mma_wait();
     tc_fence_after();
     float av[kBwdCh];
 #pragma unroll
@@ -218,7 +219,7 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
       umma_commit(mma_bar);
     }
-    if (!mma_wait()) { ok = false; break; }
+    ok &= mma_wait();
     tc_fence_after();
     uint32_t db_p[kBwdCh / 2], h_p[kBwdCh / 2];
 #pragma unroll
@@ -271,7 +272,8 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       umma_commit(mma_bar);
     }
     column_sum(sa_acc);  // reads the tile the MMAs read
-    if (!mma_wait()) { ok = false; break; }
+    ok &= mma_wait();
+    named_bar_sync(1, kBwdThreads);  // every thread's column-sum reads come before the tile is rewritten
     // ---- db -> scratch; d x_hat += db Wb_j', Mb += db^T x_hat (columns 256-383)
 #pragma unroll
     for (int ch = 0; ch < kBwdChunks; ++ch)
@@ -294,7 +296,8 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       umma_commit(mma_bar);
     }
     column_sum(sb_acc);
-    if (!mma_wait()) { ok = false; break; }
+    ok &= mma_wait();
+    named_bar_sync(1, kBwdThreads);
     // ---- h -> scratch; dWs_j += dy^T h (columns 384-511; lanes = channels c, columns = hidden units)
 #pragma unroll
     for (int ch = 0; ch < kBwdChunks; ++ch)
@@ -323,7 +326,7 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         ldg_chunks(src, true, dx_prev);  // the workspace is 1024-byte aligned
       }
     }
-    if (!mma_wait()) { ok = false; break; }
+    ok &= mma_wait();
     tc_fence_after();
     if constexpr (!LAST) {
       // x_hat and dy * c have been read for the last time: the next tile's inputs land while this one finishes
@@ -392,7 +395,8 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
     tc_fence_before();
     fence_proxy_async_smem();
-    __syncthreads();
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;  // a thread that gave up takes the whole CTA out here
+    if (!ok) break;
     if (threadIdx.x == 0) {
 #pragma unroll
       for (int kh = 0; kh < 2; ++kh) tma_store_2d(&map_out, s_s + kh * 16384, kh * 64, p0);

@@ -87,13 +87,9 @@ __device__ __forceinline__ void ldg_chunks(const uint4* p, bool wide, uint4 (&ou
 }
 __device__ __forceinline__ float sigmoid_fast(float x) { return fmaf(tanh_approx(0.5f * x), 0.5f, 0.5f); }
 
-// Bounded wait of one thread on an mbarrier, without a CTA-wide barrier (which costs 200-300 cycles for 512 threads, and
-// 540 in the form below): false when the thread gave up or the CTA is giving up. The caller carries on with the tile
-// (every later wait then returns within one poll, on whatever data there is: all addresses stay valid) and the CTA
-// leaves together at the tile's closing barrier, which ANDs the threads' flags.
+// (see mbar_wait_thread: a thread that gives up carries on and the CTA leaves together at the tile's closing barrier)
 __device__ __forceinline__ bool thread_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait(bar, parity, abort_flag, status, code);
+  return mbar_wait_thread(bar, parity, abort_flag, status, code);
 }
 // CTA-wide bounded wait on an mbarrier: one lane per warp polls, the decision is shared by all 256 threads.
 __device__ __forceinline__ bool cta_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {

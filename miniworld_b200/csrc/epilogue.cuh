@@ -230,15 +230,14 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
     const uint32_t tcol = ts + ((2 * pp) >> 6) * 16384 + ((pp & 3) << 2);
     const uint32_t tchunk = ((2 * pp) & 63) >> 3;
     int it = 0;
+    bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       if ((it & 1) != grp) continue;
       const uint32_t ph = (it >> 1) & 1;
       const int row = tile / p.tiles_per_row;
       const int j0 = (tile - row * p.tiles_per_row) * 128;
-      {
-        const bool got = mbar_wait_warp(t_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
-        if (!named_bar_and(bar_id, 256, got)) break;
-      }
+      // (waits are per thread; a thread that gives up carries on and the group leaves at the tile's last barrier)
+      ok &= mbar_wait_thread(t_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
       // ---- output partial statistics: two adjacent positions, 32 channels of the t tile
       {
         float2 pv = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
@@ -260,10 +259,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
                      "f"(m20), "f"(mean1), "f"(m21)
                      : "memory");
       }
-      {
-        const bool got = mbar_wait_warp(z_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
-        if (!named_bar_and(bar_id, 256, got)) break;
-      }
+      ok &= mbar_wait_thread(z_full(grp), ph, abort_flag, p.status, kDevTimeoutStats);
       // ---- input partial statistics over this thread's C / 2 channels of its z row (kept for the residual)
       // C = 128: the thread's channels are one 64-channel half of the tile; C = 64: four of the eight 16-byte chunks of
       // the tile's only half
@@ -323,12 +319,9 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
       const float2 rs_in2 = make_float2(rs_in, rs_in), nmr_in2 = make_float2(nmr_in, nmr_in);
       const float2 rs_out2 = make_float2(rs_out, rs_out), nmr_out2 = make_float2(nmr_out, nmr_out);
 
-      {
-        const bool got = mbar_wait_warp(acc_full(grp), ph, abort_flag, p.status, kDevTimeoutEpilogue);
-        if (!named_bar_and(bar_id, 256, got)) break;
-      }
+      ok &= mbar_wait_thread(acc_full(grp), ph, abort_flag, p.status, kDevTimeoutEpilogue);
       tc_fence_after();
-      // every thread is past its output statistics (barrier above) and the P MMAs are complete: t is dead
+      // every thread is past its output statistics (the exchange barrier above) and the P MMAs are complete: t is dead
       if (store_thread) mbar_arrive(t_empty(grp));
       // C / 16 chunks of 8 channels; the TMEM loads of chunk cc+1 are in flight while chunk cc is finished
       uint32_t vp[2][8], vg[2][8];
@@ -371,7 +364,7 @@ epilogue_kernel(const __grid_constant__ CUtensorMap map_t, const __grid_constant
                      : "memory");
       }
       fence_proxy_async_smem();
-      named_bar_sync(bar_id, 256);
+      if (!named_bar_and(bar_id, 256, ok)) break;
       if (store_thread) {
 #pragma unroll
         for (int kh = 0; kh < kZHalves; ++kh) tma_store_3d(&map_y, zs + kh * 16384, kh * 64, j0, row);

@@ -233,7 +233,7 @@ def test_errors_are_loud():
 
 
 def test_large_complex_workload_full_size_rows():
-    """BASELINE workload 4 (B = 1, N = 2048, 4 chains, 5 % of tokens masked) at full size: a sample of pair rows is
+    """The large-complex workload (B = 1, N = 2048, 4 chains, 5 % of tokens masked) at full size: a sample of pair rows is
     compared with the oracle (which forms the O(N^3) contraction only for those rows), both directions; plus the
     size-independent identity that an all-invalid mask returns the input."""
     w = make_workload("complex2048", seed=0)
@@ -258,7 +258,7 @@ def test_large_complex_workload_full_size_rows():
 
 
 def test_fp32_workload_is_served_through_bf16():
-    """BASELINE workload 0 (fp32, N = 128, all-ones mask, outgoing) is a CPU configuration of the reference; the
+    """The fp32 workload (N = 128, all-ones mask, outgoing) is a CPU configuration of the reference; the
     module takes the fp32 tensor, rounds it to bf16 once, and returns fp32. Checked against the oracle evaluated on
     the same rounded input and weights."""
     w = make_workload("cpu128", seed=0)

@@ -379,3 +379,33 @@ def test_backward_numerical_corners(kind):
     _check("dz", zd.grad, dz_ref, tol)
     for k in _PARAM_KEYS:
         _check(k, pd[k].grad, gp_ref[k], tol)
+
+
+def test_backward_soak_is_bit_identical():
+    """The backward kernels synchronise through per-thread waits on mbarriers with few CTA-wide barriers; a missing
+    order would show as run-to-run differences. Forty backward calls (N = 384: three 128-wide
+    column blocks per row, ragged masks, both directions, plus the bidirectional module) must give the first call's bits
+    for the input gradient and every parameter gradient."""
+    from miniworld_b200 import functional as F_
+    from tests.test_gpu_bidirectional import bidir_params
+
+    B, N = 1, 384
+    g = torch.Generator().manual_seed(4242)
+    z = torch.randn(B, N, N, 128, generator=g).to(torch.bfloat16).to(DEV)
+    dy = (torch.randn(B, N, N, 128, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    mask = (torch.rand(B, N, generator=g) > 0.15).to(DEV)
+    for outgoing in (True, False, None):
+        p = bidir_params(77) if outgoing is None else rand_params(76)
+        p = {k: v.to(DEV) for k, v in p.items()}
+        ws = F_.aligned_empty(F_.workspace_bytes(B, N, outgoing), torch.device(DEV))
+        F_.trimul_forward(z, p, mask, outgoing=outgoing, workspace=ws)
+        first = None
+        for it in range(40 if outgoing is not None else 15):
+            dz, grads = F_.trimul_backward(dy, z, p, ws, mask, outgoing=outgoing, check=True)
+            cur = [dz] + [grads[k] for k in sorted(grads)]
+            assert all(torch.isfinite(t.float()).all() for t in cur)
+            if first is None:
+                first = [t.clone() for t in cur]
+            else:
+                for a, b in zip(first, cur):
+                    assert torch.equal(a, b), (outgoing, it)

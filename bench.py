@@ -167,6 +167,25 @@ def time_events(fn, steps: int, stream, before_end=None) -> float:
     return start.elapsed_time(end)
 
 
+def graph_ms(fn, steps: int, stream, dev):
+    """Median milliseconds per call of fn replayed from a CUDA graph of one call (device-paced launches), or None
+    when the call cannot be captured here."""
+    try:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            fn()
+        stream.wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        for _ in range(3):
+            graph.replay()
+        return statistics.median(sorted(time_events(graph.replay, steps, stream) / steps for _ in range(REPEATS)))
+    except RuntimeError:
+        return None
+
+
 class HostPipeline:
     """End-to-end step with host buffers: pinned z -> device (copy stream), two module forwards (current
     stream), y -> pinned host (second copy stream). Two device input buffers, so the copies of one step overlap
@@ -650,6 +669,9 @@ def block_operators(r: "Runner", steps: int, stream, dev) -> dict:
     ms = sorted(time_events(tr_bwd, steps, stream) / steps for _ in range(REPEATS))
     out["training"]["transition"] = {"ms_forward": out["transition"]["ms_per_forward"], "ms_backward": statistics.median(ms),
                                      "backward_over_forward": statistics.median(ms) / out["transition"]["ms_per_forward"]}
+    g = graph_ms(tr_bwd, steps, stream, dev)
+    if g is not None:
+        out["training"]["transition"]["ms_backward_graph"] = g
     return out
 
 
@@ -683,6 +705,9 @@ def training_step(r: "Runner", steps: int, stream, dev, bid) -> dict:
                 fn()
             ms = sorted(time_events(fn, steps, stream) / steps for _ in range(REPEATS))
             entry[f"ms_{name}"] = statistics.median(ms)
+        g = graph_ms(bwd, steps, stream, dev)  # the same call with device-paced launches
+        if g is not None:
+            entry["ms_backward_graph"] = g
         F_.check_status(bws[:64].view(torch.int32), "b200_trimul_backward")
         entry["backward_over_forward"] = entry["ms_backward"] / entry["ms_forward"]
         res[direction] = entry

@@ -75,6 +75,10 @@ struct OutputMaps {
   int n_left, n_right;
   int step_left, step_right;    // bytes between the destinations' channel slices in a 16 KiB half staging tile
   int shift_left, shift_right;  // added to the row coordinate
+  // One GPU: the same two outputs with a box of 32 channel rows, so that every epilogue warp stores the 32 rows it
+  // wrote by itself and the warps of a group never wait for one another (warp_store != 0).
+  CUtensorMap left_warp, right_warp;
+  int warp_store;
 };
 
 constexpr int kProThreads = 864;

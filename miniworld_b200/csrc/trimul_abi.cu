@@ -584,6 +584,15 @@ static int prologue_impl(const void* z, const void* packed, const uint8_t* token
     out.step_left = out.step_right = mode == kChannels ? static_cast<int>(ch) * 128 : 0;
     out.shift_left = mode == kChannels ? row_begin : 0;
     out.shift_right = mode == kLocal ? 0 : row_begin;
+    out.warp_store = 0;
+    if (mode == kLocal && n_left == 1 && n_right == 1) {
+      const uint32_t box_w[3] = {64, 32, 1};
+      rc = make_map(&out.left_warp, left_dst[0], 3, dims_local, strides, box_w);
+      if (rc != B200_TRIMUL_OK) return rc;
+      rc = make_map(&out.right_warp, right_dst[0], 3, dims_local, strides, box_w);
+      if (rc != B200_TRIMUL_OK) return rc;
+      out.warp_store = 1;
+    }
   }
   {
     // the four left / right matrices [128, d_pair], one after the other at the start of the packed block

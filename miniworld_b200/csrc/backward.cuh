@@ -918,11 +918,11 @@ bwd_prologue_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     if (it == 0) ok &= thread_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma);
     ok &= thread_wait(z_full, it & 1, abort_flag, p.status, kDevTimeoutStats);
     if (load_thread) z_pending = -1;
+    // ---- phase 1: x_hat in place
+    const float rstd_in = normalise_tile<true, true, C>(z_s, xchg, pos, part, p.eps_in);
     // this tile's dgate scratch held the previous tile's output: its store must have read it before phase 3 (the
     // barrier that closes phase 1 orders this wait before every thread's phase 3)
     if (store_thread) bulk_wait_read<0>();
-    // ---- phase 1: x_hat in place
-    const float rstd_in = normalise_tile<true, true, C>(z_s, xchg, pos, part, p.eps_in);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();

@@ -129,7 +129,6 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int p0 = tile * 128;
     if (threadIdx.x == 0) {
       if (!loads_pending) issue_inputs(p0);  // (not LAST: requested while the previous tile finished)
-      bulk_wait_read<0>();                   // the previous tile's store has read the scratch tile
     }
     if (it == 0) ok &= thread_wait(w_full, 0, abort_flag, p.status, kDevTimeoutMma);
     ok &= thread_wait(in_full, it & 1, abort_flag, p.status, kDevTimeoutStats);
@@ -148,6 +147,9 @@ bwd_transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
       st_chunk(addr, o[0], o[1], o[2], o[3]);
     }
+    // the previous tile's store has read the scratch tile (rewritten after the third GEMM round; the barrier below
+    // orders this wait before every thread's writes)
+    if (threadIdx.x == 0) bulk_wait_read<0>();
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();

@@ -229,8 +229,9 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const uint32_t ws = w_base + slot * kTrWStageBytes + 16384;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          // H[b]: 32 columns of the D2 buffer that is idle during this tile; 8 columns = 16 fp16 per 16-deep MMA
-          const uint32_t a_tmem = tmem_base + kTrColD2 + ((t + 1) & 1) * 128 + b * 32 + ks * 8;
+          // H[b][(hb >> 1) & 1]: 32 of the 128 columns of the D2 buffer that is idle during this tile (two buffers per
+          // SwiGLU group, used in turn); 8 columns = 16 fp16 per 16-deep MMA
+          const uint32_t a_tmem = tmem_base + kTrColD2 + ((t + 1) & 1) * 128 + ((hb >> 1) & 1) * 64 + b * 32 + ks * 8;
           const uint64_t db = umma_desc_kmajor(ws) + static_cast<uint64_t>(ks * 2);
           umma_pair_ta(tmem_base + kTrColD2 + (t & 1) * 128, a_tmem, db, idesc, (hb | ks) != 0 ? 1u : 0u);
         }
@@ -312,9 +313,10 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     const uint32_t t_d1 = tmem_base + lane_off + grp * 128 + uh * 32;
     for (int t = 0; t < my_tiles; ++t) {
-      // h of this tile borrows the first 64 columns of the D2 buffer that is not accumulating: H[grp] = 32 of them
+      // h of this tile borrows the D2 buffer that is not accumulating: H[grp][0 / 1] = 32 columns each, used in turn, so
+      // that a block's h never waits for the G2 of the group's previous block
       const int hbuf = (t + 1) & 1;
-      const uint32_t t_h = tmem_base + lane_off + kTrColD2 + hbuf * 128 + grp * 32 + uh * 16;
+      const uint32_t t_h0 = tmem_base + lane_off + kTrColD2 + hbuf * 128 + grp * 32 + uh * 16;
       bool alive = true;
 #pragma unroll 1
       for (int hb = grp; hb < kTrBlocks; hb += 2) {
@@ -345,10 +347,12 @@ transition_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             o[pq * 8 + i] = pack_f16x2_sat(__fmul2_rn(__ffma2_rn(th, a2, a2), bb));
           }
         }
-        // H[grp] is free once G2 of block gb - 2 (weight stage (gb - 2) % WS) is complete; the first h of a tile also
-        // waits until this CTA's output group has read tile t - 1 out of the D2 buffer that h borrows
-        if (gb >= 2) {
-          const long long pb = gb - 2;
+        // this H buffer is free once G2 of block gb - 4 (weight stage (gb - 4) % WS) is complete (block gb + 1, the next
+        // one in the same stage, cannot have completed yet: its G2 is issued after this block's); the first h of a tile
+        // also waits until this CTA's output group has read tile t - 1 out of the D2 buffer that h borrows
+        const uint32_t t_h = t_h0 + ((hb >> 1) & 1) * 64;
+        if (gb >= 4) {
+          const long long pb = gb - 4;
           if (!mbar_wait_warp(blk_done(static_cast<int>(pb % WS)), static_cast<uint32_t>((pb / WS) & 1), abort_flag, p.status,
                               kDevTimeoutEpilogue)) {
             alive = false;
